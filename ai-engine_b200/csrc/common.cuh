@@ -1,0 +1,71 @@
+// Shared device helpers for the sm_100a kernels: dtype conversion, block
+// reductions with a fixed order (so a row's result does not depend on what
+// else is in the batch), and the device error word.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+// dtype codes of the extern "C" launchers
+#define AIE_F32 0
+#define AIE_BF16 1
+
+// launcher return codes (>0 are cudaError_t values)
+#define AIE_BAD_ARG (-1)
+#define AIE_UNSUPPORTED (-2)
+
+// bits of the device error word that kernels set instead of trapping
+#define AIE_DEV_TOKEN_OOB 1u    // token id outside the vocabulary
+#define AIE_DEV_PAGE_OOB 2u     // block table entry outside the pool
+#define AIE_DEV_WAIT_TIMEOUT 4u // a bounded wait ran out
+#define AIE_DEV_SLOT_OOB 8u     // request row / slot outside its table
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum / max; every thread gets the result.  `red` is >= 32 floats of
+// shared memory.  The order of additions is fixed by the block size alone.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = (lane < nw) ? red[lane] : 0.f;
+    r = warp_sum(r);
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = (lane < nw) ? red[lane] : -INFINITY;
+    r = warp_max(r);
+    return r;
+}
+
+#define AIE_LAUNCH_CHECK()                                   \
+    do {                                                     \
+        cudaError_t e__ = cudaGetLastError();                \
+        return (int)e__;                                     \
+    } while (0)

@@ -1,0 +1,154 @@
+// Memory-bound row kernels: embedding gather, residual add fused with RMSNorm,
+// SiLU(gate) * up, dtype casts.  The residual stream is float32 in both compute
+// dtypes; statistics and scaling are float32.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// x[t, :] = float(E[ids[t], :])        (crates/ai-engine-runtime/src/arch/embedding.rs:14-20)
+// ---------------------------------------------------------------------------
+template <typename W>
+__global__ void embed_gather_kernel(const int* __restrict__ ids, const W* __restrict__ table,
+                                    float* __restrict__ x, int D, int vocab, unsigned* err) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicOr(err, AIE_DEV_TOKEN_OOB);
+        for (int i = threadIdx.x; i < D; i += blockDim.x) x[(size_t)t * D + i] = 0.f;
+        return;
+    }
+    const W* row = table + (size_t)id * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) x[(size_t)t * D + i] = to_f32<W>(row[i]);
+}
+
+extern "C" int aie_embed_gather(const int* ids, const void* table, int table_dtype, float* x,
+                                int T, int D, int vocab, unsigned* err, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (table_dtype == AIE_F32)
+        embed_gather_kernel<float><<<T, 256, 0, stream>>>(ids, (const float*)table, x, D, vocab, err);
+    else if (table_dtype == AIE_BF16)
+        embed_gather_kernel<bf16><<<T, 256, 0, stream>>>(ids, (const bf16*)table, x, D, vocab, err);
+    else
+        return AIE_BAD_ARG;
+    AIE_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// Residual add + RMSNorm (crates/ai-engine-runtime/src/arch/rmsnorm.rs:29-42):
+//   s = x[row] (+ delta[row]);  ms = mean(s^2);  r = 1/sqrt(ms + eps);
+//   out[i] = (s * r) * w          with eps inside the root and the weight last.
+// `rows` (optional) picks input rows; `write_back` stores s into x.
+// ---------------------------------------------------------------------------
+template <typename A, typename W, typename O>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const A* __restrict__ delta,
+                                   const W* __restrict__ w, O* __restrict__ out,
+                                   const int* __restrict__ rows, int D, float eps, int write_back) {
+    extern __shared__ float srow[];   // D floats + 32
+    float* red = srow + D;
+    const int o = blockIdx.x;
+    const size_t r = rows ? (size_t)rows[o] : (size_t)o;
+    float* xr = x + r * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float s = xr[i];
+        if (delta) s += to_f32<A>(delta[r * D + i]);
+        srow[i] = s;
+        ss += s * s;
+    }
+    ss = block_sum(ss, red);
+    const float ms = ss / (float)D;
+    const float rinv = 1.0f / sqrtf(ms + eps);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float s = srow[i];
+        if (write_back) xr[i] = s;
+        out[(size_t)o * D + i] = from_f32<O>((s * rinv) * to_f32<W>(w[i]));
+    }
+}
+
+template <typename A, typename W>
+static int launch_rmsnorm_o(float* x, const void* delta, const void* w, void* out, int out_dtype,
+                            const int* rows, int n, int D, float eps, int write_back,
+                            cudaStream_t stream) {
+    const size_t smem = (size_t)(D + 32) * sizeof(float);
+    if (smem > 200 * 1024) return AIE_UNSUPPORTED;
+    const int threads = D >= 1024 ? 512 : 256;
+    if (out_dtype == AIE_F32) {
+        auto k = add_rmsnorm_kernel<A, W, float>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k<<<n, threads, smem, stream>>>(x, (const A*)delta, (const W*)w, (float*)out, rows, D, eps, write_back);
+    } else if (out_dtype == AIE_BF16) {
+        auto k = add_rmsnorm_kernel<A, W, bf16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k<<<n, threads, smem, stream>>>(x, (const A*)delta, (const W*)w, (bf16*)out, rows, D, eps, write_back);
+    } else
+        return AIE_BAD_ARG;
+    AIE_LAUNCH_CHECK();
+}
+
+extern "C" int aie_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void* w,
+                               int w_dtype, void* out, int out_dtype, const int* rows, int n, int D,
+                               float eps, int write_back, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (delta == nullptr) delta_dtype = AIE_F32;
+#define GO(A, W) return launch_rmsnorm_o<A, W>(x, delta, w, out, out_dtype, rows, n, D, eps, write_back, stream)
+    if (delta_dtype == AIE_F32 && w_dtype == AIE_F32) GO(float, float);
+    if (delta_dtype == AIE_F32 && w_dtype == AIE_BF16) GO(float, bf16);
+    if (delta_dtype == AIE_BF16 && w_dtype == AIE_F32) GO(bf16, float);
+    if (delta_dtype == AIE_BF16 && w_dtype == AIE_BF16) GO(bf16, bf16);
+#undef GO
+    return AIE_BAD_ARG;
+}
+
+// ---------------------------------------------------------------------------
+// a[t, f] = silu(gu[t, f]) * gu[t, F + f]   (crates/ai-engine-runtime/src/arch/ffn.rs:50-54)
+// silu(z) = z * sigmoid(z), in float32.
+// ---------------------------------------------------------------------------
+template <typename A>
+__global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ a, int F, size_t total) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const size_t t = i / F, f = i % F;
+        const float g = to_f32<A>(gu[t * 2 * F + f]);
+        const float u = to_f32<A>(gu[t * 2 * F + F + f]);
+        const float s = g * (1.0f / (1.0f + expf(-g)));
+        a[i] = from_f32<A>(s * u);
+    }
+}
+
+extern "C" int aie_silu_mul(const void* gu, void* a, int dtype, int T, int F, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const size_t total = (size_t)T * F;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == AIE_F32)
+        silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)a, F, total);
+    else if (dtype == AIE_BF16)
+        silu_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)a, F, total);
+    else
+        return AIE_BAD_ARG;
+    AIE_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// casts between float32 and bfloat16 (a 32-bit weight under bf16 activations)
+// ---------------------------------------------------------------------------
+template <typename I, typename O>
+__global__ void cast_kernel(const I* __restrict__ in, O* __restrict__ out, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) out[i] = from_f32<O>(to_f32<I>(in[i]));
+}
+
+extern "C" int aie_cast(const void* in, int in_dtype, void* out, int out_dtype, long long n,
+                        cudaStream_t stream) {
+    if (n <= 0) return 0;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (in_dtype == AIE_F32 && out_dtype == AIE_BF16)
+        cast_kernel<float, bf16><<<blocks, 256, 0, stream>>>((const float*)in, (bf16*)out, (size_t)n);
+    else if (in_dtype == AIE_BF16 && out_dtype == AIE_F32)
+        cast_kernel<bf16, float><<<blocks, 256, 0, stream>>>((const bf16*)in, (float*)out, (size_t)n);
+    else
+        return AIE_BAD_ARG;
+    AIE_LAUNCH_CHECK();
+}

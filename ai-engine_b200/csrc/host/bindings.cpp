@@ -1,0 +1,105 @@
+// pybind11 bindings of the host runtime (cache manager, scheduler).
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "runtime.hpp"
+
+namespace py = pybind11;
+using namespace aie;
+
+PYBIND11_MODULE(_aie_host, m) {
+    m.doc() = "host runtime: page pool, block tables, state slots, scheduler";
+
+    py::class_<PagePool>(m, "PagePool")
+        .def(py::init<int>())
+        .def_property_readonly("num_pages", &PagePool::num_pages)
+        .def_property_readonly("free_count", &PagePool::free_count)
+        .def_property_readonly("in_use", &PagePool::in_use)
+        .def_property_readonly("high_water", &PagePool::high_water)
+        .def_property_readonly("total_allocations", &PagePool::total_allocations)
+        .def("is_held", &PagePool::is_held)
+        .def("alloc", [](PagePool& p, int n) -> py::object {
+            std::vector<int> out;
+            if (!p.alloc(n, out)) return py::none();
+            return py::cast(out);
+        })
+        .def("release", &PagePool::release);
+
+    py::class_<GroupSpec>(m, "GroupSpec")
+        .def(py::init([](int page_size, int num_pages, int window) {
+                 GroupSpec g; g.page_size = page_size; g.num_pages = num_pages; g.window = window; return g;
+             }), py::arg("page_size"), py::arg("num_pages"), py::arg("window") = 0)
+        .def_readwrite("page_size", &GroupSpec::page_size)
+        .def_readwrite("num_pages", &GroupSpec::num_pages)
+        .def_readwrite("window", &GroupSpec::window);
+
+    py::class_<CacheManager>(m, "CacheManager")
+        .def(py::init<std::vector<GroupSpec>, int, int>(), py::arg("groups"), py::arg("max_seqs"), py::arg("max_pages_per_seq"))
+        .def_property_readonly("num_groups", &CacheManager::num_groups)
+        .def_property_readonly("max_seqs", &CacheManager::max_seqs)
+        .def_property_readonly("max_pages_per_seq", &CacheManager::max_pages_per_seq)
+        .def_property_readonly("free_slots", &CacheManager::free_slots)
+        .def("group", &CacheManager::group)
+        .def("free_pages", [](const CacheManager& c, int g) { return c.pool(g).free_count(); })
+        .def("pages_in_use", [](const CacheManager& c, int g) { return c.pool(g).in_use(); })
+        .def("high_water", [](const CacheManager& c, int g) { return c.pool(g).high_water(); })
+        .def("total_allocations", [](const CacheManager& c, int g) { return c.pool(g).total_allocations(); })
+        .def("slot_live", &CacheManager::slot_live)
+        .def("admit", &CacheManager::admit)
+        .def("ensure", &CacheManager::ensure)
+        .def("tokens_that_fit", &CacheManager::tokens_that_fit)
+        .def("advance", &CacheManager::advance)
+        .def("release_pages", &CacheManager::release_pages)
+        .def("finish", &CacheManager::finish)
+        .def("pages", &CacheManager::pages)
+        .def("first_live", &CacheManager::first_live)
+        .def("check_invariants", &CacheManager::check_invariants)
+        .def("fill_block_table", [](const CacheManager& c, int g, std::vector<int> slots, int width,
+                                    py::array_t<int32_t, py::array::c_style> out) {
+            auto buf = out.mutable_unchecked<2>();
+            if (buf.shape(0) < (py::ssize_t)slots.size() || buf.shape(1) != width)
+                throw std::invalid_argument("fill_block_table: out must be [>= len(slots), width]");
+            c.fill_block_table(g, slots.data(), (int)slots.size(), width, out.mutable_data());
+        });
+
+    py::class_<StepEntry>(m, "StepEntry")
+        .def_readonly("id", &StepEntry::id)
+        .def_readonly("slot", &StepEntry::slot)
+        .def_readonly("start", &StepEntry::start)
+        .def_readonly("n_tokens", &StepEntry::n_tokens)
+        .def_readonly("sample", &StepEntry::sample)
+        .def("__repr__", [](const StepEntry& e) {
+            return "StepEntry(id=" + std::to_string(e.id) + ", slot=" + std::to_string(e.slot) + ", start=" + std::to_string(e.start) +
+                   ", n_tokens=" + std::to_string(e.n_tokens) + ", sample=" + (e.sample ? "True" : "False") + ")";
+        });
+
+    py::class_<StepPlan>(m, "StepPlan")
+        .def_readonly("entries", &StepPlan::entries)
+        .def_readonly("preempted", &StepPlan::preempted)
+        .def_readonly("admitted", &StepPlan::admitted);
+
+    py::class_<Scheduler>(m, "Scheduler")
+        .def(py::init<CacheManager*, int, int, int>(), py::arg("cache"), py::arg("max_num_seqs"),
+             py::arg("max_num_batched_tokens"), py::arg("max_seq_len"), py::keep_alive<1, 2>())
+        .def("add", &Scheduler::add)
+        .def("has_work", &Scheduler::has_work)
+        .def_property_readonly("num_running", &Scheduler::num_running)
+        .def_property_readonly("num_waiting", &Scheduler::num_waiting)
+        .def("schedule", &Scheduler::schedule)
+        .def("commit", &Scheduler::commit)
+        .def("on_token", &Scheduler::on_token)
+        .def("finish", &Scheduler::finish)
+        .def("computed", &Scheduler::computed)
+        .def("generated", &Scheduler::generated)
+        .def("slot", &Scheduler::slot)
+        .def("running", &Scheduler::running)
+        .def("waiting", &Scheduler::waiting)
+        .def("stats", [](const Scheduler& s) {
+            const auto& st = s.stats();
+            py::dict d;
+            d["steps"] = st.steps; d["prompt_tokens"] = st.prompt_tokens; d["decode_tokens"] = st.decode_tokens;
+            d["preemptions"] = st.preemptions; d["admitted"] = st.admitted; d["finished"] = st.finished;
+            return d;
+        });
+}

@@ -1,0 +1,199 @@
+"""Python faces of the CUDA kernels: each takes torch tensors on the device,
+checks what the kernel cannot check itself, and launches on torch's current
+stream.  Shapes and dtypes a kernel does not take are refused with an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from .loader import KernelError, check, library, require_cuda
+
+F32, BF16 = 0, 1
+
+
+def dtype_code(t) -> int:
+    dt = t if isinstance(t, torch.dtype) else t.dtype
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"dtype {dt} is not taken by the kernels (float32, bfloat16)")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dev(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            require_cuda()
+            raise KernelError("kernel operands must live on the CUDA device")
+        if t is not None and not t.is_contiguous():
+            raise KernelError("kernel operands must be contiguous")
+
+
+# ---------------------------------------------------------------------------
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, err: torch.Tensor,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x[t] = float32(table[ids[t]]); an id outside the table sets the error word."""
+    _dev(ids, table, err)
+    T, (V, D) = ids.shape[0], table.shape
+    if out is None:
+        out = torch.empty((T, D), dtype=torch.float32, device=table.device)
+    lib = library("elementwise.cu")
+    check(lib.aie_embed_gather(_p(ids), _p(table), c_int(dtype_code(table)), _p(out), c_int(T),
+                               c_int(D), c_int(V), _p(err), _stream()), "embed_gather")
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
+                write_back: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """s = x (+ delta); out = (s / sqrt(mean(s^2) + eps)) * weight.  `x` is the
+    float32 residual stream and receives s when `write_back`; `rows` picks rows."""
+    _dev(x, delta, weight, rows)
+    if x.dtype != torch.float32:
+        raise KernelError("add_rmsnorm: the residual stream must be float32")
+    D = x.shape[-1]
+    if weight.shape != (D,):
+        raise KernelError(f"add_rmsnorm: weight shape {tuple(weight.shape)} != ({D},)")
+    if delta is not None and delta.shape != x.shape:
+        raise KernelError("add_rmsnorm: delta shape differs from x")
+    n = x.shape[0] if rows is None else rows.shape[0]
+    if out is None:
+        out = torch.empty((n, D), dtype=out_dtype, device=x.device)
+    lib = library("elementwise.cu")
+    check(lib.aie_add_rmsnorm(_p(x), _p(delta), c_int(dtype_code(delta) if delta is not None else 0),
+                              _p(weight), c_int(dtype_code(weight)), _p(out),
+                              c_int(dtype_code(out)), _p(rows), c_int(n), c_int(D), c_float(eps),
+                              c_int(1 if (write_back and rows is None) else 0), _stream()),
+          "add_rmsnorm")
+    return out
+
+
+def silu_mul(gu: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a[t, f] = silu(gu[t, f]) * gu[t, F + f]."""
+    _dev(gu)
+    T, F2 = gu.shape
+    F = F2 // 2
+    if out is None:
+        out = torch.empty((T, F), dtype=gu.dtype, device=gu.device)
+    lib = library("elementwise.cu")
+    check(lib.aie_silu_mul(_p(gu), _p(out), c_int(dtype_code(gu)), c_int(T), c_int(F), _stream()),
+          "silu_mul")
+    return out
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if x.dtype == dtype:
+        return x
+    _dev(x)
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    lib = library("elementwise.cu")
+    check(lib.aie_cast(_p(x), c_int(dtype_code(x)), _p(out), c_int(dtype_code(out)),
+                       c_longlong(x.numel()), _stream()), "cast")
+    return out
+
+
+# ---------------------------------------------------------------------------
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, rows: Optional[torch.Tensor] = None,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M, N] = a[M, K] . w[N, K]^T in true float32 (FMA on CUDA cores)."""
+    _dev(a, w, rows)
+    if a.dtype != torch.float32:
+        raise KernelError("gemm_f32: activations must be float32")
+    K = a.shape[1]
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"gemm_f32: inner sizes differ ({K} vs {w.shape[1]})")
+    M = a.shape[0] if rows is None else rows.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    lib = library("gemm_f32.cu")
+    check(lib.aie_gemm_f32(_p(a), _p(w), c_int(dtype_code(w)), _p(out), _p(rows), c_int(M), c_int(N),
+                           c_int(K), c_int(out.stride(0)), _stream()), "gemm_f32")
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x . w^T.  float32 activations (or a weight stored in 32-bit) take the true
+    float32 kernel; bfloat16 x bfloat16 takes the library matrix product, as the
+    reference's engine does for its products
+    (crates/ai-engine-candle/src/paged/transformer.rs:153-155)."""
+    out_dtype = out_dtype or x.dtype
+    if x.dtype == torch.float32 or w.dtype == torch.float32:
+        y = gemm_f32(cast(x, torch.float32), w)
+        return cast(y, out_dtype)
+    _dev(x, w)
+    if out_dtype == torch.float32:
+        return torch.mm(x, w.t(), out_dtype=torch.float32)
+    return torch.mm(x, w.t())
+
+
+# ---------------------------------------------------------------------------
+def rope_kv_write(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                  positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor,
+                  inv_freq: torch.Tensor, H: int, K: int, d: int, err: torch.Tensor,
+                  q_out: Optional[torch.Tensor] = None, write: bool = True) -> torch.Tensor:
+    """Rotate q and k by position, write k and v to their pages; returns q [T, H, d].
+    k_pages / v_pages: [num_pages, K, page, d] of one layer."""
+    _dev(qkv, k_pages, v_pages, positions, token_req, block_table, inv_freq, err)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (H + 2 * K) * d:
+        raise KernelError("rope_kv_write: qkv width differs from (H + 2K) * d")
+    num_pages, Kp, P, dp = k_pages.shape
+    if (Kp, dp) != (K, d) or v_pages.shape != k_pages.shape:
+        raise KernelError("rope_kv_write: page shape does not fit (K, d)")
+    if k_pages.dtype != qkv.dtype:
+        raise KernelError("rope_kv_write: cache dtype differs from the activations'")
+    rot = inv_freq.shape[0] * 2
+    if q_out is None:
+        q_out = torch.empty((T, H, d), dtype=qkv.dtype, device=qkv.device)
+    lib = library("rope_kv.cu")
+    check(lib.aie_rope_kv_write(_p(qkv), _p(q_out), _p(k_pages), _p(v_pages), c_int(dtype_code(qkv)),
+                                _p(positions), _p(token_req), _p(block_table),
+                                c_int(block_table.shape[1]), c_int(num_pages), c_int(P), c_int(T),
+                                c_int(H), c_int(K), c_int(d), c_int(rot), _p(inv_freq),
+                                c_int(1 if write else 0), _p(err), _stream()), "rope_kv_write")
+    return q_out
+
+
+def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                          positions: torch.Tensor, token_req: torch.Tensor,
+                          block_table: torch.Tensor, scale: float, window: int, err: torch.Tensor,
+                          out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """softmax(q.k * scale over keys j <= pos (and j > pos - window)) . v per query
+    token and head, keys read through the block table.  q, out: [T, H, d]."""
+    _dev(q, k_pages, v_pages, positions, token_req, block_table, err)
+    T, H, d = q.shape
+    num_pages, K, P, dp = k_pages.shape
+    if dp != d or H % K:
+        raise KernelError("paged_attention: head sizes do not fit")
+    if d > 256:
+        raise KernelError(f"paged_attention: head_dim {d} > 256 is not supported")
+    if out is None:
+        out = torch.empty_like(q)
+    lib = library("attention_plain.cu")
+    check(lib.aie_paged_attention_plain(_p(q), _p(k_pages), _p(v_pages), _p(out),
+                                        c_int(dtype_code(q)), _p(positions), _p(token_req),
+                                        _p(block_table), c_int(block_table.shape[1]),
+                                        c_int(num_pages), c_int(P), c_int(T), c_int(H), c_int(K),
+                                        c_int(d), c_int(window), c_float(scale), _p(err), _stream()),
+          "paged_attention_plain")
+    return out
+
+
+def paged_attention(q, k_pages, v_pages, ctx, block_table, scale: float, window: int):
+    """Attention of a step's query tokens over the cache.  float32 takes the plain
+    kernel; bfloat16 takes the fast kernels where they accept the sizes."""
+    return paged_attention_plain(q, k_pages, v_pages, ctx.positions, ctx.token_req, block_table,
+                                 scale, window, ctx.err)

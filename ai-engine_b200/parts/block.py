@@ -1,0 +1,25 @@
+"""The pre-norm residual block (crates/ai-engine-runtime/src/arch/block.rs:13-27):
+x = x + mixer(norm(x)); x = x + ffn(norm(x)).
+
+The residual stream stays float32.  A branch's output is not added by a kernel
+of its own: it travels as `pending` into the next norm, which adds it in
+float32, stores the sum and normalises it in one pass over the row.
+"""
+from __future__ import annotations
+
+from .base import Block
+
+
+class PreNormBlock(Block):
+    roles = ("mixer_norm", "mixer", "ffn_norm", "ffn")
+
+    def __init__(self, spec, env, parts):
+        super().__init__(spec, env)
+        self.mixer_norm, self.mixer = parts["mixer_norm"], parts["mixer"]
+        self.ffn_norm, self.ffn = parts["ffn_norm"], parts["ffn"]
+
+    def forward(self, x, pending, ctx, cache):
+        h = self.mixer_norm.forward(x, pending)
+        a = self.mixer.forward(h, ctx, cache)
+        h = self.ffn_norm.forward(x, a)
+        return x, self.ffn.forward(h, ctx)

@@ -15,7 +15,10 @@ TINY_A = dict(
     num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
     vocab_size=256, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
     max_position_embeddings=128)
-TINY_A_OPTS = dict(seed=0, norm_std=0.0, block_size=16)
+# qk_gain scales the q and k projections so that attention scores have a standard
+# deviation near 1.6 (0.0256 g^2 for A, 0.064 g^2 for B, 0.038 g^2 for C): single keys
+# stand out, and bfloat16 rounding of the scores stays within the bf16 tolerance.
+TINY_A_OPTS = dict(seed=0, norm_std=0.0, block_size=16, qk_gain=8.0)
 
 TINY_B = dict(
     architectures=["LlamaForCausalLM"], hidden_size=160, intermediate_size=416,
@@ -24,7 +27,7 @@ TINY_B = dict(
     max_position_embeddings=256,
     rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
                       original_max_position_embeddings=64))
-TINY_B_OPTS = dict(seed=1, norm_std=0.1, block_size=8)
+TINY_B_OPTS = dict(seed=1, norm_std=0.1, block_size=8, qk_gain=5.0)
 
 # a third shape for long sequences: hundreds of keys, a head size of 48, 6 heads in 3 groups
 TINY_C = dict(
@@ -32,7 +35,7 @@ TINY_C = dict(
     num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=3, head_dim=48,
     vocab_size=200, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
     max_position_embeddings=1024)
-TINY_C_OPTS = dict(seed=2, norm_std=0.05, block_size=16)
+TINY_C_OPTS = dict(seed=2, norm_std=0.05, block_size=16, qk_gain=6.0)
 
 TINY = {"A": (TINY_A, TINY_A_OPTS), "B": (TINY_B, TINY_B_OPTS), "C": (TINY_C, TINY_C_OPTS)}
 
@@ -49,7 +52,7 @@ TOL_F32_SCHEDULES = 2e-5
 TOL_BF16 = 3e-2
 
 
-def make_model_dir(tmp_path, name: str, dtype: str = "bfloat16", qk_gain: float = 1.0) -> str:
+def make_model_dir(tmp_path, name: str, dtype: str = "bfloat16", qk_gain=None) -> str:
     """A model folder for tiny configuration `name`, written by the engine's
     random-weights mode.  qk_gain scales the q and k projections so that scores
     spread and single keys stand out (a wrong key or page then changes logits
@@ -57,6 +60,7 @@ def make_model_dir(tmp_path, name: str, dtype: str = "bfloat16", qk_gain: float 
     import ai_engine_b200 as aie
 
     raw, opts = TINY[name]
+    qk_gain = opts["qk_gain"] if qk_gain is None else qk_gain
     cfg = aie.LlamaConfig.from_dict(raw)
     d = os.path.join(str(tmp_path), f"tiny{name}_{dtype}_{qk_gain}")
     aie.write_random_model(cfg, d, seed=opts["seed"], dtype=dtype, norm_std=opts["norm_std"])

@@ -44,7 +44,7 @@ CASES = [("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16"
 
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_whole_prompts(tmp_path, name, dtype):
-    d = make_model_dir(tmp_path, name, qk_gain=8.0)
+    d = make_model_dir(tmp_path, name)
     vocab = TINY[name][0]["vocab_size"]
     rep = replayer(d, dtype, name, max_tokens=128)
     for n, seed in ((1, 3), (5, 4), (17, 5), (33, 6), (120, 7)):
@@ -59,7 +59,7 @@ def test_whole_prompts(tmp_path, name, dtype):
 
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_last_32_one_by_one(tmp_path, name, dtype):
-    d = make_model_dir(tmp_path, name, qk_gain=8.0)
+    d = make_model_dir(tmp_path, name)
     vocab = TINY[name][0]["vocab_size"]
     ids = random_ids(100, vocab, 11)
     ref = plain_logits(d, ids, oracle_dtype(dtype))
@@ -81,7 +81,7 @@ PORTIONS = [2, 3, 7, 16, 5, 2, 13, 2, 31, 9, 2, 8]   # sums to 100
 
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_portions_of_changing_size(tmp_path, name, dtype):
-    d = make_model_dir(tmp_path, name, qk_gain=8.0)
+    d = make_model_dir(tmp_path, name)
     vocab = TINY[name][0]["vocab_size"]
     ids = random_ids(sum(PORTIONS), vocab, 12)
     ref = plain_logits(d, ids, oracle_dtype(dtype))
@@ -142,7 +142,7 @@ def pool_tokens_for(steps, seqs):
 
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_mixed_requests_with_pages_used_again(tmp_path, name, dtype):
-    d = make_model_dir(tmp_path, name, qk_gain=8.0)
+    d = make_model_dir(tmp_path, name)
     vocab = TINY[name][0]["vocab_size"]
     lengths = [40, 9, 120, 1, 77, 33, 64, 18, 100]
     steps, seqs = mixed_trace(lengths, vocab, 21)
@@ -168,7 +168,7 @@ def test_mixed_requests_with_pages_used_again(tmp_path, name, dtype):
 
 def test_trace_run_program(tmp_path):
     """bin/trace_run as a user starts it: JSON lines in, <step>.f32 out, `done <step>`."""
-    d = make_model_dir(tmp_path, "A", qk_gain=8.0)
+    d = make_model_dir(tmp_path, "A")
     ids = random_ids(40, 256, 5)
     out_dir = os.path.join(str(tmp_path), "out")
     lines = [dict(step=0, entries=[dict(id="a", tokens=ids[:30], want=[0, 29])], end=[]),

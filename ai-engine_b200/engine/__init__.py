@@ -1,0 +1,3 @@
+from .step import StepEntry, StepError, StepRunner
+
+__all__ = ["StepEntry", "StepError", "StepRunner"]

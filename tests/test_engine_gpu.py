@@ -1,0 +1,192 @@
+"""The engine through its Python entry point: greedy generation against the plain
+implementation, batched == solo (the reference's batched_matches_solo,
+crates/ai-engine-candle/tests/paged_batching.rs:41-51), preemption that reproduces the
+same tokens, seeded temperature sampling, long decoding, and the command line."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+from helpers import TINY, TOL_BF16, TOL_F32, make_model_dir, plain_logits, random_ids
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def engine(d, name, dtype="fp32", **kw):
+    import ai_engine_b200 as aie
+
+    opts = dict(dtype=dtype, block_size=TINY[name][1]["block_size"], kv_cache_blocks=64,
+                max_num_seqs=4, max_num_batched_tokens=64)
+    opts.update(kw)
+    return aie.Engine(d, **opts)
+
+
+def greedy_with_margin(d, prompt, n, dtype, tol):
+    """Greedy tokens from the plain implementation, and for each the gap between the
+    best and second-best logit: a token is only compared where the gap exceeds what
+    rounding could flip."""
+    w, cfg = pl.read_weights(d, dtype), pl.read_config(d)
+    ids, out, margins = list(prompt), [], []
+    for _ in range(n):
+        logits = pl.forward(w, cfg, ids)[-1]
+        top = torch.topk(logits, 2).values
+        t = int(torch.argmax(logits))
+        out.append(t)
+        margins.append(float(top[0] - top[1]))
+        ids.append(t)
+    return out, margins
+
+
+def assert_same_until_a_close_call(got, want, margins, tol):
+    for i, (g, w) in enumerate(zip(got, want)):
+        if g != w:
+            assert margins[i] <= 2 * tol, f"token {i}: got {g}, plain {w}, margin {margins[i]}"
+            return                      # after a legitimate flip the sequences part ways
+    assert len(got) == len(want)
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "fp32"), ("A", "bf16"), ("B", "fp32"), ("B", "bf16")])
+def test_greedy_generation_matches_the_plain_implementation(tmp_path, name, dtype):
+    import ai_engine_b200 as aie
+
+    d = make_model_dir(tmp_path, name)
+    vocab = TINY[name][0]["vocab_size"]
+    lens = (5, 17, 33) if name == "A" else (1, 9, 40, 120)
+    prompts = [random_ids(n, vocab, 30 + n) for n in lens]
+    eng = engine(d, name, dtype, max_num_batched_tokens=16 if name == "B" else 64)
+    outs = eng.generate(prompts, aie.SamplingParams(max_tokens=8, ignore_eos=True))
+    tol = TOL_F32 if dtype == "fp32" else TOL_BF16
+    for p, o in zip(prompts, outs):
+        want, margins = greedy_with_margin(d, p, 8, torch.float64 if dtype == "fp32" else torch.float32, tol)
+        assert_same_until_a_close_call(o, want, margins, tol)
+    st = eng.stats()
+    assert st["finished"] == len(prompts) and st["cache"]["group0"]["in_use"] == 0
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_batched_matches_solo(tmp_path, dtype):
+    import ai_engine_b200 as aie
+
+    d = make_model_dir(tmp_path, "B")
+    prompts = [random_ids(n, 384, 50 + n) for n in (3, 21, 8, 64)]
+    sp = aie.SamplingParams(max_tokens=24, ignore_eos=True)
+    solo = [engine(d, "B", dtype, max_num_seqs=1).generate([p], sp)[0] for p in prompts]
+    together = engine(d, "B", dtype, max_num_seqs=4, max_num_batched_tokens=16).generate(prompts, sp)
+    if dtype == "fp32":
+        assert together == solo            # float32: the same bits whatever the batch
+    else:
+        agree = sum(a == b for a, b in zip(together, solo))
+        assert agree >= 3                  # bfloat16: a library product may round differently per batch size
+
+
+def test_preemption_reproduces_the_same_tokens(tmp_path):
+    import ai_engine_b200 as aie
+
+    d = make_model_dir(tmp_path, "A")
+    prompts = [random_ids(n, 256, 70 + n) for n in (20, 25, 30)]
+    params = [aie.SamplingParams(max_tokens=30, ignore_eos=True),
+              aie.SamplingParams(max_tokens=30, ignore_eos=True, temperature=0.8, seed=7),
+              aie.SamplingParams(max_tokens=30, ignore_eos=True, temperature=1.1, seed=8, top_k=40)]
+    roomy = engine(d, "A", "fp32", kv_cache_blocks=64).generate(prompts, params)
+    tight_engine = engine(d, "A", "fp32", kv_cache_blocks=9)       # 144 tokens for 3 x 50..60
+    tight = tight_engine.generate(prompts, params)
+    assert tight_engine.stats()["preemptions"] >= 1
+    assert tight == roomy
+
+
+def test_seeded_sampling_is_reproducible_and_seed_matters(tmp_path):
+    import ai_engine_b200 as aie
+
+    d = make_model_dir(tmp_path, "B")
+    prompts = [random_ids(n, 384, 90 + n) for n in (1, 9, 40, 120)]
+    sp = lambda s: aie.SamplingParams(max_tokens=12, temperature=0.8, seed=s, ignore_eos=True)
+    a = engine(d, "B", "fp32", max_num_batched_tokens=16).generate(prompts, sp(3))
+    b = engine(d, "B", "fp32", max_num_batched_tokens=16).generate(prompts, sp(3))
+    c = engine(d, "B", "fp32", max_num_batched_tokens=16).generate(prompts, sp(4))
+    assert a == b and a != c
+    # the first sampled token of each request against the plain sampler on plain logits
+    from ai_engine_b200.sampling.rng import uniform
+    for p, o in zip(prompts, a):
+        logits = plain_logits(d, p)[-1]
+        want = pl.sample(logits.tolist(), 0.8, r=uniform(3, 0))
+        near = {pl.sample(logits.tolist(), 0.8, r=min(max(uniform(3, 0) + dr, 0.0), 1.0)) for dr in (-1e-4, 1e-4)}
+        assert o[0] == want or o[0] in near
+
+
+def test_eos_ends_a_request_and_is_not_returned(tmp_path):
+    import ai_engine_b200 as aie
+
+    d = make_model_dir(tmp_path, "A")
+    p = random_ids(12, 256, 5)
+    free = engine(d, "A", "fp32").generate([p], aie.SamplingParams(max_tokens=10, ignore_eos=True))[0]
+    cfgp = os.path.join(d, "config.json")
+    raw = json.load(open(cfgp))
+    raw["eos_token_id"] = [free[4], 99999]
+    json.dump(raw, open(cfgp, "w"))
+    stopped = engine(d, "A", "fp32").generate([p], aie.SamplingParams(max_tokens=10))[0]
+    assert stopped == free[:free.index(free[4])]
+
+
+def test_long_decoding_and_first_tokens(tmp_path):
+    """300 tokens decoded one by one after a 3-token prompt: logits of the first tokens and
+    of every decoded position against the plain implementation run on the final sequence."""
+    from ai_engine_b200.engine.replay import Replayer
+
+    d = make_model_dir(tmp_path, "C")
+    ids = random_ids(303, 200, 17)
+    ref = plain_logits(d, ids, torch.float64)
+    rep = Replayer(d, "float32", max_tokens=320, block_size=16)
+    got = [rep.run_step([dict(id="x", tokens=ids[:3], want=[0, 1, 2])]).numpy()]
+    for t in ids[3:]:
+        got.append(rep.run_step([dict(id="x", tokens=[t], want=[0])]).numpy())
+    got = np.concatenate(got).astype(np.float64)
+    err = np.abs(got - ref).max(axis=1)
+    assert err.max() <= TOL_F32, f"first wrong token {int(np.argmax(err > TOL_F32))}"
+    rep16 = Replayer(d, "bfloat16", max_tokens=320, block_size=16)
+    ref32 = plain_logits(d, ids, torch.float32)
+    g = [rep16.run_step([dict(id="x", tokens=ids[:3], want=[0, 1, 2])]).numpy()]
+    for t in ids[3:]:
+        g.append(rep16.run_step([dict(id="x", tokens=[t], want=[0])]).numpy())
+    err = np.abs(np.concatenate(g) - ref32).max(axis=1)
+    assert err.max() <= TOL_BF16, f"first wrong token {int(np.argmax(err > TOL_BF16))}"
+
+
+def test_rejections_and_bad_options(tmp_path):
+    import ai_engine_b200 as aie
+
+    d = make_model_dir(tmp_path, "A")
+    eng = engine(d, "A", "fp32", kv_cache_blocks=4, max_seq_len=128)
+    with pytest.raises(ValueError, match="never fit"):
+        eng.add_request(list(range(100)), aie.SamplingParams(max_tokens=5))
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        eng.add_request([1, 2, 999])
+    with pytest.raises(ValueError, match="max context"):
+        eng.add_request([1] * 200)
+    with pytest.raises(ValueError, match="cuda:0 only"):
+        aie.Engine(d, device="cpu")
+    with pytest.raises(ValueError, match="unknown engine option"):
+        aie.Engine(d, pool_sizes=3)
+
+
+def test_command_line(tmp_path):
+    d = make_model_dir(tmp_path, "A")
+    cfg = tmp_path / "provider.toml"
+    cfg.write_text(f'[[provider]]\nid = "local"\nkind = "b200"\nweights_path = "{d}"\n'
+                   'device = "cuda:0"\ndtype = "fp32"\nmax_num_seqs = 2\nblock_size = 16\nkv_cache_blocks = 32\n')
+    exe = [sys.executable, os.path.join(ROOT, "bin", "ai-engine")]
+    assert subprocess.run(exe + ["-c", str(cfg), "--check"], capture_output=True, text=True).stdout.strip() == "ok"
+    p = subprocess.run(exe + ["-c", str(cfg), "--prompt-ids", "5,17,3", "--prompt-ids", "9,9", "--max-tokens", "6",
+                              "--ignore-eos", "--stats"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-1500:]
+    lines = [[int(t) for t in l.split(",")] for l in p.stdout.strip().splitlines()]
+    assert len(lines) == 2 and all(len(l) == 6 for l in lines)
+    want, margins = greedy_with_margin(d, [5, 17, 3], 6, torch.float64, TOL_F32)
+    assert_same_until_a_close_call(lines[0], want, margins, TOL_F32)
+    bad = subprocess.run(exe + ["--model", str(tmp_path / "none"), "--prompt-ids", "1"], capture_output=True, text=True)
+    assert bad.returncode == 1 and "error" in bad.stderr

@@ -1,0 +1,303 @@
+"""Each kernel alone against a plain PyTorch float32/float64 restatement of the same
+op, at sizes other than the engine's tiny configurations."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def ops():
+    from ai_engine_b200.kernels import ops as o
+    return o
+
+
+def err_word():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("V,D", [(77, 24), (1000, 4096), (130, 200)])
+def test_embed_gather(dtype, V, D):
+    torch.manual_seed(0)
+    table = torch.randn(V, D, device=DEV).to(dtype)
+    ids = torch.randint(0, V, (19,), device=DEV, dtype=torch.int32)
+    e = err_word()
+    x = ops().embed_gather(ids, table, e)
+    assert x.dtype == torch.float32 and torch.equal(x, table[ids.long()].float())
+    assert int(e.item()) == 0
+    bad = ids.clone()
+    bad[3] = V
+    x = ops().embed_gather(bad, table, e)
+    assert int(e.item()) & 1 and torch.all(x[3] == 0)       # flagged, not trapped
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("D,eps", [(48, 1e-5), (4096, 1e-6), (1000, 1e-3), (8200, 1e-5)])
+def test_add_rmsnorm(dtype, D, eps):
+    torch.manual_seed(1)
+    n = 13
+    x = torch.randn(n, D, device=DEV) * 3
+    delta = torch.randn(n, D, device=DEV).to(dtype)
+    w = (1 + 0.1 * torch.randn(D, device=DEV)).to(dtype)
+    s = x.double() + delta.double()
+    want = pl.rms_norm(s, w.double(), eps)
+    x_in = x.clone()
+    out = ops().add_rmsnorm(x_in, delta, w, eps, dtype)
+    assert torch.allclose(x_in.double(), s, atol=1e-6)      # the sum was stored back in float32
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert (out.double() - want).abs().max() <= tol * max(1.0, float(want.abs().max()))
+    # without a pending branch, at chosen rows, not stored back
+    rows = torch.tensor([5, 0, 12], device=DEV, dtype=torch.int32)
+    x2 = x.clone()
+    out2 = ops().add_rmsnorm(x2, None, w, eps, dtype, rows=rows, write_back=False)
+    want2 = pl.rms_norm(x.double()[rows.long()], w.double(), eps)
+    assert torch.equal(x2, x) and (out2.double() - want2).abs().max() <= tol * max(1.0, float(want2.abs().max()))
+    # a 32-bit weight under bfloat16 activations stays 32-bit
+    out3 = ops().add_rmsnorm(x.clone(), delta, w.float(), eps, dtype)
+    assert (out3.double() - want).abs().max() <= tol * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,F", [(1, 24), (7, 1000), (33, 14336)])
+def test_silu_mul(dtype, T, F):
+    torch.manual_seed(2)
+    gu = (torch.randn(T, 2 * F, device=DEV) * 2).to(dtype)
+    g, u = gu[:, :F].double(), gu[:, F:].double()
+    want = g * torch.sigmoid(g) * u
+    out = ops().silu_mul(gu)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert (out.double() - want).abs().max() <= tol * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (5, 70, 33), (64, 64, 16), (130, 257, 1000), (3, 128256, 64)])
+@pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
+def test_gemm_f32_is_true_float32(M, N, K, wdtype):
+    torch.manual_seed(3)
+    a = torch.randn(M, K, device=DEV)
+    w = torch.randn(N, K, device=DEV).to(wdtype)
+    want = a.double() @ w.double().T
+    out = ops().gemm_f32(a, w)
+    assert (out.double() - want).abs().max() <= 2e-6 * K ** 0.5 * max(1.0, float(want.abs().max()))
+    # a row's result does not depend on the other rows of the batch
+    one = ops().gemm_f32(a[M // 2: M // 2 + 1].contiguous(), w)
+    assert torch.equal(one[0], out[M // 2])
+    # chosen rows
+    rows = torch.tensor([M - 1, 0], device=DEV, dtype=torch.int32)
+    sel = ops().gemm_f32(a, w, rows=rows)
+    assert torch.equal(sel, out[rows.long()])
+
+
+def paged_setup(dtype, H, K, d, P, lens, q_lens, seed, num_pages=None, shuffle=True):
+    """Random q/k/v for requests with `lens` tokens in total, of which the last
+    q_lens are this step's queries; pages scattered through the pool."""
+    rng = np.random.RandomState(seed)
+    torch.manual_seed(seed)
+    R = len(lens)
+    pages_per = [(n + P - 1) // P for n in lens]
+    num_pages = num_pages or sum(pages_per) + 3
+    perm = rng.permutation(num_pages) if shuffle else np.arange(num_pages)
+    W = max(pages_per)
+    bt = -np.ones((R, W), dtype=np.int32)
+    at = 0
+    for r, n in enumerate(pages_per):
+        bt[r, :n] = perm[at:at + n]
+        at += n
+    k_pages = torch.full((num_pages, K, P, d), float("nan"), device=DEV, dtype=dtype)
+    v_pages = torch.full((num_pages, K, P, d), float("nan"), device=DEV, dtype=dtype)
+    ks = [(torch.randn(n, K, d, device=DEV) * 1.5).to(dtype) for n in lens]
+    vs = [torch.randn(n, K, d, device=DEV).to(dtype) for n in lens]
+    for r, n in enumerate(lens):
+        for pos in range(n):
+            pg, sl = bt[r, pos // P], pos % P
+            k_pages[pg, :, sl] = ks[r][pos]
+            v_pages[pg, :, sl] = vs[r][pos]
+    T = sum(q_lens)
+    q = torch.randn(T, H, d, device=DEV).to(dtype)
+    positions, token_req = [], []
+    for r, (n, ql) in enumerate(zip(lens, q_lens)):
+        positions += list(range(n - ql, n))
+        token_req += [r] * ql
+    return dict(q=q, k_pages=k_pages, v_pages=v_pages, ks=ks, vs=vs,
+                positions=torch.tensor(positions, device=DEV, dtype=torch.int32),
+                token_req=torch.tensor(token_req, device=DEV, dtype=torch.int32),
+                bt=torch.tensor(bt, device=DEV), lens=lens, q_lens=q_lens)
+
+
+def attention_reference(s, H, K, d, scale, window):
+    """[T, H, d] in float64 from the unpaged keys and values."""
+    out = []
+    t = 0
+    for r, (n, ql) in enumerate(zip(s["lens"], s["q_lens"])):
+        k = s["ks"][r].double().repeat_interleave(H // K, dim=1)       # [n, H, d]
+        v = s["vs"][r].double().repeat_interleave(H // K, dim=1)
+        for i in range(ql):
+            pos = n - ql + i
+            q = s["q"][t].double()                                      # [H, d]
+            sc = torch.einsum("hd,nhd->hn", q, k) * scale
+            j = torch.arange(n, device=DEV)
+            ok = j <= pos
+            if window:
+                ok &= j > pos - window
+            sc = sc.masked_fill(~ok[None], float("-inf"))
+            out.append(torch.einsum("hn,nhd->hd", torch.softmax(sc, -1), v))
+            t += 1
+    return torch.stack(out)
+
+
+ATTN_SHAPES = [  # H, K, d, P, lens, q_lens, window
+    (4, 2, 16, 16, [5, 40], [5, 1], 0),
+    (5, 1, 32, 8, [1, 9, 120], [1, 2, 120], 0),
+    (6, 3, 48, 16, [300, 17], [1, 17], 0),
+    (8, 8, 64, 4, [33, 64, 2], [3, 64, 1], 0),
+    (32, 8, 128, 16, [700, 130], [1, 2], 0),
+    (2, 1, 256, 32, [45], [45], 0),
+    (4, 2, 80, 16, [150, 60], [150, 1], 37),
+    (3, 1, 16, 8, [260], [1], 100),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", ATTN_SHAPES)
+def test_paged_attention_plain(dtype, shape):
+    H, K, d, P, lens, q_lens, window = shape
+    s = paged_setup(dtype, H, K, d, P, lens, q_lens, seed=H * 100 + d)
+    scale = 1.0 / math.sqrt(d)
+    e = err_word()
+    out = ops().paged_attention_plain(s["q"], s["k_pages"], s["v_pages"], s["positions"], s["token_req"],
+                                      s["bt"], scale, window, e)
+    want = attention_reference(s, H, K, d, scale, window)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    assert int(e.item()) == 0
+    assert not torch.isnan(out).any()
+    assert (out.double() - want).abs().max() <= tol
+
+
+def test_far_key_among_hundreds_is_found():
+    """One key far back is made to match the query; the output must be its value."""
+    H, K, d, P = 4, 2, 32, 16
+    s = paged_setup(torch.float32, H, K, d, P, [600], [1], seed=9)
+    far = 37
+    pg, sl = int(s["bt"][0, far // P]), far % P
+    s["k_pages"][pg, :, sl] = 0
+    for h in range(H):
+        s["k_pages"][pg, h // (H // K), sl] += s["q"][0, h] * 10 / (H // K)
+    out = ops().paged_attention_plain(s["q"], s["k_pages"], s["v_pages"], s["positions"], s["token_req"],
+                                      s["bt"], 1.0, 0, err_word())
+    s["ks"][0][far] = s["k_pages"][pg, :, sl]
+    want = attention_reference(s, H, K, d, 1.0, 0)
+    assert (out.double() - want).abs().max() <= 2e-5
+    assert (out[0, 0] - s["v_pages"][pg, 0, sl]).abs().max() < 0.2     # dominated by the far key's value
+
+
+def test_bad_page_is_flagged_not_followed():
+    s = paged_setup(torch.float32, 2, 1, 16, 8, [20], [1], seed=4)
+    s["bt"][0, 1] = 10_000
+    e = err_word()
+    out = ops().paged_attention_plain(s["q"], s["k_pages"], s["v_pages"], s["positions"], s["token_req"],
+                                      s["bt"], 1.0, 0, e)
+    torch.cuda.synchronize()
+    assert int(e.item()) & 2 and not torch.isnan(out).any()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,K,d,P,rot", [(4, 2, 16, 16, 16), (5, 1, 32, 8, 32), (6, 3, 48, 4, 32),
+                                         (32, 8, 128, 16, 128), (2, 2, 64, 16, 0)])
+def test_rope_kv_write(dtype, H, K, d, P, rot):
+    torch.manual_seed(5)
+    lens, q_lens = [9, 41, 3], [9, 2, 1]
+    s = paged_setup(dtype, H, K, d, P, lens, q_lens, seed=6)
+    T = sum(q_lens)
+    qkv = torch.randn(T, (H + 2 * K) * d, device=DEV).to(dtype)
+    inv_freq = torch.from_numpy(pl.inv_freq_default(rot, 500000.0)).to(DEV) if rot else torch.zeros(0, device=DEV)
+    before_k = s["k_pages"].clone()
+    e = err_word()
+    q = ops().rope_kv_write(qkv, s["k_pages"], s["v_pages"], s["positions"], s["token_req"], s["bt"],
+                            inv_freq, H, K, d, e)
+    assert int(e.item()) == 0
+    x = qkv.double().view(T, H + 2 * K, d)
+    pos = s["positions"].cpu()
+
+    def rot_ref(t):     # [T, heads, d]
+        if not rot:
+            return t
+        r = pl.rope(t[..., :rot].transpose(0, 1), pos, pl.inv_freq_default(rot, 500000.0)).transpose(0, 1)
+        return torch.cat([r, t[..., rot:]], dim=-1)
+
+    xq, xk, xv = x[:, :H].cpu(), x[:, H:H + K].cpu(), x[:, H + K:].cpu()
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    assert (q.double().cpu() - rot_ref(xq)).abs().max() <= tol * 4
+    kr = rot_ref(xk)
+    touched = torch.zeros_like(before_k, dtype=torch.bool)
+    for t in range(T):
+        r, p = int(s["token_req"][t]), int(pos[t])
+        pg, sl = int(s["bt"][r, p // P]), p % P
+        assert (s["k_pages"][pg, :, sl].double().cpu() - kr[t]).abs().max() <= tol * 4
+        assert (s["v_pages"][pg, :, sl].double().cpu() - xv[t]).abs().max() <= tol
+        touched[pg, :, sl] = True
+    same = (s["k_pages"] == before_k) | (torch.isnan(s["k_pages"]) & torch.isnan(before_k))
+    assert bool(same[~touched].all())           # nothing else in the pool was written
+    # write=False leaves the pool alone and still rotates q
+    k2 = s["k_pages"].clone()
+    q2 = ops().rope_kv_write(qkv, s["k_pages"], s["v_pages"], s["positions"], s["token_req"], s["bt"],
+                             inv_freq, H, K, d, e, write=False)
+    assert torch.equal(q2, q) and bool(((s["k_pages"] == k2) | torch.isnan(k2)).all())
+
+
+def test_sampling_kernel_against_the_plain_sampler():
+    from ai_engine_b200.sampling.sampler import sample_rows
+
+    rng = np.random.RandomState(0)
+    V = 1000
+    cases = []
+    for i in range(120):
+        T = [0.0, 0.8, 1.0, 2.5][i % 4]
+        k = [0, 0, 5, 50][(i // 4) % 4]
+        p = [1.0, 0.9, 0.3, 1.0][(i // 16) % 4]
+        cases.append((T, k, p, float(np.float32(rng.rand()))))
+    logits = torch.randn(len(cases), V) * 2
+    logits[7, 100] = logits[7].max() + 1            # ties for the maximum: the first wins
+    logits[7, 10] = logits[7, 100]
+    logits[8] = torch.round(logits[8] * 2) / 2      # many ties under temperature
+    logits[9] = torch.round(logits[9])
+    dev = lambda a, dt: torch.tensor(a, dtype=dt, device=DEV)
+    out = sample_rows(logits.to(DEV), dev([c[0] for c in cases], torch.float32),
+                      dev([c[1] for c in cases], torch.int32), dev([c[2] for c in cases], torch.float32),
+                      dev([c[3] for c in cases], torch.float32)).cpu().tolist()
+    wrong = []
+    for i, (T, k, p, r) in enumerate(cases):
+        want = pl.sample(logits[i].tolist(), T, top_k=k or None, top_p=p if p < 1 else None, r=r)
+        if out[i] != want:
+            # a draw that falls within float rounding of a boundary of the cumulative sum may
+            # land on either neighbour; anything else is a fault
+            near = {pl.sample(logits[i].tolist(), T, top_k=k or None, top_p=p if p < 1 else None, r=r2)
+                    for r2 in (max(r - 2e-6, 0.0), min(r + 2e-6, 1.0))}
+            if out[i] not in near:
+                wrong.append((i, T, k, p, r, out[i], want))
+    assert not wrong, wrong[:5]
+    assert out[7] == 10 or cases[7][0] != 0.0
+
+
+def test_sampling_distribution_and_large_vocab():
+    from ai_engine_b200.sampling.sampler import sample_rows
+
+    V, N = 128256, 64
+    torch.manual_seed(1)
+    base = torch.randn(V) * 3
+    logits = base[None].repeat(N, 1).to(DEV)
+    greedy = sample_rows(logits, torch.zeros(N, device=DEV), torch.zeros(N, dtype=torch.int32, device=DEV),
+                         torch.ones(N, device=DEV), torch.zeros(N, device=DEV))
+    assert greedy.tolist() == [int(base.argmax())] * N
+    r = torch.linspace(0, 0.999, N, device=DEV)
+    out = sample_rows(logits, torch.ones(N, device=DEV), torch.full((N,), 20, dtype=torch.int32, device=DEV),
+                      torch.ones(N, device=DEV), r).cpu().tolist()
+    top20 = set(torch.topk(base, 20).indices.tolist())
+    assert set(out) <= top20
+    # the walk is monotone: a larger draw never lands on a more likely token
+    vals = [float(base[t]) for t in out]
+    assert all(vals[i] >= vals[i + 1] - 1e-6 for i in range(N - 1))

@@ -1,0 +1,256 @@
+"""Each part alone against the plain implementation's function of the same name, and
+parts that are not Llama's, defined here, registered, built and stepped without a
+change to the package: a mixer with state of its own, a layer named twice in the run
+order, a layer that reads another's cache, windowed attention in a group of its own."""
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+from helpers import random_ids
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def env(dtype, hidden):
+    from ai_engine_b200.parts import BuildEnv
+    return BuildEnv(hidden, dtype, torch.device(DEV))
+
+
+def source(tensors, specs, dtype):
+    from ai_engine_b200.weights import from_tensors
+    return from_tensors(tensors, specs, dtype, DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part(dtype):
+    from ai_engine_b200.parts import PartSpec, RMSNorm
+
+    D = 200
+    p = RMSNorm(PartSpec("rmsnorm", dict(size=D, eps=1e-3), dict(weight="w")), env(dtype, D))
+    w = (1 + 0.2 * torch.randn(D)).to(dtype)
+    p.load(source({"w": w}, p.tensor_specs(), dtype))
+    x = torch.randn(9, D, device=DEV)
+    out = p.forward(x.clone())
+    want = pl.rms_norm(x.double().cpu(), w.double(), 1e-3)
+    assert out.dtype == dtype
+    assert (out.double().cpu() - want).abs().max() <= (1e-5 if dtype == torch.float32 else 3e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_part(dtype):
+    from ai_engine_b200.parts import PartSpec, SwiGLU
+
+    D, F = 72, 200
+    p = SwiGLU(PartSpec("swiglu", dict(hidden_size=D, intermediate_size=F), dict(gate="g", up="u", down="d")),
+               env(dtype, D))
+    ts = {"g": (torch.randn(F, D) * 0.2).to(dtype), "u": (torch.randn(F, D) * 0.2).to(dtype),
+          "d": (torch.randn(D, F) * 0.2).to(dtype)}
+    p.load(source(ts, p.tensor_specs(), dtype))
+    h = torch.randn(11, D).to(dtype)
+    out = p.forward(h.to(DEV), None)
+    want = pl.swiglu(h.double(), ts["g"].double(), ts["u"].double(), ts["d"].double())
+    tol = 1e-5 if dtype == torch.float32 else 5e-2
+    assert (out.double().cpu() - want).abs().max() <= tol * max(1.0, float(want.abs().max()))
+
+
+def test_rotary_part_frequencies():
+    from ai_engine_b200.parts import PartSpec, RotaryEncoding
+
+    sc = dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+              original_max_position_embeddings=8192)
+    for d, theta, scaling in ((16, 10000.0, None), (128, 500000.0, sc), (64, 500000.0, sc)):
+        p = RotaryEncoding(PartSpec("rotary", dict(rot_dim=d, theta=theta, scaling=scaling)), env(torch.float32, 8))
+        p.load(None)
+        want = pl.inv_freq_for(dict(head_dim=d, theta=theta, scaling=scaling))
+        assert np.array_equal(p.inv_freq.cpu().numpy(), want)
+
+
+def tiny_toy_spec(order, layers_kinds, hidden=32, vocab=50, window=0):
+    """A model spec from toy and built-in parts (no architecture of anyone's)."""
+    from ai_engine_b200.parts import LayerSpec, ModelSpec, PartSpec, RunStep
+
+    layers = []
+    for i, kind in enumerate(layers_kinds):
+        if kind == "ema":
+            mixer = PartSpec("toy_ema", dict(hidden_size=hidden, decay=0.5 + 0.1 * i), dict(w=f"l{i}.mix.w"))
+        else:
+            mixer = PartSpec("gqa_attention", dict(hidden_size=hidden, num_heads=2, num_kv_heads=1, head_dim=16,
+                                                   window=window if kind == "window" else 0, scale=None,
+                                                   position_encoding="rope"),
+                             dict(q=f"l{i}.q", k=f"l{i}.k", v=f"l{i}.v", o=f"l{i}.o"))
+        layers.append(LayerSpec("prenorm", {
+            "mixer_norm": PartSpec("rmsnorm", dict(size=hidden, eps=1e-5), dict(weight=f"l{i}.n1")),
+            "mixer": mixer,
+            "ffn_norm": PartSpec("rmsnorm", dict(size=hidden, eps=1e-5), dict(weight=f"l{i}.n2")),
+            "ffn": PartSpec("swiglu", dict(hidden_size=hidden, intermediate_size=48),
+                            dict(gate=f"l{i}.g", up=f"l{i}.u", down=f"l{i}.d"))}))
+    return ModelSpec(hidden_size=hidden, vocab_size=vocab, max_position=512,
+                     embedding=PartSpec("token_embedding", dict(vocab_size=vocab, hidden_size=hidden), dict(weight="emb")),
+                     layers=layers, order=[RunStep(*o) if isinstance(o, tuple) else RunStep(o) for o in order],
+                     final_norm=PartSpec("rmsnorm", dict(size=hidden, eps=1e-5), dict(weight="fn")),
+                     lm_head=PartSpec("lm_head", dict(vocab_size=vocab, hidden_size=hidden), dict(weight="head")),
+                     position_encodings={"rope": PartSpec("rotary", dict(rot_dim=16, theta=10000.0, scaling=None))})
+
+
+def register_toy_mixer():
+    """An exponential moving average over a request's tokens: state s <- decay*s + h*w
+    per token, output s.  Its state is one [hidden] vector per request, kept in the
+    engine's state slots; it has no pages."""
+    from ai_engine_b200.parts import Mixer, StateRequest, register_mixer
+    from ai_engine_b200.weights import TensorSpec
+
+    class ToyEMA(Mixer):
+        def __init__(self, spec, env):
+            super().__init__(spec, env)
+            self.hidden, self.decay = int(spec.params["hidden_size"]), float(spec.params["decay"])
+
+        def tensor_specs(self):
+            return [TensorSpec(self.spec.tensors["w"], (self.hidden,), init="ones")]
+
+        def load(self, source):
+            self.w = source.get(self.spec.tensors["w"]).float()
+
+        def state_request(self):
+            return StateRequest((self.hidden,), torch.float32)
+
+        def forward(self, h, ctx, cache):
+            out = torch.empty_like(h)
+            for r in range(ctx.R):
+                slot, a, n = int(ctx.h_slots[r]), int(ctx.h_q_start[r]), int(ctx.h_q_len[r])
+                s = cache.state[slot]
+                for t in range(a, a + n):
+                    s.mul_(self.decay).add_(h[t].float() * self.w)
+                    out[t] = s.to(h.dtype)
+            return out
+
+    register_mixer("toy_ema", ToyEMA)
+
+
+def plain_toy_forward(weights, kinds, order, ids, window=0):
+    """Whole-sequence float64 restatement of the toy model with the plain functions."""
+    w = {k: v.double() for k, v in weights.items()}
+    cfg = dict(heads=2, kv_heads=1, head_dim=16)
+    f = pl.inv_freq_default(16, 10000.0)
+    pos = torch.arange(len(ids))
+    x = pl.embed(torch.tensor(ids), w["emb"])
+    kv_seen = {}
+    for step, o in enumerate(order):
+        i, src = (o if isinstance(o, tuple) else (o, None))
+        h = pl.rms_norm(x, w[f"l{i}.n1"], 1e-5)
+        if kinds[i] == "ema":
+            s, outs = torch.zeros(x.shape[1], dtype=torch.float64), []
+            for t in range(len(ids)):
+                s = (0.5 + 0.1 * i) * s + h[t] * w[f"l{i}.mix.w"]
+                outs.append(s)
+            a = torch.stack(outs)
+        else:
+            h_kv = h if src is None else kv_seen[src]
+            kv_seen[step] = h_kv
+            a = pl_attention_with_kv_from(h, h_kv, w, i, order[src][0] if src is not None and isinstance(order[src], tuple)
+                                          else (order[src] if src is not None else i), pos, cfg, f,
+                                          window if kinds[i] == "window" else None)
+        x = x + a
+        h = pl.rms_norm(x, w[f"l{i}.n2"], 1e-5)
+        x = x + pl.swiglu(h, w[f"l{i}.g"], w[f"l{i}.u"], w[f"l{i}.d"])
+    return pl.rms_norm(x, w["fn"], 1e-5) @ w["head"].T
+
+
+def pl_attention_with_kv_from(h_q, h_kv, w, i, kv_layer, pos, cfg, f, window):
+    """pl.attention, with keys and values projected by layer `kv_layer` from `h_kv`
+    (a run that reads another run's cache sees that run's keys and values)."""
+    if kv_layer == i and h_q is h_kv:
+        return pl.attention(h_q, w[f"l{i}.q"], w[f"l{i}.k"], w[f"l{i}.v"], w[f"l{i}.o"], pos, cfg, f, window)
+    S, H, K, d = h_q.shape[0], 2, 1, 16
+    q = pl.rope((h_q @ w[f"l{i}.q"].T).view(S, H, d).transpose(0, 1), pos, f)
+    k = pl.rope((h_kv @ w[f"l{kv_layer}.k"].T).view(S, K, d).transpose(0, 1), pos, f).expand(H, S, d)
+    v = (h_kv @ w[f"l{kv_layer}.v"].T).view(S, K, d).transpose(0, 1).expand(H, S, d)
+    sc = (q @ k.transpose(1, 2)) / math.sqrt(d)
+    sc = sc.masked_fill(~(pos[None, :] <= pos[:, None])[None], float("-inf"))
+    return (torch.softmax(sc, -1) @ v).transpose(0, 1).reshape(S, H * d) @ w[f"l{i}.o"].T
+
+
+def build_toy(kinds, order, dtype=torch.float32, window=0, seed=0, page=8, pages=24):
+    from ai_engine_b200.cache import PagedCache
+    from ai_engine_b200.engine.step import StepRunner
+    from ai_engine_b200.parts import Model
+    from ai_engine_b200.weights import from_tensors, random_tensors
+
+    register_toy_mixer()
+    spec = tiny_toy_spec(order, kinds, window=window)
+    model = Model(spec, dtype, DEV)
+    specs = model.tensor_specs()
+    stored = dict(random_tensors(specs, seed, dtype, "cpu", std=0.15, norm_std=0.1))
+    model.load(from_tensors(stored, specs, dtype, DEV))
+    weights = {k: v.float() for k, v in stored.items()}
+    cache = PagedCache(model.cache_requests(), page, pages, 3, 192, dtype, DEV)
+    return model, cache, StepRunner(model, cache), weights
+
+
+def run_in_portions(runner, cache, ids, portions):
+    from ai_engine_b200.engine.step import StepEntry
+
+    slot, at, out = cache.admit(), 0, []
+    for p in portions:
+        assert cache.ensure(slot, at + p)
+        out.append(runner.step([StepEntry(slot, at, ids[at:at + p], list(range(p)))]).cpu())
+        at += p
+        cache.advance(slot, at)
+    runner.check_errors()
+    cache.finish(slot)
+    return torch.cat(out).double()
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped():
+    kinds, order = ["ema", "attn", "ema"], [0, 1, 2]
+    model, cache, runner, weights = build_toy(kinds, order)
+    reqs = model.cache_requests()
+    assert reqs[0][1] is not None and reqs[0][0] is None and reqs[1][0] is not None
+    assert set(cache.state) == {0, 2} and len(cache.groups) == 1
+    ids = random_ids(40, 50, 3)
+    want = plain_toy_forward(weights, kinds, order, ids)
+    whole = run_in_portions(runner, cache, ids, [40])
+    cut = run_in_portions(runner, cache, ids, [2, 9, 1, 1, 20, 7])
+    assert (whole - want).abs().max() <= 1e-4 and (cut - want).abs().max() <= 1e-4
+    # two requests side by side keep their own state
+    from ai_engine_b200.engine.step import StepEntry
+    other = random_ids(12, 50, 4)
+    a, b = cache.admit(), cache.admit()
+    cache.ensure(a, 40), cache.ensure(b, 12)
+    runner.step([StepEntry(a, 0, ids[:30], []), StepEntry(b, 0, other[:5], [])])
+    out = runner.step([StepEntry(b, 5, other[5:], [6]), StepEntry(a, 30, ids[30:], [9])]).cpu().double()
+    want_b = plain_toy_forward(weights, kinds, order, other)
+    assert (out[0] - want_b[11]).abs().max() <= 1e-4 and (out[1] - want[39]).abs().max() <= 1e-4
+
+
+def test_a_layer_named_twice_and_a_layer_that_reads_anothers_cache():
+    kinds = ["attn", "attn"]
+    order = [0, 1, 0, (1, 1)]           # layer 0 runs twice (two caches); the last run reads run 1's cache
+    model, cache, runner, weights = build_toy(kinds, order, seed=5)
+    assert len(cache.groups) == 1 and cache.groups[0].entries == [0, 1, 2]
+    assert cache.where[3] == cache.where[1]
+    ids = random_ids(33, 50, 6)
+    want = plain_toy_forward(weights, kinds, order, ids)
+    got = run_in_portions(runner, cache, ids, [5, 2, 17, 1, 8])
+    assert (got - want).abs().max() <= 1e-4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_windowed_layers_have_pages_of_their_own_and_give_them_back(dtype):
+    kinds, order = ["window", "attn"], [0, 1]
+    W = 20
+    model, cache, runner, weights = build_toy(kinds, order, dtype=dtype, window=W, seed=7, page=8, pages=20)
+    assert len(cache.groups) == 2 and sorted(g.request.window for g in cache.groups) == [0, W]
+    ids = random_ids(150, 50, 8)
+    want = plain_toy_forward(weights, kinds, order, ids, window=W)
+    got = run_in_portions(runner, cache, ids, [33, 2, 40, 1, 1, 1, 30, 42])
+    tol = 1e-4 if dtype == torch.float32 else 5e-2
+    err = (got - want).abs().max(dim=1).values
+    assert err.max() <= tol, f"first wrong token {int((err > tol).nonzero()[0])}"
+    wg = [g for g, grp in enumerate(cache.groups) if grp.request.window][0]
+    assert cache.book.high_water(wg) <= (42 + W) // 8 + 2       # never the whole sequence
+    assert cache.book.high_water(1 - wg) == (150 + 7) // 8

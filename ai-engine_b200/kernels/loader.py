@@ -44,8 +44,12 @@ def require_cuda() -> None:
             "no CUDA device: this engine runs on sm_100a kernels only and has no CPU path")
 
 
+LAUNCHES = [0]      # launches of this package's own kernels (library products not counted)
+
+
 def check(code: int, what: str) -> None:
     if code == 0:
+        LAUNCHES[0] += 1
         return
     if code == -1:
         raise KernelError(f"{what}: bad argument (dtype or shape combination not accepted)")

@@ -1,0 +1,275 @@
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Default run: the layer sizes of Llama-3-8B (32 layers, hidden 4096, 32 heads, 8 kv
+heads, head size 128, intermediate 14336, vocabulary 128256, bf16, random weights
+N(0, 0.02)), 8 requests with 1,024-token prompts in the cache of an 8,192-token
+context, KV page 16.  A step is one decode step of the whole batch.  Prints ONE
+JSON line: `value` = decoded tokens per second on the device (CUDA events around K
+steps), `e2e` = the same through Engine.add_request()/Engine.step() with host
+tokens in and out, `prefill` = one 2,048-token prompt in one step, `roofline` = the
+bytes a decode step has to read (every weight once + the live requests' cache)
+over its time against the measured copy bandwidth, `points` = decode at batch 1
+and 64.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA3_8B = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, intermediate_size=14336,
+                 num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                 vocab_size=128256, max_position_embeddings=8192, rope_theta=500000.0,
+                 rms_norm_eps=1e-5, tie_word_embeddings=False)
+CONTEXT, PROMPT_LEN, PREFILL_TOKENS, PAGE = 8192, 1024, 2048, 16
+
+
+def peaks():
+    """Measured peaks if the driver wrote them, else the stated fallback."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            m = json.load(open(p))
+            return dict(hbm_gbs=float(m["hbm_gbs"]), bf16_tflops=float(m["bf16_tflops"]),
+                        source="measured")
+        except Exception:
+            pass
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """SM clock and throttle reasons every 100 ms while the timed region runs (read only)."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+               0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self):
+        self.samples, self.reasons, self.max_mhz, self._stop = [], set(), None, threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv, self.h = pynvml, pynvml.nvmlDeviceGetHandleByIndex(0)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        while not self._stop.wait(0.1):
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                r = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                self.reasons |= {n for bit, n in self.REASONS.items() if r & bit}
+            except Exception:
+                pass
+
+    def __enter__(self):
+        if self.nv:
+            self.t = threading.Thread(target=self._run, daemon=True)
+            self.t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self.nv:
+            self.t.join()
+
+    def summary(self):
+        return dict(sm_mhz=statistics.median(self.samples) if self.samples else None,
+                    sm_max_mhz=self.max_mhz, reasons=sorted(self.reasons))
+
+
+def time_decode(torch, aie, model, batch, prompt_len, steps, warmup, ctx_cap):
+    """Device time of `steps` decode steps of `batch` requests that each hold
+    prompt_len tokens.  The cache is filled by a real prefill through the step function."""
+    from ai_engine_b200.cache import PagedCache
+    from ai_engine_b200.engine.step import StepEntry, StepRunner
+    from ai_engine_b200.kernels.loader import LAUNCHES
+    from ai_engine_b200.sampling.sampler import sample_rows
+
+    total = prompt_len + warmup + steps + 1
+    pages = batch * ((total + PAGE - 1) // PAGE) + 4
+    cache = PagedCache(model.cache_requests(), PAGE, pages, batch, ctx_cap, model.dtype, model.device)
+    runner = StepRunner(model, cache)
+    g = torch.Generator().manual_seed(0)
+    vocab = model.spec.vocab_size
+    slots = [cache.admit() for _ in range(batch)]
+    for s in slots:
+        assert cache.ensure(s, total)
+    for s in slots:           # prefill, one request a step, in portions of 2,048 tokens
+        ids = torch.randint(0, vocab, (prompt_len,), generator=g).tolist()
+        for a in range(0, prompt_len, 2048):
+            runner.step([StepEntry(s, a, ids[a:a + 2048], [])])
+    runner.check_errors()
+    zeros = torch.zeros(batch, device=model.device)
+    zk = torch.zeros(batch, dtype=torch.int32, device=model.device)
+    ones = torch.ones(batch, device=model.device)
+    tokens = torch.randint(0, vocab, (batch,), generator=g).tolist()
+
+    def one(i):
+        nonlocal tokens
+        logits = runner.step([StepEntry(s, prompt_len + i, [tokens[j]], [0]) for j, s in enumerate(slots)])
+        return sample_rows(logits, zeros, zk, ones, zeros)
+
+    for i in range(warmup):
+        out = one(i)
+    tokens = out.cpu().tolist()
+    torch.cuda.synchronize()
+    l0 = LAUNCHES[0]
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        out = one(warmup + i)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    runner.check_errors()
+    launches = LAUNCHES[0] - l0
+    ctx_tokens = batch * (prompt_len + warmup + steps / 2.0)
+    bytes_step = model.step_weight_bytes() + cache.kv_bytes_per_token() * ctx_tokens
+    del cache, runner
+    torch.cuda.empty_cache()
+    return dict(ms=ms, tok_s=batch * 1000.0 / ms, launches=launches, bytes=bytes_step)
+
+
+def time_e2e(torch, aie, model_cfg, batch, prompt_len, steps, warmup, layers):
+    """Through the public API: add_request(host ids) then step() — every step copies its
+    inputs from pinned host memory and reads the sampled tokens back."""
+    eng = aie.Engine(model_cfg, dtype="bf16", random_weights=True, seed=0, max_num_seqs=batch,
+                     block_size=PAGE, kv_cache_blocks=batch * ((prompt_len + steps + warmup + 32) // PAGE + 2),
+                     max_num_batched_tokens=2048, max_seq_len=CONTEXT)
+    g = torch.Generator().manual_seed(1)
+    sp = aie.SamplingParams(max_tokens=steps + warmup + 8, ignore_eos=True)
+    for _ in range(batch):
+        eng.add_request(torch.randint(0, model_cfg["vocab_size"], (prompt_len,), generator=g).tolist(), sp)
+    while eng.scheduler.num_waiting or any(eng.scheduler.computed(r) < prompt_len for r in eng.scheduler.running()):
+        eng.step()
+    for _ in range(warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    c0 = dict(eng.counters)
+    t0 = time.perf_counter()
+    n = 0
+    for _ in range(steps):
+        n += len(eng.step())
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    c1 = eng.counters
+    return dict(value=n / dt, unit="tokens/s",
+                h2d_bytes_per_step=(c1["h2d_bytes"] - c0["h2d_bytes"]) // steps,
+                d2h_bytes_per_step=(c1["d2h_bytes"] - c0["d2h_bytes"]) // steps), eng
+
+
+def time_prefill(torch, model, tokens, pk):
+    from ai_engine_b200.cache import PagedCache
+    from ai_engine_b200.engine.step import StepEntry, StepRunner
+
+    cache = PagedCache(model.cache_requests(), PAGE, tokens // PAGE + 2, 1, CONTEXT, model.dtype, model.device)
+    runner = StepRunner(model, cache)
+    ids = torch.randint(0, model.spec.vocab_size, (tokens,), generator=torch.Generator().manual_seed(2)).tolist()
+    best = None
+    for it in range(4):
+        slot = cache.admit()
+        cache.ensure(slot, tokens)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        runner.step([StepEntry(slot, 0, ids, [tokens - 1])])
+        e.record()
+        torch.cuda.synchronize()
+        cache.finish(slot)
+        if it >= 1:
+            ms = s.elapsed_time(e)
+            best = ms if best is None else min(best, ms)
+    runner.check_errors()
+    c = model.spec
+    lw = sum(p.numel() for l in model.layers for part in l.parts.values()
+             for p in (getattr(part, "w_qkv", None), getattr(part, "w_o", None), getattr(part, "w_gu", None),
+                       getattr(part, "w_down", None)) if p is not None)
+    att = model.layers[0].mixer
+    flops = 2.0 * tokens * lw + 2.0 * tokens * tokens * att.d * att.H * len(model.order) + 2.0 * c.vocab_size * c.hidden_size
+    return dict(value=tokens * 1000.0 / best, tokens=tokens, ms=best,
+                frac=flops / (best * 1e-3) / (pk["bf16_tflops"] * 1e12))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--layers", type=int, default=LLAMA3_8B["num_hidden_layers"],
+                    help="run fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="time one part only and print its numbers (for profiling)")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "einyx/ai-engine is a Rust workspace (cargo/rustc are not installed, pip cannot "
+                          "install it); no offline install of the reference is possible here"}))
+        return 0
+    if a.gpus != 1:
+        print("bench.py: this engine runs on one GPU; --gpus %d is not supported" % a.gpus)
+        return 2
+    import torch
+
+    import ai_engine_b200 as aie
+    from ai_engine_b200.engine.loading import random_model
+
+    warmup = max(a.warmup, 3)
+    pk = peaks()
+    cfg = dict(LLAMA3_8B)
+    cfg["num_hidden_layers"] = a.layers
+    model, _ = random_model(cfg, seed=0, dtype="bf16")
+    if a.only:
+        r = (time_decode(torch, aie, model, a.batch, PROMPT_LEN, a.steps, warmup, CONTEXT) if a.only == "decode"
+             else time_prefill(torch, model, PREFILL_TOKENS, pk))
+        print(json.dumps({"only": a.only, "layers": a.layers, **{k: round(v, 4) for k, v in r.items()}}))
+        return 0
+    with ClockSampler() as clocks:
+        main_pt = time_decode(torch, aie, model, a.batch, PROMPT_LEN, a.steps, warmup, CONTEXT)
+    points = {}
+    prefill = time_prefill(torch, model, PREFILL_TOKENS, pk)
+    if not a.skip_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = round(time_decode(torch, aie, model, b, PROMPT_LEN, min(a.steps, 32), 3, CONTEXT)["tok_s"], 1)
+        long = time_decode(torch, aie, model, a.batch, CONTEXT - 64, min(a.steps, 32), 3, CONTEXT)
+        points[f"decode_b{a.batch}_ctx{CONTEXT}"] = round(long["tok_s"], 1)
+    del model
+    torch.cuda.empty_cache()
+    e2e, eng = time_e2e(torch, aie, cfg, a.batch, PROMPT_LEN, a.steps, warmup, a.layers)
+    achieved = main_pt["bytes"] / (main_pt["ms"] * 1e-3) / 1e9
+    line = {
+        "metric": "decode tok/s at batch 8 (Llama-3-8B shape, bf16, 1,024-token prompts, context 8,192)",
+        "value": round(main_pt["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": a.steps,
+        "warmup": warmup, "ms_per_step": round(main_pt["ms"], 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0, 0.02), uniform random token ids",
+        "impl": "ours",
+        "config": {"model": "Llama-3-8B shape", "layers": a.layers, "layers_of_config": 32,
+                   "hidden": 4096, "heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 14336,
+                   "vocab": 128256, "global_batch": a.batch, "seq_len": PROMPT_LEN, "context": CONTEXT,
+                   "kv_page": PAGE, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (weights read every step)",
+                   "peaks": pk["source"]},
+        "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
+        "gpu_launches": main_pt["launches"],
+        "prefill": {"value": round(prefill["value"], 1), "tokens": prefill["tokens"],
+                    "ms": round(prefill["ms"], 3), "frac": round(prefill["frac"], 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

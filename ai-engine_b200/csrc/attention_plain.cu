@@ -1,4 +1,5 @@
-// Plain paged attention: one block per (query token, query head); keys are read
+// Plain paged attention: one block per (query token, query head) — all T tokens of
+// the step, or the T tokens named by `token_list`; keys are read
 // from the layer's pages through the request's block table.  It serves the
 // float32 path of the engine and is the reference the fast kernels are checked
 // against.  Formula (crates/ai-engine-runtime/src/arch/attention.rs:148-157,
@@ -20,14 +21,15 @@ paged_attention_plain_kernel(const A* __restrict__ q, const C* __restrict__ k_pa
                              const C* __restrict__ v_pages, A* __restrict__ out,
                              const int* __restrict__ positions, const int* __restrict__ token_req,
                              const int* __restrict__ block_table, int bt_width, int num_pages,
-                             int P, int H, int K, int d, int window, float scale, unsigned* err) {
+                             int P, int H, int K, int d, int window, float scale,
+                             const int* __restrict__ token_list, unsigned* err) {
     extern __shared__ __align__(16) float sm[];
     float* q_s = sm;                                  // d
     float* p_s = q_s + d;                             // CHUNK
     float* red = p_s + PLAIN_CHUNK;                   // 32
     long long* off_s = (long long*)(red + 32);        // CHUNK  (8-byte aligned: d is a multiple of 2)
 
-    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int t = token_list ? token_list[blockIdx.x] : blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int pos = positions[t];
     const int row = token_req[t];
     const int kvh = h / (H / K);
@@ -89,7 +91,8 @@ extern "C" int aie_paged_attention_plain(const void* q, const void* k_pages, con
                                          void* out, int dtype, const int* positions,
                                          const int* token_req, const int* block_table, int bt_width,
                                          int num_pages, int P, int T, int H, int K, int d, int window,
-                                         float scale, unsigned* err, cudaStream_t stream) {
+                                         float scale, const int* token_list, unsigned* err,
+                                         cudaStream_t stream) {
     if (T <= 0) return 0;
     if (d <= 0 || d > 2 * PLAIN_CHUNK || (d % 2) || K <= 0 || H % K) return AIE_UNSUPPORTED;
     const size_t smem = (size_t)(d + PLAIN_CHUNK + 32) * sizeof(float) + PLAIN_CHUNK * sizeof(long long);
@@ -98,11 +101,11 @@ extern "C" int aie_paged_attention_plain(const void* q, const void* k_pages, con
     if (dtype == AIE_F32)
         paged_attention_plain_kernel<float, float><<<grid, PLAIN_CHUNK, smem, stream>>>(
             (const float*)q, (const float*)k_pages, (const float*)v_pages, (float*)out, positions,
-            token_req, block_table, bt_width, num_pages, P, H, K, d, window, scale, err);
+            token_req, block_table, bt_width, num_pages, P, H, K, d, window, scale, token_list, err);
     else if (dtype == AIE_BF16)
         paged_attention_plain_kernel<bf16, bf16><<<grid, PLAIN_CHUNK, smem, stream>>>(
             (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, positions,
-            token_req, block_table, bt_width, num_pages, P, H, K, d, window, scale, err);
+            token_req, block_table, bt_width, num_pages, P, H, K, d, window, scale, token_list, err);
     else
         return AIE_BAD_ARG;
     AIE_LAUNCH_CHECK();

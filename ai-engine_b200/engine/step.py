@@ -72,7 +72,13 @@ class StepContext:
         def pad4(n):
             return (n + 3) // 4 * 4
 
+        # requests that bring one token (decode) and the tokens of all others
+        dec = q_start[q_len == 1]
+        other = np.nonzero(np.repeat(q_len != 1, q_len))[0].astype(np.int32)
+        self.n_decode = int(dec.shape[0])
+        self.max_decode_len = int((ctx_len[q_len == 1] + 1).max()) if self.n_decode else 0
         segs = [("token_ids", token_ids.astype(np.int32)), ("positions", positions),
+                ("decode_tokens", dec.astype(np.int32)), ("other_tokens", other),
                 ("token_req", token_req), ("q_start", q_start), ("q_len", q_len),
                 ("ctx_len", ctx_len), ("slots", slots),
                 ("logit_rows", np.asarray(rows, dtype=np.int32))]
@@ -98,6 +104,7 @@ class StepContext:
         self.token_ids, self.positions, self.token_req = seg("token_ids"), seg("positions"), seg("token_req")
         self.q_start, self.q_len, self.ctx_len, self.slots = seg("q_start"), seg("q_len"), seg("ctx_len"), seg("slots")
         self.logit_rows = seg("logit_rows")
+        self.decode_tokens, self.other_tokens = seg("decode_tokens"), seg("other_tokens")
         self.block_tables = [seg(f"bt{g}").view(R, width) for g in range(len(tables))]
         self.err = err
         self.device = device

@@ -170,10 +170,12 @@ def rope_kv_write(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
 def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                           positions: torch.Tensor, token_req: torch.Tensor,
                           block_table: torch.Tensor, scale: float, window: int, err: torch.Tensor,
-                          out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                          out: Optional[torch.Tensor] = None,
+                          token_list: Optional[torch.Tensor] = None) -> torch.Tensor:
     """softmax(q.k * scale over keys j <= pos (and j > pos - window)) . v per query
-    token and head, keys read through the block table.  q, out: [T, H, d]."""
-    _dev(q, k_pages, v_pages, positions, token_req, block_table, err)
+    token and head, keys read through the block table.  q, out: [T, H, d].
+    `token_list`: only these tokens are computed (the others' rows of out are left)."""
+    _dev(q, k_pages, v_pages, positions, token_req, block_table, err, token_list)
     T, H, d = q.shape
     num_pages, K, P, dp = k_pages.shape
     if dp != d or H % K:
@@ -186,14 +188,59 @@ def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
     check(lib.aie_paged_attention_plain(_p(q), _p(k_pages), _p(v_pages), _p(out),
                                         c_int(dtype_code(q)), _p(positions), _p(token_req),
                                         _p(block_table), c_int(block_table.shape[1]),
-                                        c_int(num_pages), c_int(P), c_int(T), c_int(H), c_int(K),
-                                        c_int(d), c_int(window), c_float(scale), _p(err), _stream()),
+                                        c_int(num_pages), c_int(P),
+                                        c_int(T if token_list is None else token_list.shape[0]),
+                                        c_int(H), c_int(K), c_int(d), c_int(window), c_float(scale),
+                                        _p(token_list), _p(err), _stream()),
           "paged_attention_plain")
     return out
 
 
+def decode_splits(n_dec: int, kv_heads: int, group: int, max_keys: int) -> int:
+    """How many parts to cut each decode request's keys into so that the grid fills
+    the machine: about two waves of CTAs, parts of at least 128 keys."""
+    ctas = n_dec * kv_heads * ((group + 3) // 4)
+    want = max(1, (2 * 148 * 3 + ctas - 1) // ctas)
+    return max(1, min(want, (max_keys + 127) // 128, 64))
+
+
+def paged_attention_decode(q, k_pages, v_pages, dec_tokens, positions, token_req, block_table,
+                           scale: float, window: int, splits: int, err, out) -> None:
+    """bfloat16 split-KV attention for the tokens in `dec_tokens` (requests that bring
+    one token).  Head sizes 64 and 128.  Uses scratch for the parts when splits > 1."""
+    _dev(q, k_pages, v_pages, dec_tokens, positions, token_req, block_table, err, out)
+    T, H, d = q.shape
+    num_pages, K, P, _ = k_pages.shape
+    n = dec_tokens.shape[0]
+    part_o = part_lse = None
+    if splits > 1:
+        part_o = torch.empty((n, H, splits, d), dtype=torch.float32, device=q.device)
+        part_lse = torch.empty((n, H, splits), dtype=torch.float32, device=q.device)
+    lib = library("attention_fast.cu")
+    check(lib.aie_paged_attention_decode(_p(q), _p(k_pages), _p(v_pages), _p(out), _p(part_o),
+                                         _p(part_lse), _p(dec_tokens), c_int(n), _p(positions),
+                                         _p(token_req), _p(block_table), c_int(block_table.shape[1]),
+                                         c_int(num_pages), c_int(P), c_int(H), c_int(K), c_int(d),
+                                         c_int(window), c_float(scale), c_int(splits), _p(err),
+                                         _stream()), "paged_attention_decode")
+
+
 def paged_attention(q, k_pages, v_pages, ctx, block_table, scale: float, window: int):
     """Attention of a step's query tokens over the cache.  float32 takes the plain
-    kernel; bfloat16 takes the fast kernels where they accept the sizes."""
-    return paged_attention_plain(q, k_pages, v_pages, ctx.positions, ctx.token_req, block_table,
-                                 scale, window, ctx.err)
+    kernel.  bfloat16 with a head size of 64 or 128: requests that bring one token
+    take the split-KV decode kernel, the others the plain kernel."""
+    T, H, d = q.shape
+    K = k_pages.shape[1]
+    fast = q.dtype == torch.bfloat16 and d in (64, 128)
+    if not fast or ctx.n_decode == 0:
+        return paged_attention_plain(q, k_pages, v_pages, ctx.positions, ctx.token_req, block_table,
+                                     scale, window, ctx.err)
+    out = torch.empty_like(q)
+    keys = ctx.max_decode_len if window <= 0 else min(window, ctx.max_decode_len)
+    paged_attention_decode(q, k_pages, v_pages, ctx.decode_tokens, ctx.positions, ctx.token_req,
+                           block_table, scale, window, decode_splits(ctx.n_decode, K, H // K, keys),
+                           ctx.err, out)
+    if ctx.n_decode < T:
+        paged_attention_plain(q, k_pages, v_pages, ctx.positions, ctx.token_req, block_table, scale,
+                              window, ctx.err, out=out, token_list=ctx.other_tokens)
+    return out

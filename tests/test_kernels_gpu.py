@@ -178,6 +178,55 @@ def test_paged_attention_plain(dtype, shape):
     assert (out.double() - want).abs().max() <= tol
 
 
+DECODE_SHAPES = [  # H, K, d, P, lens (one query each, the last token), window, splits
+    (4, 1, 64, 16, [1, 40, 700], 0, 1),
+    (32, 8, 128, 16, [1024, 3, 517, 90], 0, 4),
+    (6, 2, 64, 8, [33, 257], 0, 3),
+    (5, 1, 128, 16, [300, 31], 0, 2),          # a group of 5: two CTAs per kv head
+    (8, 1, 64, 32, [129], 0, 7),               # more splits than 32-key tiles in places
+    (2, 2, 128, 4, [64, 65, 1], 0, 1),
+    (8, 2, 128, 16, [900, 40], 100, 3),        # window
+    (24, 8, 128, 16, [2100], 0, 16),
+]
+
+
+@pytest.mark.parametrize("shape", DECODE_SHAPES)
+def test_paged_attention_decode_split_kv(shape):
+    H, K, d, P, lens, window, splits = shape
+    s = paged_setup(torch.bfloat16, H, K, d, P, lens, [1] * len(lens), seed=H + d + splits)
+    scale = 1.0 / math.sqrt(d)
+    e = err_word()
+    out = torch.full_like(s["q"], float("nan"))
+    dec = torch.arange(len(lens), device=DEV, dtype=torch.int32)
+    ops().paged_attention_decode(s["q"], s["k_pages"], s["v_pages"], dec, s["positions"], s["token_req"],
+                                 s["bt"], scale, window, splits, e, out)
+    want = attention_reference(s, H, K, d, scale, window)
+    assert int(e.item()) == 0 and not torch.isnan(out).any()
+    assert (out.double() - want).abs().max() <= 2e-2
+    plain = ops().paged_attention_plain(s["q"], s["k_pages"], s["v_pages"], s["positions"], s["token_req"],
+                                        s["bt"], scale, window, e)
+    assert (out.float() - plain.float()).abs().max() <= 1e-2
+
+
+def test_decode_kernel_takes_listed_tokens_only_and_plain_takes_the_rest():
+    """A mixed step: requests 0 and 2 bring one token, request 1 brings five."""
+    H, K, d, P = 8, 2, 64, 16
+    s = paged_setup(torch.bfloat16, H, K, d, P, [70, 30, 200], [1, 5, 1], seed=3)
+    scale = 1.0 / math.sqrt(d)
+
+    class Ctx:
+        pass
+
+    ctx = Ctx()
+    ctx.positions, ctx.token_req, ctx.err = s["positions"], s["token_req"], err_word()
+    ctx.n_decode, ctx.max_decode_len = 2, 200
+    ctx.decode_tokens = torch.tensor([0, 6], device=DEV, dtype=torch.int32)
+    ctx.other_tokens = torch.tensor([1, 2, 3, 4, 5], device=DEV, dtype=torch.int32)
+    out = ops().paged_attention(s["q"], s["k_pages"], s["v_pages"], ctx, s["bt"], scale, 0)
+    want = attention_reference(s, H, K, d, scale, 0)
+    assert (out.double() - want).abs().max() <= 2e-2
+
+
 def test_far_key_among_hundreds_is_found():
     """One key far back is made to match the query; the output must be its value."""
     H, K, d, P = 4, 2, 32, 16

@@ -39,7 +39,8 @@ def whole(rep, rid, ids):
     return out.numpy().astype(np.float64)
 
 
-CASES = [("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16")]
+CASES = [("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16"),
+         ("D", "float32"), ("D", "bfloat16")]
 
 
 @pytest.mark.parametrize("name,dtype", CASES)

@@ -47,3 +47,33 @@ extern "C" int aie_paged_attention_decode(const void* q, const void* k_pages, co
     }
     AIE_LAUNCH_CHECK();
 }
+
+// ---------------------------------------------------------------------------
+#include "attention_prefill.cuh"
+
+// tiles: [n_tiles][2] = (request row, offset of the 64-token tile within the request's tokens)
+extern "C" int aie_paged_attention_prefill(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                           const int* tiles, int n_tiles, const int* q_start, const int* q_len,
+                                           const int* ctx_len, const int* block_table, int bt_width,
+                                           int num_pages, int P, int H, int K, int d, int window, float scale,
+                                           unsigned* err, cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (K <= 0 || H % K) return AIE_BAD_ARG;
+    if (d != 64 && d != 128) return AIE_UNSUPPORTED;
+    if (H > 65535) return AIE_UNSUPPORTED;
+    dim3 grid(n_tiles, H);
+    if (d == 64) {
+        const size_t smem = prefill_smem_bytes<64>();
+        cudaFuncSetAttribute(paged_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        paged_prefill_kernel<64><<<grid, PF_WARPS * 32, smem, stream>>>(
+            (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, tiles, q_start, q_len, ctx_len,
+            block_table, bt_width, num_pages, P, H, K, window, scale, err);
+    } else {
+        const size_t smem = prefill_smem_bytes<128>();
+        cudaFuncSetAttribute(paged_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        paged_prefill_kernel<128><<<grid, PF_WARPS * 32, smem, stream>>>(
+            (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, tiles, q_start, q_len, ctx_len,
+            block_table, bt_width, num_pages, P, H, K, window, scale, err);
+    }
+    AIE_LAUNCH_CHECK();
+}

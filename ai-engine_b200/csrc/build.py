@@ -105,6 +105,13 @@ def _build(target: str, cmd_prefix: List[str], sources: List[str], deps: List[st
     tmp = f"{target}.{os.getpid()}.tmp"
     _run(cmd_prefix + flags + sources + ["-o", tmp], what)
     os.replace(tmp, target)
+    stem = os.path.basename(target).rsplit("-", 1)[0] + "-"      # older builds of the same source
+    for f in os.listdir(os.path.dirname(target)):
+        if f.startswith(stem) and f.endswith(".so") and f != os.path.basename(target):
+            try:
+                os.remove(os.path.join(os.path.dirname(target), f))
+            except OSError:
+                pass
     return target
 
 

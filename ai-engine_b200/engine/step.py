@@ -77,8 +77,10 @@ class StepContext:
         other = np.nonzero(np.repeat(q_len != 1, q_len))[0].astype(np.int32)
         self.n_decode = int(dec.shape[0])
         self.max_decode_len = int((ctx_len[q_len == 1] + 1).max()) if self.n_decode else 0
+        tiles = [(r, o) for r in range(R) if q_len[r] != 1 for o in range(0, int(q_len[r]), 64)]
         segs = [("token_ids", token_ids.astype(np.int32)), ("positions", positions),
                 ("decode_tokens", dec.astype(np.int32)), ("other_tokens", other),
+                ("prefill_tiles", np.asarray(tiles, dtype=np.int32).reshape(-1)),
                 ("token_req", token_req), ("q_start", q_start), ("q_len", q_len),
                 ("ctx_len", ctx_len), ("slots", slots),
                 ("logit_rows", np.asarray(rows, dtype=np.int32))]
@@ -105,6 +107,7 @@ class StepContext:
         self.q_start, self.q_len, self.ctx_len, self.slots = seg("q_start"), seg("q_len"), seg("ctx_len"), seg("slots")
         self.logit_rows = seg("logit_rows")
         self.decode_tokens, self.other_tokens = seg("decode_tokens"), seg("other_tokens")
+        self.prefill_tiles = seg("prefill_tiles").view(-1, 2)
         self.block_tables = [seg(f"bt{g}").view(R, width) for g in range(len(tables))]
         self.err = err
         self.device = device

@@ -225,22 +225,41 @@ def paged_attention_decode(q, k_pages, v_pages, dec_tokens, positions, token_req
                                          _stream()), "paged_attention_decode")
 
 
+def paged_attention_prefill(q, k_pages, v_pages, tiles, q_start, q_len, ctx_len, block_table,
+                            scale: float, window: int, err, out) -> None:
+    """bfloat16 tensor-core attention for requests that bring more than one token.
+    `tiles`: int32 [n, 2] = (request row, offset of a 64-token tile in its tokens).
+    Head sizes 64 and 128."""
+    _dev(q, k_pages, v_pages, tiles, q_start, q_len, ctx_len, block_table, err, out)
+    T, H, d = q.shape
+    num_pages, K, P, _ = k_pages.shape
+    lib = library("attention_fast.cu")
+    check(lib.aie_paged_attention_prefill(_p(q), _p(k_pages), _p(v_pages), _p(out), _p(tiles),
+                                          c_int(tiles.shape[0]), _p(q_start), _p(q_len), _p(ctx_len),
+                                          _p(block_table), c_int(block_table.shape[1]),
+                                          c_int(num_pages), c_int(P), c_int(H), c_int(K), c_int(d),
+                                          c_int(window), c_float(scale), _p(err), _stream()),
+          "paged_attention_prefill")
+
+
 def paged_attention(q, k_pages, v_pages, ctx, block_table, scale: float, window: int):
     """Attention of a step's query tokens over the cache.  float32 takes the plain
     kernel.  bfloat16 with a head size of 64 or 128: requests that bring one token
-    take the split-KV decode kernel, the others the plain kernel."""
+    take the split-KV decode kernel, the others the tensor-core kernel for portions
+    of prompts; other head sizes take the plain kernel."""
     T, H, d = q.shape
     K = k_pages.shape[1]
     fast = q.dtype == torch.bfloat16 and d in (64, 128)
-    if not fast or ctx.n_decode == 0:
+    if not fast:
         return paged_attention_plain(q, k_pages, v_pages, ctx.positions, ctx.token_req, block_table,
                                      scale, window, ctx.err)
     out = torch.empty_like(q)
-    keys = ctx.max_decode_len if window <= 0 else min(window, ctx.max_decode_len)
-    paged_attention_decode(q, k_pages, v_pages, ctx.decode_tokens, ctx.positions, ctx.token_req,
-                           block_table, scale, window, decode_splits(ctx.n_decode, K, H // K, keys),
-                           ctx.err, out)
-    if ctx.n_decode < T:
-        paged_attention_plain(q, k_pages, v_pages, ctx.positions, ctx.token_req, block_table, scale,
-                              window, ctx.err, out=out, token_list=ctx.other_tokens)
+    if ctx.n_decode:
+        keys = ctx.max_decode_len if window <= 0 else min(window, ctx.max_decode_len)
+        paged_attention_decode(q, k_pages, v_pages, ctx.decode_tokens, ctx.positions, ctx.token_req,
+                               block_table, scale, window,
+                               decode_splits(ctx.n_decode, K, H // K, keys), ctx.err, out)
+    if ctx.n_decode < ctx.R:
+        paged_attention_prefill(q, k_pages, v_pages, ctx.prefill_tiles, ctx.q_start, ctx.q_len,
+                                ctx.ctx_len, block_table, scale, window, ctx.err, out)
     return out

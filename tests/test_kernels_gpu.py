@@ -208,7 +208,37 @@ def test_paged_attention_decode_split_kv(shape):
     assert (out.float() - plain.float()).abs().max() <= 1e-2
 
 
-def test_decode_kernel_takes_listed_tokens_only_and_plain_takes_the_rest():
+PREFILL_SHAPES = [  # H, K, d, P, lens, q_lens, window
+    (4, 2, 64, 16, [5, 40], [5, 7], 0),
+    (32, 8, 128, 16, [300, 130, 64], [300, 2, 64], 0),
+    (6, 2, 64, 8, [257, 65], [129, 65], 0),           # a portion that starts mid-page and mid-tile
+    (5, 1, 128, 4, [700], [63], 0),
+    (2, 2, 128, 32, [1100], [1100], 0),
+    (8, 2, 64, 16, [400, 90], [400, 30], 70),         # window
+    (3, 3, 128, 16, [200], [2], 0),
+    (4, 1, 64, 64, [191, 192, 193], [191, 128, 2], 0),
+]
+
+
+@pytest.mark.parametrize("shape", PREFILL_SHAPES)
+def test_paged_attention_prefill_tensor_cores(shape):
+    H, K, d, P, lens, q_lens, window = shape
+    s = paged_setup(torch.bfloat16, H, K, d, P, lens, q_lens, seed=H + d + len(lens))
+    scale = 1.0 / math.sqrt(d)
+    e = err_word()
+    out = torch.full_like(s["q"], float("nan"))
+    i32 = lambda a: torch.tensor(a, device=DEV, dtype=torch.int32)
+    q_start = np.concatenate([[0], np.cumsum(q_lens)[:-1]])
+    tiles = [(r, o) for r, n in enumerate(q_lens) for o in range(0, n, 64)]
+    ops().paged_attention_prefill(s["q"], s["k_pages"], s["v_pages"], i32(tiles), i32(q_start), i32(q_lens),
+                                  i32([n - ql for n, ql in zip(lens, q_lens)]), s["bt"], scale, window, e, out)
+    want = attention_reference(s, H, K, d, scale, window)
+    assert int(e.item()) == 0 and not torch.isnan(out).any()
+    err = (out.double() - want).abs().amax(dim=(1, 2))
+    assert err.max() <= 2e-2, f"first wrong token {int((err > 2e-2).nonzero()[0])} of {sum(q_lens)}: {float(err.max())}"
+
+
+def test_mixed_step_decode_and_prefill_kernels_side_by_side():
     """A mixed step: requests 0 and 2 bring one token, request 1 brings five."""
     H, K, d, P = 8, 2, 64, 16
     s = paged_setup(torch.bfloat16, H, K, d, P, [70, 30, 200], [1, 5, 1], seed=3)
@@ -222,6 +252,9 @@ def test_decode_kernel_takes_listed_tokens_only_and_plain_takes_the_rest():
     ctx.n_decode, ctx.max_decode_len = 2, 200
     ctx.decode_tokens = torch.tensor([0, 6], device=DEV, dtype=torch.int32)
     ctx.other_tokens = torch.tensor([1, 2, 3, 4, 5], device=DEV, dtype=torch.int32)
+    i32 = lambda a: torch.tensor(a, device=DEV, dtype=torch.int32)
+    ctx.R, ctx.prefill_tiles = 3, i32([[1, 0]])
+    ctx.q_start, ctx.q_len, ctx.ctx_len = i32([0, 1, 6]), i32([1, 5, 1]), i32([69, 25, 199])
     out = ops().paged_attention(s["q"], s["k_pages"], s["v_pages"], ctx, s["bt"], scale, 0)
     want = attention_reference(s, H, K, d, scale, 0)
     assert (out.double() - want).abs().max() <= 2e-2

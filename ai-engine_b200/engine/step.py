@@ -12,6 +12,7 @@ Logits come back only for the rows that are wanted.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
@@ -35,11 +36,53 @@ _ERR_BITS = {1: "a token id outside the vocabulary", 2: "a block table entry out
              4: "a bounded wait in a kernel ran out", 8: "a request row outside its table"}
 
 
+class _Buffers:
+    """Pinned host and device int32 buffers of one layout (one tuple of segment
+    lengths), reused by every step of that layout; a CUDA graph captured on them
+    stays valid because their addresses never change."""
+
+    def __init__(self, lengths, device):
+        self.offsets, o = [], 0
+        for n in lengths:
+            self.offsets.append((o, n))
+            o += (n + 3) // 4 * 4
+        self.total = max(o, 4)
+        # a ring of pinned staging buffers: the host may run ahead of the device, so a
+        # staging buffer is rewritten only after the copy that read it has finished
+        self.hosts = [torch.zeros(self.total, dtype=torch.int32, pin_memory=device.type == "cuda")
+                      for _ in range(4)]
+        self.copied = [None] * 4
+        self.turn = 0
+        self.dev = torch.zeros(self.total, dtype=torch.int32, device=device)
+        self.graph = None          # torch.cuda.CUDAGraph of a decode-only step on these buffers
+        self.graph_logits = None
+        self.graph_kernels = 0
+        self.uses = 0
+
+    def upload(self, arrays) -> None:
+        i = self.turn
+        self.turn = (i + 1) % len(self.hosts)
+        if self.copied[i] is not None:
+            self.copied[i].synchronize()
+        hv = self.hosts[i].numpy()
+        for (o, n), a in zip(self.offsets, arrays):
+            hv[o:o + n] = a
+        self.dev.copy_(self.hosts[i], non_blocking=True)
+        if self.dev.is_cuda:
+            ev = self.copied[i] or torch.cuda.Event()
+            ev.record()
+            self.copied[i] = ev
+
+
 class StepContext:
     """Device-side description of one step.  All index arrays are int32 and live
     in one buffer that is filled on the host and copied once."""
 
-    def __init__(self, entries: Sequence[StepEntry], cache, device, err: torch.Tensor):
+    SEGMENTS = ("token_ids", "positions", "token_req", "decode_tokens", "other_tokens",
+                "prefill_tiles", "q_start", "q_len", "ctx_len", "slots", "logit_rows")
+
+    def __init__(self, entries: Sequence[StepEntry], cache, device, err: torch.Tensor,
+                 buffers: Optional[dict] = None, bucket_width: bool = False):
         R = len(entries)
         q_len = np.array([len(e.tokens) for e in entries], dtype=np.int32)
         if R == 0 or int(q_len.min()) < 1:
@@ -67,72 +110,97 @@ class StepContext:
         self.max_q_len = int(q_len.max())
         self.max_total_len = int((ctx_len + q_len).max())
         width = cache.block_table_width(self.max_total_len)
+        if bucket_width:            # few distinct widths, so layouts (and graphs) are reused
+            width = max(64, 1 << (width - 1).bit_length())
+        self.bt_width = width
         tables = cache.fill_block_tables(slots.tolist(), width)
 
-        def pad4(n):
-            return (n + 3) // 4 * 4
-
         # requests that bring one token (decode) and the tokens of all others
-        dec = q_start[q_len == 1]
-        other = np.nonzero(np.repeat(q_len != 1, q_len))[0].astype(np.int32)
+        is_dec = q_len == 1
+        dec = q_start[is_dec]
+        other = np.nonzero(np.repeat(~is_dec, q_len))[0].astype(np.int32)
         self.n_decode = int(dec.shape[0])
-        self.max_decode_len = int((ctx_len[q_len == 1] + 1).max()) if self.n_decode else 0
+        self.max_decode_len = int((ctx_len[is_dec] + 1).max()) if self.n_decode else 0
+        if bucket_width and self.n_decode:
+            self.max_decode_len = width * cache.page_size      # a property of the layout, not of the step
         tiles = [(r, o) for r in range(R) if q_len[r] != 1 for o in range(0, int(q_len[r]), 64)]
-        segs = [("token_ids", token_ids.astype(np.int32)), ("positions", positions),
-                ("decode_tokens", dec.astype(np.int32)), ("other_tokens", other),
-                ("prefill_tiles", np.asarray(tiles, dtype=np.int32).reshape(-1)),
-                ("token_req", token_req), ("q_start", q_start), ("q_len", q_len),
-                ("ctx_len", ctx_len), ("slots", slots),
-                ("logit_rows", np.asarray(rows, dtype=np.int32))]
-        for g, tb in enumerate(tables):
-            segs.append((f"bt{g}", tb.reshape(-1)))
-        total = sum(pad4(len(a)) for _, a in segs)
-        pinned = device.type == "cuda"
-        host = torch.zeros(total, dtype=torch.int32, pin_memory=pinned)
-        hv = host.numpy()
-        offs, o = {}, 0
-        for name, a in segs:
-            hv[o:o + len(a)] = a
-            offs[name] = (o, len(a))
-            o += pad4(len(a))
-        self.h2d_bytes = total * 4
-        dev = host.to(device, non_blocking=True)
-        self._host_keepalive = host
-
-        def seg(name):
-            b, n = offs[name]
-            return dev[b:b + n]
-
-        self.token_ids, self.positions, self.token_req = seg("token_ids"), seg("positions"), seg("token_req")
-        self.q_start, self.q_len, self.ctx_len, self.slots = seg("q_start"), seg("q_len"), seg("ctx_len"), seg("slots")
-        self.logit_rows = seg("logit_rows")
-        self.decode_tokens, self.other_tokens = seg("decode_tokens"), seg("other_tokens")
-        self.prefill_tiles = seg("prefill_tiles").view(-1, 2)
-        self.block_tables = [seg(f"bt{g}").view(R, width) for g in range(len(tables))]
+        arrays = [token_ids.astype(np.int32), positions, token_req, dec.astype(np.int32), other,
+                  np.asarray(tiles, dtype=np.int32).reshape(-1), q_start, q_len, ctx_len, slots,
+                  np.asarray(rows, dtype=np.int32)] + [tb.reshape(-1) for tb in tables]
+        key = tuple(len(a) for a in arrays) + (width,)
+        self.layout_key = key
+        buf = buffers.get(key) if buffers is not None else None
+        if buf is None:
+            buf = _Buffers(key[:-1], device)
+            if buffers is not None:
+                if len(buffers) >= 128:
+                    buffers.pop(next(iter(buffers)))
+                buffers[key] = buf
+        buf.uses += 1
+        self.buffers = buf
+        buf.upload(arrays)
+        self.h2d_bytes = buf.total * 4
+        dev = buf.dev
+        views = [dev[o:o + n] for o, n in buf.offsets]
+        (self.token_ids, self.positions, self.token_req, self.decode_tokens, self.other_tokens,
+         pt, self.q_start, self.q_len, self.ctx_len, self.slots, self.logit_rows) = views[:11]
+        self.prefill_tiles = pt.view(-1, 2)
+        self.block_tables = [v.view(R, width) for v in views[11:]]
         self.err = err
         self.device = device
 
 
 class StepRunner:
-    """Binds a model to its cache and runs steps."""
+    """Binds a model to its cache and runs steps.  Steps in which every request
+    brings one token (decode) are captured once per layout as a CUDA graph and
+    replayed: the launch cost of some hundred kernels a step is paid once."""
 
-    def __init__(self, model, cache):
+    def __init__(self, model, cache, use_graphs: Optional[bool] = None):
         self.model, self.cache = model, cache
         self.device = model.device
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.last_ctx: Optional[StepContext] = None
+        self.buffers: dict = {}
+        if use_graphs is None:
+            use_graphs = (model.dtype == torch.bfloat16 and not model.has_host_parts()
+                          and not os.environ.get("AI_ENGINE_B200_NO_GRAPHS"))
+        self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
+        self.graph_launches = 0        # kernels replayed through graphs (for launch counts)
+        self.graphs_captured = 0
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the entries as one batch; float32 logits [wanted rows, vocab] on the
-        device, in the order of the entries and of their `want`."""
+        device, in the order of the entries and of their `want`.  The tensor is
+        valid until the next call of step()."""
         max_len = self.cache.max_seq_len
+        decode_only = True
         for e in entries:
             if e.start + len(e.tokens) > max_len:
                 raise StepError(f"request in slot {e.slot} would hold {e.start + len(e.tokens)} "
                                 f"tokens, more than max_seq_len {max_len}")
-        ctx = StepContext(entries, self.cache, self.device, self.err)
+            decode_only = decode_only and len(e.tokens) == 1
+        graphed = self.use_graphs and decode_only
+        ctx = StepContext(entries, self.cache, self.device, self.err, self.buffers, bucket_width=graphed)
         self.last_ctx = ctx
-        return self.model.forward(ctx, self.cache)
+        if not graphed:
+            return self.model.forward(ctx, self.cache)
+        buf = ctx.buffers
+        if buf.graph is None:
+            if buf.uses < 2:                       # a layout seen once is not worth a capture
+                return self.model.forward(ctx, self.cache)
+            from ..kernels.loader import LAUNCHES
+            self.model.forward(ctx, self.cache)    # warm-up outside the capture (library set-up)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            n0 = LAUNCHES[0]
+            with torch.cuda.graph(g):
+                buf.graph_logits = self.model.forward(ctx, self.cache)
+            buf.graph_kernels = LAUNCHES[0] - n0
+            buf.graph = g
+            self.graphs_captured += 1
+        buf.graph.replay()
+        self.graph_launches += buf.graph_kernels
+        return buf.graph_logits
 
     def check_errors(self) -> None:
         """Raise if a kernel flagged a fault since the last check (synchronises)."""

@@ -68,7 +68,11 @@ class Part:
 
 class Mixer(Part):
     """Mixes information across a request's tokens.  forward(h [T, hidden],
-    ctx, cache) -> [T, hidden] in the compute dtype."""
+    ctx, cache) -> [T, hidden] in the compute dtype.  A part whose forward reads
+    the step's host-side arrays (ctx.h_*) sets `host_side = True`; a model with such
+    a part is never replayed from a captured CUDA graph."""
+
+    host_side = False
 
     def cache_request(self) -> Optional[KVRequest]:
         return None

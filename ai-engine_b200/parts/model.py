@@ -94,6 +94,11 @@ class Model:
             out.append((kv if rs.cache_from is None else None, st, rs.cache_from))
         return out
 
+    def has_host_parts(self) -> bool:
+        """True when a part reads step data on the host inside forward (`host_side =
+        True` on its class): such a model cannot be replayed from a captured graph."""
+        return any(getattr(p, "host_side", False) for p in self.all_parts())
+
     def step_weight_bytes(self) -> int:
         """Bytes of weights one step reads: every part once per run, the head once."""
         total = self.lm_head.weight_bytes() + self.final_norm.weight_bytes()

@@ -190,3 +190,33 @@ def test_command_line(tmp_path):
     assert_same_until_a_close_call(lines[0], want, margins, TOL_F32)
     bad = subprocess.run(exe + ["--model", str(tmp_path / "none"), "--prompt-ids", "1"], capture_output=True, text=True)
     assert bad.returncode == 1 and "error" in bad.stderr
+
+
+def test_decode_steps_replayed_from_a_graph_match_eager_steps(tmp_path):
+    """bfloat16 decode steps are captured once per layout and replayed; the logits must be
+    the ones the same step gives when every kernel is launched afresh."""
+    from ai_engine_b200.cache import PagedCache
+    from ai_engine_b200.engine.loading import load_model
+    from ai_engine_b200.engine.step import StepEntry, StepRunner
+
+    d = make_model_dir(tmp_path, "D")
+    model, _ = load_model(d, "bfloat16")
+    ids = [random_ids(40 + 3 * i, 300, 60 + i) for i in range(3)]
+    outs = {}
+    for graphs in (False, True):
+        cache = PagedCache(model.cache_requests(), 16, 64, 4, 2048, model.dtype, model.device)
+        runner = StepRunner(model, cache, use_graphs=graphs)
+        slots = [cache.admit() for _ in ids]
+        for s, p in zip(slots, ids):
+            cache.ensure(s, len(p) + 40)
+            runner.step([StepEntry(s, 0, p[:20], [])])
+        got = []
+        for k in range(20):
+            got.append(runner.step([StepEntry(s, 20 + k, [p[20 + k]], [0]) for s, p in zip(slots, ids)]).cpu())
+        runner.check_errors()
+        outs[graphs] = torch.stack(got)
+        if graphs:
+            assert runner.graphs_captured == 1 and runner.graph_launches > 0
+    assert torch.equal(outs[True], outs[False])
+    ref = plain_logits(d, ids[1][:40], torch.float32)
+    assert np.abs(outs[True][:, 1].numpy() - ref[20:40]).max() <= TOL_BF16

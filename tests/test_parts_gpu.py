@@ -105,6 +105,8 @@ def register_toy_mixer():
     from ai_engine_b200.weights import TensorSpec
 
     class ToyEMA(Mixer):
+        host_side = True        # forward walks the requests on the host
+
         def __init__(self, spec, env):
             super().__init__(spec, env)
             self.hidden, self.decay = int(spec.params["hidden_size"]), float(spec.params["decay"])

@@ -5,13 +5,17 @@
 // heads that share it (so each key and value is read once for the group), over
 // one contiguous part of the request's keys (a "split"; the host picks the number
 // of splits so that the grid fills the machine however few requests there are).
-// Four warps take 32-key tiles of the split in turn.  For a tile, 8 lanes share a
-// key: each holds 1/8 of the head in registers beside the matching 1/8 of every
-// query head (float32), partial dots are joined with three shuffles, the running
-// maximum and sum are float32 (online softmax), probabilities pass through
-// shared memory, and each lane accumulates D/32 output elements per head from
-// coalesced reads of the value rows.  Warps and then splits are merged with the
-// usual (max, sum) rescaling; all softmax arithmetic is float32.
+// Each of its four warps runs a pipeline of its own: 16-key tiles of keys and
+// values are gathered page by page into the warp's ring of shared-memory stages
+// with 16-byte cp.async copies, three or four tiles ahead of the arithmetic, so
+// the memory system always has work in flight and no warp waits on a block-table
+// lookup (the CTA reads its block-table entries once, up front).  For a staged
+// tile, 8 lanes share a key: each multiplies 1/8 of the key with the matching 1/8
+// of every query head (held in registers as float32), partial dots are joined
+// with three shuffles, the running maximum and sum are float32 (online softmax),
+// probabilities pass through shared memory, and each lane accumulates D/32 output
+// elements per head.  Warps and then splits are merged with the usual (max, sum)
+// rescaling; all softmax arithmetic is float32.
 // Formula: crates/ai-engine-runtime/src/arch/attention.rs:148-157,177-196,203-224.
 #include "common.cuh"
 #include "attention_decode.cuh"
@@ -30,6 +34,7 @@ extern "C" int aie_paged_attention_decode(const void* q, const void* k_pages, co
     const int GC = G >= 4 ? 4 : G;
     const int gchunks = (G + GC - 1) / GC;
     if (K * gchunks > 65535 || n_dec > 65535) return AIE_UNSUPPORTED;
+    if ((bt_width + S - 1) / S + 2 > DEC_MAX_PAGES) return AIE_UNSUPPORTED;   // more splits needed
     dim3 grid(S, K * gchunks, n_dec);
     int rc;
     if (d == 64)

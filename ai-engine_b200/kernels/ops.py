@@ -196,12 +196,14 @@ def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
     return out
 
 
-def decode_splits(n_dec: int, kv_heads: int, group: int, max_keys: int) -> int:
+def decode_splits(n_dec: int, kv_heads: int, group: int, max_keys: int, bt_width: int = 0) -> int:
     """How many parts to cut each decode request's keys into so that the grid fills
-    the machine: about two waves of CTAs, parts of at least 128 keys."""
+    the machine (two CTAs fit on each of the 148 SMs), with parts of at least 128
+    keys, and no part spanning more block-table entries than a CTA keeps."""
     ctas = n_dec * kv_heads * ((group + 3) // 4)
-    want = max(1, (2 * 148 * 3 + ctas - 1) // ctas)
-    return max(1, min(want, (max_keys + 127) // 128, 64))
+    want = max(1, (2 * 148 + ctas - 1) // ctas)
+    s = max(1, min(want, (max_keys + 127) // 128, 64))
+    return max(s, (bt_width + 1999) // 2000)
 
 
 def paged_attention_decode(q, k_pages, v_pages, dec_tokens, positions, token_req, block_table,
@@ -258,7 +260,8 @@ def paged_attention(q, k_pages, v_pages, ctx, block_table, scale: float, window:
         keys = ctx.max_decode_len if window <= 0 else min(window, ctx.max_decode_len)
         paged_attention_decode(q, k_pages, v_pages, ctx.decode_tokens, ctx.positions, ctx.token_req,
                                block_table, scale, window,
-                               decode_splits(ctx.n_decode, K, H // K, keys), ctx.err, out)
+                               decode_splits(ctx.n_decode, K, H // K, keys, block_table.shape[1]),
+                               ctx.err, out)
     if ctx.n_decode < ctx.R:
         paged_attention_prefill(q, k_pages, v_pages, ctx.prefill_tiles, ctx.q_start, ctx.q_len,
                                 ctx.ctx_len, block_table, scale, window, ctx.err, out)

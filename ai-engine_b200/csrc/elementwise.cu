@@ -20,11 +20,35 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const W* __rest
     for (int i = threadIdx.x; i < D; i += blockDim.x) x[(size_t)t * D + i] = to_f32<W>(row[i]);
 }
 
+// bf16 table, D a multiple of 8: 16-byte loads, two float4 stores per thread
+__global__ void embed_gather_vec_kernel(const int* __restrict__ ids, const bf16* __restrict__ table,
+                                        float* __restrict__ x, int D, int vocab, unsigned* err) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;
+    if (!ok && threadIdx.x == 0) atomicOr(err, AIE_DEV_TOKEN_OOB);
+    const uint4* row = reinterpret_cast<const uint4*>(table + (size_t)(ok ? id : 0) * D);
+    float4* dst = reinterpret_cast<float4*>(x + (size_t)t * D);
+    for (int i = threadIdx.x; i < D / 8; i += blockDim.x) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        if (ok) {
+            const uint4 raw = row[i];
+            const bf16* e = reinterpret_cast<const bf16*>(&raw);
+            a = make_float4(__bfloat162float(e[0]), __bfloat162float(e[1]), __bfloat162float(e[2]), __bfloat162float(e[3]));
+            b = make_float4(__bfloat162float(e[4]), __bfloat162float(e[5]), __bfloat162float(e[6]), __bfloat162float(e[7]));
+        }
+        dst[2 * i] = a;
+        dst[2 * i + 1] = b;
+    }
+}
+
 extern "C" int aie_embed_gather(const int* ids, const void* table, int table_dtype, float* x,
                                 int T, int D, int vocab, unsigned* err, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (table_dtype == AIE_F32)
         embed_gather_kernel<float><<<T, 256, 0, stream>>>(ids, (const float*)table, x, D, vocab, err);
+    else if (table_dtype == AIE_BF16 && D % 8 == 0)
+        embed_gather_vec_kernel<<<T, D >= 4096 ? 512 : 128, 0, stream>>>(ids, (const bf16*)table, x, D, vocab, err);
     else if (table_dtype == AIE_BF16)
         embed_gather_kernel<bf16><<<T, 256, 0, stream>>>(ids, (const bf16*)table, x, D, vocab, err);
     else
@@ -64,10 +88,57 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const A* __restrict__ 
     }
 }
 
+// Fast path: D a multiple of 4 and at most 4 * 1024: the whole row lives in registers
+// (one float4 per thread), read once and written once.  Same arithmetic and the same
+// block reduction as the general kernel.
+template <typename A, typename W, typename O>
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_row_kernel(float* __restrict__ x, const A* __restrict__ delta, const W* __restrict__ w,
+                       O* __restrict__ out, const int* __restrict__ rows, int D, float eps, int write_back) {
+    __shared__ float red[32];
+    const int o = blockIdx.x;
+    const size_t r = rows ? (size_t)rows[o] : (size_t)o;
+    const int i = threadIdx.x;
+    const bool on = i < D / 4;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (on) {
+        s = reinterpret_cast<const float4*>(x + r * D)[i];
+        if (delta) {
+            const float4 dl = load4<A>(delta + r * D + 4 * i);
+            s.x += dl.x;
+            s.y += dl.y;
+            s.z += dl.z;
+            s.w += dl.w;
+        }
+    }
+    float ss = s.x * s.x;
+    ss += s.y * s.y;
+    ss += s.z * s.z;
+    ss += s.w * s.w;
+    ss = block_sum(ss, red);
+    const float rinv = 1.0f / sqrtf(ss / (float)D + eps);
+    if (on) {
+        if (write_back) reinterpret_cast<float4*>(x + r * D)[i] = s;
+        const float4 wv = load4<W>(w + 4 * i);
+        store4<O>(out + (size_t)o * D + 4 * i,
+                  make_float4((s.x * rinv) * wv.x, (s.y * rinv) * wv.y, (s.z * rinv) * wv.z, (s.w * rinv) * wv.w));
+    }
+}
+
 template <typename A, typename W>
 static int launch_rmsnorm_o(float* x, const void* delta, const void* w, void* out, int out_dtype,
                             const int* rows, int n, int D, float eps, int write_back,
                             cudaStream_t stream) {
+    if (D % 4 == 0 && D <= 4096) {
+        const int threads = ((D / 4) + 31) / 32 * 32;
+        if (out_dtype == AIE_F32)
+            add_rmsnorm_row_kernel<A, W, float><<<n, threads, 0, stream>>>(x, (const A*)delta, (const W*)w, (float*)out, rows, D, eps, write_back);
+        else if (out_dtype == AIE_BF16)
+            add_rmsnorm_row_kernel<A, W, bf16><<<n, threads, 0, stream>>>(x, (const A*)delta, (const W*)w, (bf16*)out, rows, D, eps, write_back);
+        else
+            return AIE_BAD_ARG;
+        AIE_LAUNCH_CHECK();
+    }
     const size_t smem = (size_t)(D + 32) * sizeof(float);
     if (smem > 200 * 1024) return AIE_UNSUPPORTED;
     const int threads = D >= 1024 ? 512 : 256;

@@ -124,19 +124,68 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, rows: Optional[torch.Tensor] = No
     return out
 
 
+def _row_groups(rows: int, K: int, swiglu: bool) -> int:
+    """Weight-row groups per CTA of the small-M kernel: as many as still leave two
+    CTAs for each of the 148 SMs (the rest of its 8 warps split K)."""
+    for rg in (8, 4, 2, 1):
+        if swiglu and rg < 2:
+            break
+        per_cta = (8 if swiglu else 16) * rg
+        if K % (32 * (8 // rg)) == 0 and (rows + per_cta - 1) // per_cta >= 2 * 148:
+            return rg
+    for rg in ((2, 4, 8) if swiglu else (1, 2, 4, 8)):
+        if K % (32 * (8 // rg)) == 0:
+            return rg
+    return 0
+
+
+def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False):
+    """bfloat16 x . w^T for at most 16 tokens with the weight-streaming kernel, or
+    None when the kernel does not take the sizes.  swiglu: w is the fused [2F, K]
+    gate/up matrix and the result is silu(gate) * up, [M, F]."""
+    M, K = x.shape
+    N = w.shape[0]
+    if M > 16 or N % (32 if swiglu else 16) or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return None
+    rg = _row_groups(N // 2 if swiglu else N, K, swiglu)
+    if rg == 0:
+        return None
+    _dev(x, w)
+    out = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
+    lib = library("gemm_bf16.cu")
+    check(lib.aie_gemm_small_m(_p(x), _p(w), _p(out), c_int(dtype_code(out)), c_int(M), c_int(N), c_int(K),
+                               c_int(out.stride(0)), c_int(1 if swiglu else 0), c_int(rg), _stream()),
+          "gemm_small_m")
+    return out
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """x . w^T.  float32 activations (or a weight stored in 32-bit) take the true
-    float32 kernel; bfloat16 x bfloat16 takes the library matrix product, as the
+    float32 kernel.  bfloat16 x bfloat16: up to 16 tokens take the weight-streaming
+    kernel of this package; more tokens take the library matrix product, as the
     reference's engine does for its products
     (crates/ai-engine-candle/src/paged/transformer.rs:153-155)."""
     out_dtype = out_dtype or x.dtype
     if x.dtype == torch.float32 or w.dtype == torch.float32:
         y = gemm_f32(cast(x, torch.float32), w)
         return cast(y, out_dtype)
+    y = gemm_small_m(x, w, out_dtype)
+    if y is not None:
+        return y
     _dev(x, w)
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     return torch.mm(x, w.t())
+
+
+def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor) -> torch.Tensor:
+    """silu(x . gate^T) * (x . up^T) for the fused [2F, K] gate/up weight; [T, F] in
+    x's dtype.  Few bfloat16 tokens: one kernel with the activation in its epilogue."""
+    if x.dtype == torch.bfloat16 and w_gu.dtype == torch.bfloat16:
+        y = gemm_small_m(x, w_gu, x.dtype, swiglu=True)
+        if y is not None:
+            return y
+    return silu_mul(linear(x, w_gu, x.dtype))
 
 
 # ---------------------------------------------------------------------------

@@ -71,4 +71,4 @@ class GQAAttention(Mixer):
                               write=cache.writes)
         a = ops.paged_attention(q, cache.k_pages, cache.v_pages, ctx, cache.block_table,
                                 self.scale, self.window)
-        return ops.linear(a.view(a.shape[0], self.H * self.d), self.w_o, self.env.dtype)
+        return ops.linear(a.view(a.shape[0], self.H * self.d), self.w_o, torch.float32)

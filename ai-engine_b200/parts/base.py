@@ -68,7 +68,8 @@ class Part:
 
 class Mixer(Part):
     """Mixes information across a request's tokens.  forward(h [T, hidden],
-    ctx, cache) -> [T, hidden] in the compute dtype.  A part whose forward reads
+    ctx, cache) -> [T, hidden], float32 or the compute dtype (the next norm adds it to
+    the float32 residual stream).  A part whose forward reads
     the step's host-side arrays (ctx.h_*) sets `host_side = True`; a model with such
     a part is never replayed from a captured CUDA graph."""
 
@@ -85,7 +86,7 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    """Token-local: forward(h [T, hidden], ctx) -> [T, hidden]."""
+    """Token-local: forward(h [T, hidden], ctx) -> [T, hidden], float32 or the compute dtype."""
 
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
         raise NotImplementedError

@@ -36,6 +36,5 @@ class SwiGLU(FeedForward):
         return sum(w.numel() * w.element_size() for w in (self.w_gu, self.w_down))
 
     def forward(self, h, ctx):
-        gu = ops.linear(h, self.w_gu, self.env.dtype)
-        a = ops.silu_mul(gu)
-        return ops.linear(a, self.w_down, self.env.dtype)
+        a = ops.linear_swiglu(h, self.w_gu)
+        return ops.linear(a, self.w_down, torch.float32)     # the branch joins the residual in float32

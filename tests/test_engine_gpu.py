@@ -217,6 +217,8 @@ def test_decode_steps_replayed_from_a_graph_match_eager_steps(tmp_path):
         outs[graphs] = torch.stack(got)
         if graphs:
             assert runner.graphs_captured == 1 and runner.graph_launches > 0
-    assert torch.equal(outs[True], outs[False])
+    # the replayed step cuts the keys into as many parts as its layout's widest request could
+    # need, the eager step into as many as this step needs: equal up to bfloat16 rounding
+    assert (outs[True] - outs[False]).abs().max() <= 1e-2
     ref = plain_logits(d, ids[1][:40], torch.float32)
     assert np.abs(outs[True][:, 1].numpy() - ref[20:40]).max() <= TOL_BF16

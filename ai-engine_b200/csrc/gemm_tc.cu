@@ -1,0 +1,315 @@
+// bfloat16 matrix product on the fifth-generation tensor cores:
+//     C[T, N] = X[T, K] . W[N, K]^T          (weights as stored: [out, in])
+// computed as D^T = W . X^T so that the weight matrix is the 128-row operand of
+// tcgen05.mma and the tokens are its N dimension (16 .. 256).  Few tokens (decode)
+// make this a pure weight stream, many tokens (prompts) a compute-bound product;
+// the kernel is the same, only the token tile BN differs.
+//
+// One CTA owns one 128-row tile of W, one tile of BN tokens and one part of K
+// (split-K across gridDim.z when the grid would otherwise not fill the machine).
+// Warp roles:
+//   warp 0 (one lane)  producer: TMA (cp.async.bulk.tensor.2d) loads of the W tile
+//                      [128 x 64] and the X tile [BN x 64] of each K block into a
+//                      ring of shared-memory stages, 128-byte swizzled, completion
+//                      counted in bytes on the stage's "full" mbarrier;
+//   warp 1 (one lane)  issues four tcgen05.mma (K = 16 each) per stage from shared-
+//                      memory descriptors into the float32 accumulator in tensor
+//                      memory, then tcgen05.commit, which releases the stage ("empty"
+//                      mbarrier) when those products have read it; warp 1 also owns
+//                      the tensor-memory allocation;
+//   warps 2-5          epilogue: after the last commit, tcgen05.ld their quarter of
+//                      the accumulator (lane = weight row, column = token) and store
+//                      C[token][row] (32 lanes write 32 consecutive rows of a token).
+// Every wait is bounded: after WAIT_LIMIT polls a thread raises the CTA's abort
+// flag and the device error word, the other roles leave their loops, copies in
+// flight are waited for (bounded), tensor memory is freed and the CTA returns.
+// Split-K parts are written as float32 to a workspace and summed in a fixed
+// order by a second kernel (so results do not depend on timing).
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define TC_BM 128           // weight rows per tile (the MMA's M)
+#define TC_BK 64            // K elements per stage (128 bytes: one swizzle row)
+#define TC_THREADS 192
+#define TC_WAIT_LIMIT (1u << 24)
+
+__device__ __forceinline__ unsigned tc_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(tc_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(tc_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                 : "=r"(ok) : "r"(tc_smem(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when it gave up or when another role has aborted.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag,
+                                          unsigned* err) {
+    for (unsigned i = 0; i < TC_WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicOr(err, AIE_DEV_WAIT_TIMEOUT);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, unsigned long long* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(tc_smem(dst)), "l"(map), "r"(tc_smem(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle, groups of
+// 8 rows 1024 bytes apart (what the TMA load with SWIZZLE_128B writes).
+__device__ __forceinline__ unsigned long long umma_desc(const void* tile) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((tc_smem(tile) >> 4) & 0x3FFFu);   // start address / 16
+    d |= (unsigned long long)1 << 16;                             // leading byte offset / 16 (unused under swizzle)
+    d |= (unsigned long long)(1024 >> 4) << 32;                   // stride byte offset / 16: next group of 8 rows
+    d |= (unsigned long long)1 << 46;                             // descriptor version of sm_100
+    d |= (unsigned long long)2 << 61;                             // SWIZZLE_128B
+    return d;
+}
+// bf16 x bf16 -> f32, both operands K-major, M = 128, N = n
+__device__ __forceinline__ unsigned umma_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc,
+                                     unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}\n"
+                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc_smem(bar)) : "memory");
+}
+
+template <typename OT> __device__ __forceinline__ void tc_store(OT* p, float v);
+template <> __device__ __forceinline__ void tc_store<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void tc_store<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <int BN> struct TcSmem {
+    static constexpr int stage_bytes = TC_BM * TC_BK * 2 + BN * TC_BK * 2;
+    static constexpr int stages = BN <= 32 ? 8 : (BN <= 64 ? 6 : (BN <= 128 ? 5 : 4));
+    static constexpr int bytes = stages * stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int BN, typename OT>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               OT* __restrict__ C, float* __restrict__ ws, int T, int N, int K, int ldc,
+               int kb_per_split, unsigned* err) {
+    constexpr int STAGES = TcSmem<BN>::stages;
+    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    extern __shared__ unsigned char tc_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(((size_t)tc_raw + 1023) & ~(size_t)1023);
+    unsigned long long* full = reinterpret_cast<unsigned long long*>(base + STAGES * TcSmem<BN>::stage_bytes);
+    unsigned long long* empty = full + STAGES;
+    unsigned long long* accum = empty + STAGES;
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(accum + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * TC_BM, t0 = blockIdx.y * BN;
+    const int kb_total = (K + TC_BK - 1) / TC_BK;
+    const int kb_begin = blockIdx.z * kb_per_split;
+    const int kb_end = min(kb_begin + kb_per_split, kb_total);
+    const int nkb = kb_end - kb_begin;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(accum, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {   // tensor memory for the accumulator: 128 lanes x TMEM_COLS columns of float32
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(tmem_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_d = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0 && nkb > 0) {
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                const unsigned ph = (i / STAGES) & 1;
+                if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, err)) break;
+                unsigned char* st = base + s * TcSmem<BN>::stage_bytes;
+                mbar_expect_tx(&full[s], TcSmem<BN>::stage_bytes);
+                const int k = (kb_begin + i) * TC_BK;
+                tma_load_2d(st, &map_w, &full[s], k, n0);
+                tma_load_2d(st + TC_BM * TC_BK * 2, &map_x, &full[s], k, t0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && nkb > 0) {
+            const unsigned idesc = umma_idesc(BN);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                const int s = i % STAGES;
+                const unsigned ph = (i / STAGES) & 1;
+                ok = mbar_wait(&full[s], ph, abort_flag, err);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                unsigned char* st = base + s * TcSmem<BN>::stage_bytes;
+                const unsigned long long da = umma_desc(st), db = umma_desc(st + TC_BM * TC_BK * 2);
+#pragma unroll
+                for (int j = 0; j < TC_BK / 16; ++j)     // 32 bytes further along K inside the swizzled row
+                    umma(tmem_d, da + 2 * j, db + 2 * j, idesc, (i > 0 || j > 0) ? 1u : 0u);
+                umma_commit(&empty[s]);                  // the stage is free once these products have read it
+            }
+            if (ok) umma_commit(accum);                  // the accumulator is complete
+        }
+    } else {
+        // epilogue: warps 2..5 read lanes 32 * (warp % 4) .. + 31 of tensor memory
+        const int quarter = warp & 3;
+        bool ok = nkb > 0;
+        if (ok) ok = mbar_wait(accum, 0, abort_flag, err);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;      // the whole warp follows lane 0's verdict
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const int n = n0 + quarter * 32 + lane;
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+            unsigned v[16];
+            if (ok) {
+                const unsigned taddr = tmem_d + ((unsigned)(quarter * 32) << 16) + (unsigned)c0;
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+                               "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+                               "=r"(v[14]), "=r"(v[15])
+                             : "r"(taddr));
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = 0u;      // a part without K blocks adds nothing
+            }
+            if (n < N && (ok || nkb <= 0)) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int t = t0 + c0 + j;
+                    if (t >= T) break;
+                    const float f = __uint_as_float(v[j]);
+                    if (gridDim.z == 1) tc_store<OT>(C + (size_t)t * ldc + n, f);
+                    else ws[((size_t)blockIdx.z * T + t) * N + n] = f;
+                }
+            }
+        }
+    }
+
+    // leave together; on an abort, give copies in flight a bounded time to land first
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (*abort_flag && tid == 0) {
+        for (int s = 0; s < STAGES; ++s)
+            for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(&full[s], 0) && !mbar_try_wait(&full[s], 1); ++i) {}
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_d), "r"(TMEM_COLS));
+    }
+}
+
+// C[t, n] = sum over parts, in order
+template <typename OT>
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, OT* __restrict__ C, int T, int N, int ldc, int parts) {
+    const size_t total = (size_t)T * N;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float v = 0.f;
+        for (int p = 0; p < parts; ++p) v += ws[(size_t)p * total + i];
+        tc_store<OT>(C + (i / N) * ldc + (i % N), v);
+    }
+}
+
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// a [rows, K] bf16 row-major matrix, tiles of [box_rows, 64], 128-byte swizzle, zeros outside
+static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return AIE_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : AIE_BAD_ARG;
+}
+
+template <int BN, typename OT>
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, float* ws, int T, int N, int K, int ldc,
+                     int splits, unsigned* err, cudaStream_t st) {
+    const int kb_total = (K + TC_BK - 1) / TC_BK;
+    const int kbps = (kb_total + splits - 1) / splits;
+    dim3 grid((N + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, splits);
+    auto kern = gemm_tc_kernel<BN, OT>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN>::bytes);
+    kern<<<grid, TC_THREADS, TcSmem<BN>::bytes, st>>>(mw, mx, (OT*)C, ws, T, N, K, ldc, kbps, err);
+    if (splits > 1) {
+        const size_t total = (size_t)T * N;
+        int blocks = (int)((total + 255) / 256);
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        splitk_reduce_kernel<OT><<<blocks, 256, 0, st>>>(ws, (OT*)C, T, N, ldc, splits);
+    }
+    return 0;
+}
+
+// bn: token tile (16, 32, 64, 128, 256).  splits > 1 needs ws of splits * T * N floats.
+// Requires K % 8 == 0 (16-byte rows) and 16-byte aligned X and W.
+extern "C" int aie_gemm_tc(const void* X, const void* W, void* C, int out_dtype, int T, int N, int K, int ldc,
+                           int bn, int splits, float* ws, unsigned* err, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || ((size_t)X & 15) || ((size_t)W & 15)) return AIE_UNSUPPORTED;
+    if (splits < 1 || (splits > 1 && !ws)) return AIE_BAD_ARG;
+    if (out_dtype != AIE_BF16 && out_dtype != AIE_F32) return AIE_BAD_ARG;
+    if ((T + bn - 1) / bn > 65535 || splits > 65535) return AIE_UNSUPPORTED;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, W, N, K, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mx, X, T, K, bn);
+    if (rc) return rc;
+#define GO(BNV)                                                                                          \
+    rc = out_dtype == AIE_BF16 ? launch_tc<BNV, bf16>(mw, mx, C, ws, T, N, K, ldc, splits, err, stream)  \
+                               : launch_tc<BNV, float>(mw, mx, C, ws, T, N, K, ldc, splits, err, stream)
+    switch (bn) {
+        case 16: GO(16); break;
+        case 32: GO(32); break;
+        case 64: GO(64); break;
+        case 128: GO(128); break;
+        case 256: GO(256); break;
+        default: return AIE_BAD_ARG;
+    }
+#undef GO
+    if (rc) return rc;
+    AIE_LAUNCH_CHECK();
+}

@@ -159,6 +159,43 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swigl
     return out
 
 
+def tc_tile(T: int) -> int:
+    """Token tile of the tcgen05 product: the smallest of 16 .. 256 that holds T, else 256."""
+    for bn in (16, 32, 64, 128, 256):
+        if T <= bn:
+            return bn
+    return 256
+
+
+def tc_splits(T: int, N: int, K: int, bn: int) -> int:
+    """Parts to cut K into so that about two CTAs per SM are in flight (each with its
+    own ring of TMA stages), never fewer than 4 K blocks per part."""
+    tiles = ((N + 127) // 128) * ((T + bn - 1) // bn)
+    kb = (K + 63) // 64
+    want = max(1, (2 * 148) // tiles)
+    return max(1, min(want, kb // 4 if kb >= 4 else 1, 32))
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, err: torch.Tensor,
+            bn: Optional[int] = None, splits: Optional[int] = None):
+    """bfloat16 x . w^T on tcgen05 tensor cores fed by TMA; None when the sizes are not
+    taken (K not a multiple of 8)."""
+    T, K = x.shape
+    N = w.shape[0]
+    if K % 8 or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return None
+    _dev(x, w, err)
+    bn = bn or tc_tile(T)
+    splits = splits or tc_splits(T, N, K, bn)
+    out = torch.empty((T, N), dtype=out_dtype, device=x.device)
+    ws = torch.empty((splits, T, N), dtype=torch.float32, device=x.device) if splits > 1 else None
+    lib = library("gemm_tc.cu")
+    check(lib.aie_gemm_tc(_p(x), _p(w), _p(out), c_int(dtype_code(out)), c_int(T), c_int(N), c_int(K),
+                          c_int(out.stride(0)), c_int(bn), c_int(splits), _p(ws), _p(err), _stream()),
+          "gemm_tc")
+    return out
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """x . w^T.  float32 activations (or a weight stored in 32-bit) take the true
     float32 kernel.  bfloat16 x bfloat16: up to 16 tokens take the weight-streaming
@@ -250,7 +287,7 @@ def decode_splits(n_dec: int, kv_heads: int, group: int, max_keys: int, bt_width
     the machine (two CTAs fit on each of the 148 SMs), with parts of at least 128
     keys, and no part spanning more block-table entries than a CTA keeps."""
     ctas = n_dec * kv_heads * ((group + 3) // 4)
-    want = max(1, (2 * 148 + ctas - 1) // ctas)
+    want = max(1, (2 * 148) // ctas)          # rounded down: one full wave, no short second one
     s = max(1, min(want, (max_keys + 127) // 128, 64))
     return max(s, (bt_width + 1999) // 2000)
 

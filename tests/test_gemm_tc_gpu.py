@@ -1,0 +1,65 @@
+"""The tcgen05 / TMA matrix product alone against float64, over token counts from 1 to
+thousands, widths that are no multiple of the tile, K with a ragged last block, every
+token tile, and split K."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def run(T, N, K, out_dtype=torch.float32, bn=None, splits=None, seed=0):
+    from ai_engine_b200.kernels import ops
+
+    torch.manual_seed(seed)
+    x = torch.randn(T, K, device=DEV).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = ops.gemm_tc(x, w, out_dtype, err, bn=bn, splits=splits)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0, "a bounded wait ran out"
+    want = x.double() @ w.double().T
+    tol = (2e-5 if out_dtype == torch.float32 else 1e-2) * max(1.0, float(want.abs().max())) * max(1.0, (K / 4096) ** 0.5)
+    bad = (out.double() - want).abs()
+    assert bad.max() <= tol, (T, N, K, bn, splits, float(bad.max()), tol, [int(i) for i in (bad > tol).nonzero()[0]])
+    return out
+
+
+def test_one_tile_one_block():
+    run(16, 128, 64, bn=16, splits=1)
+
+
+@pytest.mark.parametrize("T,N,K", [(8, 128, 64), (1, 256, 128), (16, 384, 512), (8, 4096, 4096), (8, 6144, 4096),
+                                   (3, 100, 200), (5, 1000, 72), (16, 128256, 256), (8, 4096, 14336)])
+def test_few_tokens(T, N, K):
+    run(T, N, K)
+    run(T, N, K, torch.bfloat16)
+
+
+@pytest.mark.parametrize("bn", [16, 32, 64, 128, 256])
+def test_every_token_tile(bn):
+    run(bn, 512, 1024, bn=bn, splits=1)
+    run(bn + 7, 300, 328, bn=bn, splits=1, seed=1)      # two token tiles, ragged N and K
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 7])
+def test_split_k(splits):
+    run(8, 256, 2048, splits=splits)
+    run(40, 200, 1032, bn=64, splits=splits, out_dtype=torch.bfloat16)
+
+
+@pytest.mark.parametrize("T,N,K", [(300, 4096, 4096), (2048, 6144, 4096), (1000, 4096, 14336), (2048, 28672, 4096)])
+def test_many_tokens(T, N, K):
+    run(T, N, K, torch.bfloat16)
+
+
+def test_a_token_does_not_depend_on_the_batch():
+    from ai_engine_b200.kernels import ops
+
+    torch.manual_seed(3)
+    x = torch.randn(16, 4096, device=DEV).bfloat16()
+    w = (torch.randn(512, 4096, device=DEV) * 0.05).bfloat16()
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    full = ops.gemm_tc(x, w, torch.float32, err, bn=16, splits=4)
+    one = ops.gemm_tc(x[5:6].contiguous(), w, torch.float32, err, bn=16, splits=4)
+    assert torch.equal(full[5], one[0])

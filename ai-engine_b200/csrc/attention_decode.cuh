@@ -41,6 +41,8 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     __shared__ int ok_s[DEC_WARPS][NST][DEC_TILE];
     __shared__ float mrg_m[DEC_WARPS][GC], mrg_l[DEC_WARPS][GC];
 
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int s = blockIdx.x, di = blockIdx.z;
     const int gchunks = (G + GC - 1) / GC;
@@ -257,6 +259,8 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
 __global__ void decode_reduce_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                      bf16* __restrict__ out, const int* __restrict__ dec_tokens,
                                      int H, int D, int S) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int di = blockIdx.x, h = blockIdx.y;
     const int t = dec_tokens[di];
     const size_t base = ((size_t)di * H + h) * S;
@@ -285,8 +289,8 @@ static int launch_decode(int GC, dim3 grid, cudaStream_t st, const bf16* q, cons
     do {                                                                                                          \
         auto kern = paged_decode_kernel<D, GCV, NST>;                                                             \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                       \
-        kern<<<grid, DEC_WARPS * 32, smem, st>>>(q, kp, vp, out, po, pl, dt, pos, tr, bt, btw, np, P, H, K, G,  \
-                                                 window, scale, S, err);                                          \
+        launch_pdl(kern, grid, dim3(DEC_WARPS * 32), smem, st, q, kp, vp, out, po, pl, dt, pos, tr, bt, btw, np, \
+                   P, H, K, G, window, scale, S, err);                                                            \
     } while (0)
     switch (GC) {
         case 1: GO(1); break;

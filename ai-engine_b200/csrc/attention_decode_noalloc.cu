@@ -65,7 +65,7 @@ extern "C" int aie_paged_attention_decode_noalloc(const void* q, const void* k_p
         // every (token, head, part) slot of the scratch that this reduce reads was
         // written by the launch above, so stale contents of earlier calls are never seen
         dim3 rg(n_dec, H);
-        decode_reduce_kernel<<<rg, d < 128 ? 64 : 128, 0, stream>>>(part_o, part_lse, (bf16*)out, dec_tokens, H, d, S);
+        launch_pdl(decode_reduce_kernel, rg, dim3(d < 128 ? 64 : 128), 0, stream, (const float*)part_o, (const float*)part_lse, (bf16*)out, dec_tokens, H, d, S);
     }
     return (int)cudaGetLastError();
 }

@@ -48,7 +48,7 @@ extern "C" int aie_paged_attention_decode(const void* q, const void* k_pages, co
     if (rc) return rc;
     if (S > 1) {
         dim3 rg(n_dec, H);
-        decode_reduce_kernel<<<rg, d < 128 ? 64 : 128, 0, stream>>>(part_o, part_lse, (bf16*)out, dec_tokens, H, d, S);
+        launch_pdl(decode_reduce_kernel, rg, dim3(d < 128 ? 64 : 128), 0, stream, (const float*)part_o, (const float*)part_lse, (bf16*)out, dec_tokens, H, d, S);
     }
     AIE_LAUNCH_CHECK();
 }

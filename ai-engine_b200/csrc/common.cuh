@@ -86,6 +86,31 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return r;
 }
 
+// Programmatic dependent launch: a kernel launched with launch_pdl may become resident
+// while the kernel before it in the stream is still running.  It must call pdl_wait()
+// before it reads anything an earlier kernel wrote and before it writes anything an
+// earlier kernel may still read; pdl_launch_dependents() lets the kernel after it start
+// becoming resident.  Work placed before pdl_wait() (setting up barriers, fetching
+// weights) overlaps the tail of the previous kernel.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 #define AIE_LAUNCH_CHECK()                                   \
     do {                                                     \
         cudaError_t e__ = cudaGetLastError();                \

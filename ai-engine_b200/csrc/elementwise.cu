@@ -23,6 +23,8 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const W* __rest
 // bf16 table, D a multiple of 8: 16-byte loads, two float4 stores per thread
 __global__ void embed_gather_vec_kernel(const int* __restrict__ ids, const bf16* __restrict__ table,
                                         float* __restrict__ x, int D, int vocab, unsigned* err) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < vocab;
@@ -48,7 +50,7 @@ extern "C" int aie_embed_gather(const int* ids, const void* table, int table_dty
     if (table_dtype == AIE_F32)
         embed_gather_kernel<float><<<T, 256, 0, stream>>>(ids, (const float*)table, x, D, vocab, err);
     else if (table_dtype == AIE_BF16 && D % 8 == 0)
-        embed_gather_vec_kernel<<<T, D >= 4096 ? 512 : 128, 0, stream>>>(ids, (const bf16*)table, x, D, vocab, err);
+        launch_pdl(embed_gather_vec_kernel, dim3(T), dim3(D >= 4096 ? 512 : 128), 0, stream, ids, (const bf16*)table, x, D, vocab, err);
     else if (table_dtype == AIE_BF16)
         embed_gather_kernel<bf16><<<T, 256, 0, stream>>>(ids, (const bf16*)table, x, D, vocab, err);
     else
@@ -96,6 +98,8 @@ __global__ void __launch_bounds__(1024)
 add_rmsnorm_row_kernel(float* __restrict__ x, const A* __restrict__ delta, const W* __restrict__ w,
                        O* __restrict__ out, const int* __restrict__ rows, int D, float eps, int write_back) {
     __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int o = blockIdx.x;
     const size_t r = rows ? (size_t)rows[o] : (size_t)o;
     const int i = threadIdx.x;
@@ -132,9 +136,9 @@ static int launch_rmsnorm_o(float* x, const void* delta, const void* w, void* ou
     if (D % 4 == 0 && D <= 4096) {
         const int threads = ((D / 4) + 31) / 32 * 32;
         if (out_dtype == AIE_F32)
-            add_rmsnorm_row_kernel<A, W, float><<<n, threads, 0, stream>>>(x, (const A*)delta, (const W*)w, (float*)out, rows, D, eps, write_back);
+            launch_pdl(add_rmsnorm_row_kernel<A, W, float>, dim3(n), dim3(threads), 0, stream, x, (const A*)delta, (const W*)w, (float*)out, rows, D, eps, write_back);
         else if (out_dtype == AIE_BF16)
-            add_rmsnorm_row_kernel<A, W, bf16><<<n, threads, 0, stream>>>(x, (const A*)delta, (const W*)w, (bf16*)out, rows, D, eps, write_back);
+            launch_pdl(add_rmsnorm_row_kernel<A, W, bf16>, dim3(n), dim3(threads), 0, stream, x, (const A*)delta, (const W*)w, (bf16*)out, rows, D, eps, write_back);
         else
             return AIE_BAD_ARG;
         AIE_LAUNCH_CHECK();
@@ -170,31 +174,37 @@ extern "C" int aie_add_rmsnorm(float* x, const void* delta, int delta_dtype, con
 }
 
 // ---------------------------------------------------------------------------
-// a[t, f] = silu(gu[t, f]) * gu[t, F + f]   (crates/ai-engine-runtime/src/arch/ffn.rs:50-54)
-// silu(z) = z * sigmoid(z), in float32.
+// a[t, f] = silu(gate) * up   (crates/ai-engine-runtime/src/arch/ffn.rs:50-54), silu(z) = z * sigmoid(z)
+// in float32.  block == 0: gu[t] = [gate (F) | up (F)].  block > 0: gu[t] is in groups of
+// 2 * block columns, `block` gate columns followed by their `block` up columns.
 // ---------------------------------------------------------------------------
 template <typename A>
-__global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ a, int F, size_t total) {
+__global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ a, int F, int block, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < total; i += stride) {
         const size_t t = i / F, f = i % F;
-        const float g = to_f32<A>(gu[t * 2 * F + f]);
-        const float u = to_f32<A>(gu[t * 2 * F + F + f]);
+        const size_t gc = block ? (f / block) * 2 * block + f % block : f;
+        const size_t uc = block ? gc + block : F + f;
+        const float g = to_f32<A>(gu[t * 2 * F + gc]);
+        const float u = to_f32<A>(gu[t * 2 * F + uc]);
         const float s = g * (1.0f / (1.0f + expf(-g)));
         a[i] = from_f32<A>(s * u);
     }
 }
 
-extern "C" int aie_silu_mul(const void* gu, void* a, int dtype, int T, int F, cudaStream_t stream) {
+extern "C" int aie_silu_mul(const void* gu, void* a, int dtype, int T, int F, int block, cudaStream_t stream) {
+    if (block < 0 || (block && F % block)) return AIE_BAD_ARG;
     if (T <= 0) return 0;
     const size_t total = (size_t)T * F;
     int blocks = (int)((total + 255) / 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == AIE_F32)
-        silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)a, F, total);
+        launch_pdl(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)a, F, block, total);
     else if (dtype == AIE_BF16)
-        silu_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)a, F, total);
+        launch_pdl(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gu, (bf16*)a, F, block, total);
     else
         return AIE_BAD_ARG;
     AIE_LAUNCH_CHECK();

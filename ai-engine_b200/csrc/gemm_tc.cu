@@ -20,11 +20,19 @@
 //   warps 2-5          epilogue: after the last commit, tcgen05.ld their quarter of
 //                      the accumulator (lane = weight row, column = token) and store
 //                      C[token][row] (32 lanes write 32 consecutive rows of a token).
+// Split K: the CTAs that share an output tile form a thread-block cluster along z.
+// Each stores its float32 partial tile in its own shared memory; after a cluster
+// barrier the CTA of rank 0 adds the tiles through distributed shared memory in rank
+// order (so the sum does not depend on timing), applies the epilogue and stores.
+// Epilogues: plain store (bf16 or float32), or SwiGLU on a weight whose 128-row tiles
+// hold 64 gate rows followed by their 64 up rows: a[t, f] = silu(g) * u in float32
+// (crates/ai-engine-runtime/src/arch/ffn.rs:50-54).
+// The kernel is launched as a programmatic dependent: barriers, tensor memory and the
+// first weight tiles of the ring are set up and requested before griddepcontrol.wait,
+// while the previous kernel is still finishing; only the token tiles wait for it.
 // Every wait is bounded: after WAIT_LIMIT polls a thread raises the CTA's abort
 // flag and the device error word, the other roles leave their loops, copies in
 // flight are waited for (bounded), tensor memory is freed and the CTA returns.
-// Split-K parts are written as float32 to a workspace and summed in a fixed
-// order by a second kernel (so results do not depend on timing).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -97,15 +105,37 @@ template <> __device__ __forceinline__ void tc_store<bf16>(bf16* p, float v) { *
 
 template <int BN> struct TcSmem {
     static constexpr int stage_bytes = TC_BM * TC_BK * 2 + BN * TC_BK * 2;
-    static constexpr int stages = BN <= 32 ? 8 : (BN <= 64 ? 6 : (BN <= 128 ? 5 : 4));
+    // few tokens: short rings so that three CTAs share an SM and hide each other's start and end;
+    // many tokens: one CTA per SM with as deep a ring as fits
+    static constexpr int stages = BN <= 32 ? 4 : (BN <= 64 ? 4 : (BN <= 128 ? 6 : 4));
     static constexpr int bytes = stages * stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-template <int BN, typename OT>
+#define TC_EPI_STORE 0
+#define TC_EPI_SWIGLU 1
+
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// the float at `addr` (a shared-memory address of this CTA) in the CTA of rank `rank`
+__device__ __forceinline__ float ld_peer(unsigned addr, unsigned rank) {
+    unsigned peer;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(peer) : "r"(addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(peer) : "memory");
+    return v;
+}
+
+template <int BN, int EPI, typename OT>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               OT* __restrict__ C, float* __restrict__ ws, int T, int N, int K, int ldc,
-               int kb_per_split, unsigned* err) {
+               OT* __restrict__ C, int T, int N, int K, int ldc, int kb_per_split, unsigned* err) {
     constexpr int STAGES = TcSmem<BN>::stages;
     constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
     extern __shared__ unsigned char tc_raw[];
@@ -115,13 +145,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     unsigned long long* accum = empty + STAGES;
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(accum + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* tile_s = reinterpret_cast<float*>(base);      // [BN][128] partial tile, after the ring is idle
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * TC_BM, t0 = blockIdx.y * BN;
+    const int parts = gridDim.z;                          // = cluster size along z
     const int kb_total = (K + TC_BK - 1) / TC_BK;
     const int kb_begin = blockIdx.z * kb_per_split;
     const int kb_end = min(kb_begin + kb_per_split, kb_total);
-    const int nkb = kb_end - kb_begin;
+    const int nkb = max(kb_end - kb_begin, 0);
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -141,10 +173,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem_d = *tmem_slot;
+    pdl_launch_dependents();
 
     if (warp == 0) {
-        if (lane == 0 && nkb > 0) {
-            for (int i = 0; i < nkb; ++i) {
+        if (lane == 0) {
+            // weights do not depend on the previous kernel: request the first ring of W tiles now
+            const int pre = min(nkb, STAGES);
+            for (int i = 0; i < pre; ++i) {
+                mbar_expect_tx(&full[i], TcSmem<BN>::stage_bytes);
+                tma_load_2d(base + i * TcSmem<BN>::stage_bytes, &map_w, &full[i], (kb_begin + i) * TC_BK, n0);
+            }
+            pdl_wait();        // the tokens are the previous kernel's output
+            for (int i = 0; i < pre; ++i)
+                tma_load_2d(base + i * TcSmem<BN>::stage_bytes + TC_BM * TC_BK * 2, &map_x, &full[i],
+                            (kb_begin + i) * TC_BK, t0);
+            for (int i = pre; i < nkb; ++i) {
                 const int s = i % STAGES;
                 const unsigned ph = (i / STAGES) & 1;
                 if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, err)) break;
@@ -159,7 +202,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (lane == 0 && nkb > 0) {
             const unsigned idesc = umma_idesc(BN);
             bool ok = true;
-            for (int i = 0; i < nkb && ok; ++i) {
+            for (int i = 0; i < nkb; ++i) {
                 const int s = i % STAGES;
                 const unsigned ph = (i / STAGES) & 1;
                 ok = mbar_wait(&full[s], ph, abort_flag, err);
@@ -175,13 +218,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (ok) umma_commit(accum);                  // the accumulator is complete
         }
     } else {
-        // epilogue: warps 2..5 read lanes 32 * (warp % 4) .. + 31 of tensor memory
+        // epilogue warps 2..5 read lanes 32 * (warp % 4) .. + 31 of tensor memory: lane = weight row
         const int quarter = warp & 3;
         bool ok = nkb > 0;
         if (ok) ok = mbar_wait(accum, 0, abort_flag, err);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;      // the whole warp follows lane 0's verdict
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const int n = n0 + quarter * 32 + lane;
+        pdl_wait();             // nothing is stored before the previous kernel is done with its buffers
+        const int r = quarter * 32 + lane;               // row of the tile
+        const bool direct = parts == 1 && EPI == TC_EPI_STORE;
 #pragma unroll
         for (int c0 = 0; c0 < BN; c0 += 16) {
             unsigned v[16];
@@ -195,19 +240,55 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
             } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] = 0u;      // a part without K blocks adds nothing
+                for (int j = 0; j < 16; ++j) v[j] = 0u;      // a part without K blocks (or an abort) adds nothing
             }
-            if (n < N && (ok || nkb <= 0)) {
+            if (direct) {
+                if (n0 + r < N && ok) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int t = t0 + c0 + j;
-                    if (t >= T) break;
-                    const float f = __uint_as_float(v[j]);
-                    if (gridDim.z == 1) tc_store<OT>(C + (size_t)t * ldc + n, f);
-                    else ws[((size_t)blockIdx.z * T + t) * N + n] = f;
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t0 + c0 + j;
+                        if (t >= T) break;
+                        tc_store<OT>(C + (size_t)t * ldc + n0 + r, __uint_as_float(v[j]));
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) tile_s[(c0 + j) * TC_BM + r] = __uint_as_float(v[j]);
+            }
+        }
+    }
+
+    if (parts > 1 || EPI != TC_EPI_STORE) {
+        // join the parts: every CTA of the cluster has its tile in shared memory
+        __syncwarp();
+        if (parts > 1) cluster_sync_all(); else __syncthreads();
+        if (cluster_rank() == 0 && warp >= 2 && !*abort_flag) {
+            const int e = tid - 64;                        // 0 .. 127
+            const unsigned tile_addr = tc_smem(tile_s);
+            if (EPI == TC_EPI_STORE) {
+                for (int idx = e; idx < BN * TC_BM; idx += 128) {
+                    const int tt = idx / TC_BM, r = idx % TC_BM;
+                    float acc = tile_s[idx];
+                    for (int p = 1; p < parts; ++p) acc += ld_peer(tile_addr + idx * 4, p);
+                    if (t0 + tt < T && n0 + r < N) tc_store<OT>(C + (size_t)(t0 + tt) * ldc + n0 + r, acc);
+                }
+            } else {
+                // rows 0..63 of the tile are gate rows, rows 64..127 their up rows; output column f
+                const int f0 = blockIdx.x * (TC_BM / 2), F = N / 2;
+                for (int idx = e; idx < BN * (TC_BM / 2); idx += 128) {
+                    const int tt = idx / (TC_BM / 2), j = idx % (TC_BM / 2);
+                    float g = tile_s[tt * TC_BM + j], u = tile_s[tt * TC_BM + 64 + j];
+                    for (int p = 1; p < parts; ++p) {
+                        g += ld_peer(tile_addr + (tt * TC_BM + j) * 4, p);
+                        u += ld_peer(tile_addr + (tt * TC_BM + 64 + j) * 4, p);
+                    }
+                    const float sv = g * (1.0f / (1.0f + expf(-g)));
+                    if (t0 + tt < T && f0 + j < F) tc_store<OT>(C + (size_t)(t0 + tt) * ldc + f0 + j, sv * u);
                 }
             }
         }
+        __syncwarp();
+        if (parts > 1) cluster_sync_all();       // peers keep their tiles until rank 0 has read them
     }
 
     // leave together; on an abort, give copies in flight a bounded time to land first
@@ -219,19 +300,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     __syncthreads();
     if (warp == 1) {
+        __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_d), "r"(TMEM_COLS));
-    }
-}
-
-// C[t, n] = sum over parts, in order
-template <typename OT>
-__global__ void splitk_reduce_kernel(const float* __restrict__ ws, OT* __restrict__ C, int T, int N, int ldc, int parts) {
-    const size_t total = (size_t)T * N;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        float v = 0.f;
-        for (int p = 0; p < parts; ++p) v += ws[(size_t)p * total + i];
-        tc_store<OT>(C + (i / N) * ldc + (i % N), v);
     }
 }
 
@@ -266,41 +337,59 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_
     return r == CUDA_SUCCESS ? 0 : AIE_BAD_ARG;
 }
 
-template <int BN, typename OT>
-static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, float* ws, int T, int N, int K, int ldc,
+template <int BN, int EPI, typename OT>
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, int ldc,
                      int splits, unsigned* err, cudaStream_t st) {
     const int kb_total = (K + TC_BK - 1) / TC_BK;
     const int kbps = (kb_total + splits - 1) / splits;
-    dim3 grid((N + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, splits);
-    auto kern = gemm_tc_kernel<BN, OT>;
+    auto kern = gemm_tc_kernel<BN, EPI, OT>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN>::bytes);
-    kern<<<grid, TC_THREADS, TcSmem<BN>::bytes, st>>>(mw, mx, (OT*)C, ws, T, N, K, ldc, kbps, err);
-    if (splits > 1) {
-        const size_t total = (size_t)T * N;
-        int blocks = (int)((total + 255) / 256);
-        if (blocks > 148 * 8) blocks = 148 * 8;
-        splitk_reduce_kernel<OT><<<blocks, 256, 0, st>>>(ws, (OT*)C, T, N, ldc, splits);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((N + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, splits);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = TcSmem<BN>::bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+    if (splits > 1) {      // the parts of one output tile are one cluster
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = splits;
+        ++na;
     }
-    return 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, mx, (OT*)C, T, N, K, ldc, kbps, err);
+    return (int)e;
 }
 
-// bn: token tile (16, 32, 64, 128, 256).  splits > 1 needs ws of splits * T * N floats.
+// bn: token tile (16, 32, 64, 128, 256).  splits: parts of K, 1 .. 8 (a cluster).
+// swiglu: W is [2F, K] in 128-row tiles of 64 gate rows + their 64 up rows (N = 2F), C is [T, F].
 // Requires K % 8 == 0 (16-byte rows) and 16-byte aligned X and W.
 extern "C" int aie_gemm_tc(const void* X, const void* W, void* C, int out_dtype, int T, int N, int K, int ldc,
-                           int bn, int splits, float* ws, unsigned* err, cudaStream_t stream) {
+                           int bn, int splits, int swiglu, unsigned* err, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ((size_t)X & 15) || ((size_t)W & 15)) return AIE_UNSUPPORTED;
-    if (splits < 1 || (splits > 1 && !ws)) return AIE_BAD_ARG;
+    if (splits < 1 || splits > 8) return AIE_BAD_ARG;
     if (out_dtype != AIE_BF16 && out_dtype != AIE_F32) return AIE_BAD_ARG;
-    if ((T + bn - 1) / bn > 65535 || splits > 65535) return AIE_UNSUPPORTED;
+    if (swiglu && N % 128) return AIE_UNSUPPORTED;
+    if ((T + bn - 1) / bn > 65535) return AIE_UNSUPPORTED;
     CUtensorMap mw, mx;
     int rc = make_map(&mw, W, N, K, TC_BM);
     if (rc) return rc;
     rc = make_map(&mx, X, T, K, bn);
     if (rc) return rc;
-#define GO(BNV)                                                                                          \
-    rc = out_dtype == AIE_BF16 ? launch_tc<BNV, bf16>(mw, mx, C, ws, T, N, K, ldc, splits, err, stream)  \
-                               : launch_tc<BNV, float>(mw, mx, C, ws, T, N, K, ldc, splits, err, stream)
+#define GO(BNV)                                                                                                   \
+    if (swiglu)                                                                                                   \
+        rc = out_dtype == AIE_BF16 ? launch_tc<BNV, TC_EPI_SWIGLU, bf16>(mw, mx, C, T, N, K, ldc, splits, err, stream)  \
+                                   : launch_tc<BNV, TC_EPI_SWIGLU, float>(mw, mx, C, T, N, K, ldc, splits, err, stream); \
+    else                                                                                                          \
+        rc = out_dtype == AIE_BF16 ? launch_tc<BNV, TC_EPI_STORE, bf16>(mw, mx, C, T, N, K, ldc, splits, err, stream)   \
+                                   : launch_tc<BNV, TC_EPI_STORE, float>(mw, mx, C, T, N, K, ldc, splits, err, stream)
     switch (bn) {
         case 16: GO(16); break;
         case 32: GO(32); break;
@@ -310,6 +399,5 @@ extern "C" int aie_gemm_tc(const void* X, const void* W, void* C, int out_dtype,
         default: return AIE_BAD_ARG;
     }
 #undef GO
-    if (rc) return rc;
-    AIE_LAUNCH_CHECK();
+    return rc;
 }

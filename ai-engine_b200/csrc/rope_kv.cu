@@ -22,6 +22,8 @@ __global__ void rope_kv_write_kernel(const A* __restrict__ qkv, A* __restrict__ 
                                      unsigned* err) {
     // one block per (token, head slot): slots [0, H) are q heads, [H, H+K) k heads,
     // [H+K, H+2K) v heads; threads walk the head's rotated pairs, then its other elements
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x, slot_h = blockIdx.y;
     const int pos = positions[t];
     const int half = rot_dim / 2;
@@ -80,11 +82,11 @@ extern "C" int aie_rope_kv_write(const void* qkv, void* q_out, void* k_pages, vo
     const dim3 grid(T, H + 2 * K);
     const int threads = d >= 128 ? 64 : 32;
     if (dtype == AIE_F32)
-        rope_kv_write_kernel<float, float><<<grid, threads, 0, stream>>>(
+        launch_pdl(rope_kv_write_kernel<float, float>, grid, dim3(threads), 0, stream,
             (const float*)qkv, (float*)q_out, (float*)k_pages, (float*)v_pages, positions, token_req,
             block_table, bt_width, num_pages, P, H, K, d, rot_dim, inv_freq, write, err);
     else if (dtype == AIE_BF16)
-        rope_kv_write_kernel<bf16, bf16><<<grid, threads, 0, stream>>>(
+        launch_pdl(rope_kv_write_kernel<bf16, bf16>, grid, dim3(threads), 0, stream,
             (const bf16*)qkv, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, positions, token_req,
             block_table, bt_width, num_pages, P, H, K, d, rot_dim, inv_freq, write, err);
     else

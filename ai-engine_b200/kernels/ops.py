@@ -5,6 +5,7 @@ stream.  Shapes and dtypes a kernel does not take are refused with an error.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -80,16 +81,17 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
     return out
 
 
-def silu_mul(gu: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """a[t, f] = silu(gu[t, f]) * gu[t, F + f]."""
+def silu_mul(gu: torch.Tensor, out: Optional[torch.Tensor] = None, block: int = 0) -> torch.Tensor:
+    """a[t, f] = silu(gate) * up.  block == 0: gu[t] = [gate (F) | up (F)]; block > 0: gu[t]
+    is in groups of `block` gate columns followed by their `block` up columns."""
     _dev(gu)
     T, F2 = gu.shape
     F = F2 // 2
     if out is None:
         out = torch.empty((T, F), dtype=gu.dtype, device=gu.device)
     lib = library("elementwise.cu")
-    check(lib.aie_silu_mul(_p(gu), _p(out), c_int(dtype_code(gu)), c_int(T), c_int(F), _stream()),
-          "silu_mul")
+    check(lib.aie_silu_mul(_p(gu), _p(out), c_int(dtype_code(gu)), c_int(T), c_int(F), c_int(block),
+                           _stream()), "silu_mul")
     return out
 
 
@@ -124,41 +126,6 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, rows: Optional[torch.Tensor] = No
     return out
 
 
-def _row_groups(rows: int, K: int, swiglu: bool) -> int:
-    """Weight-row groups per CTA of the small-M kernel: as many as still leave two
-    CTAs for each of the 148 SMs (the rest of its 8 warps split K)."""
-    for rg in (8, 4, 2, 1):
-        if swiglu and rg < 2:
-            break
-        per_cta = (8 if swiglu else 16) * rg
-        if K % (32 * (8 // rg)) == 0 and (rows + per_cta - 1) // per_cta >= 2 * 148:
-            return rg
-    for rg in ((2, 4, 8) if swiglu else (1, 2, 4, 8)):
-        if K % (32 * (8 // rg)) == 0:
-            return rg
-    return 0
-
-
-def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False):
-    """bfloat16 x . w^T for at most 16 tokens with the weight-streaming kernel, or
-    None when the kernel does not take the sizes.  swiglu: w is the fused [2F, K]
-    gate/up matrix and the result is silu(gate) * up, [M, F]."""
-    M, K = x.shape
-    N = w.shape[0]
-    if M > 16 or N % (32 if swiglu else 16) or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
-        return None
-    rg = _row_groups(N // 2 if swiglu else N, K, swiglu)
-    if rg == 0:
-        return None
-    _dev(x, w)
-    out = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
-    lib = library("gemm_bf16.cu")
-    check(lib.aie_gemm_small_m(_p(x), _p(w), _p(out), c_int(dtype_code(out)), c_int(M), c_int(N), c_int(K),
-                               c_int(out.stride(0)), c_int(1 if swiglu else 0), c_int(rg), _stream()),
-          "gemm_small_m")
-    return out
-
-
 def tc_tile(T: int) -> int:
     """Token tile of the tcgen05 product: the smallest of 16 .. 256 that holds T, else 256."""
     for bn in (16, 32, 64, 128, 256):
@@ -168,61 +135,73 @@ def tc_tile(T: int) -> int:
 
 
 def tc_splits(T: int, N: int, K: int, bn: int) -> int:
-    """Parts to cut K into so that about two CTAs per SM are in flight (each with its
-    own ring of TMA stages), never fewer than 4 K blocks per part."""
+    """Parts to cut K into (one cluster of CTAs per output tile, at most 8) so that about
+    three CTAs per SM are in flight, never fewer than 4 K blocks per part."""
     tiles = ((N + 127) // 128) * ((T + bn - 1) // bn)
     kb = (K + 63) // 64
-    want = max(1, (2 * 148) // tiles)
-    return max(1, min(want, kb // 4 if kb >= 4 else 1, 32))
+    want = max(1, (3 * 148) // tiles)
+    return max(1, min(want, kb // 4 if kb >= 4 else 1, 8))
+
+
+TC_SWIGLU_BLOCK = 64     # gate/up rows per half of a 128-row weight tile
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, err: torch.Tensor,
-            bn: Optional[int] = None, splits: Optional[int] = None):
+            bn: Optional[int] = None, splits: Optional[int] = None, swiglu: bool = False):
     """bfloat16 x . w^T on tcgen05 tensor cores fed by TMA; None when the sizes are not
-    taken (K not a multiple of 8)."""
+    taken (K not a multiple of 8).  swiglu: w is the fused gate/up weight [2F, K] in tiles
+    of 64 gate rows + their 64 up rows; the result is silu(gate) * up, [T, F]."""
     T, K = x.shape
     N = w.shape[0]
-    if K % 8 or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+    if K % 8 or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or (swiglu and N % 128):
         return None
     _dev(x, w, err)
     bn = bn or tc_tile(T)
     splits = splits or tc_splits(T, N, K, bn)
-    out = torch.empty((T, N), dtype=out_dtype, device=x.device)
-    ws = torch.empty((splits, T, N), dtype=torch.float32, device=x.device) if splits > 1 else None
+    out = torch.empty((T, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
     lib = library("gemm_tc.cu")
     check(lib.aie_gemm_tc(_p(x), _p(w), _p(out), c_int(dtype_code(out)), c_int(T), c_int(N), c_int(K),
-                          c_int(out.stride(0)), c_int(bn), c_int(splits), _p(ws), _p(err), _stream()),
-          "gemm_tc")
+                          c_int(out.stride(0)), c_int(bn), c_int(splits), c_int(1 if swiglu else 0),
+                          _p(err), _stream()), "gemm_tc")
     return out
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+TC_MAX_TOKENS = 64       # up to here the tcgen05 kernel of this package; above, the library product
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           err: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x . w^T.  float32 activations (or a weight stored in 32-bit) take the true
-    float32 kernel.  bfloat16 x bfloat16: up to 16 tokens take the weight-streaming
-    kernel of this package; more tokens take the library matrix product, as the
+    float32 kernel.  bfloat16 x bfloat16: steps of up to 64 tokens take this package's
+    tcgen05 kernel (a weight stream); more tokens take the library matrix product, as the
     reference's engine does for its products
     (crates/ai-engine-candle/src/paged/transformer.rs:153-155)."""
     out_dtype = out_dtype or x.dtype
     if x.dtype == torch.float32 or w.dtype == torch.float32:
         y = gemm_f32(cast(x, torch.float32), w)
         return cast(y, out_dtype)
-    y = gemm_small_m(x, w, out_dtype)
-    if y is not None:
-        return y
+    if x.shape[0] <= TC_MAX_TOKENS and err is not None:
+        y = gemm_tc(x, w, out_dtype, err)
+        if y is not None:
+            return y
     _dev(x, w)
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     return torch.mm(x, w.t())
 
 
-def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor) -> torch.Tensor:
-    """silu(x . gate^T) * (x . up^T) for the fused [2F, K] gate/up weight; [T, F] in
-    x's dtype.  Few bfloat16 tokens: one kernel with the activation in its epilogue."""
-    if x.dtype == torch.bfloat16 and w_gu.dtype == torch.bfloat16:
-        y = gemm_small_m(x, w_gu, x.dtype, swiglu=True)
+def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor, block: int = 0,
+                  err: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """silu(x . gate^T) * (x . up^T) for the fused gate/up weight [2F, K]; [T, F] in x's
+    dtype.  block == 0: rows [0, F) are gate, [F, 2F) up.  block == 64: tiles of 64 gate
+    rows + their 64 up rows, which lets the tcgen05 kernel apply the activation in its
+    epilogue when the step is small."""
+    if (block == TC_SWIGLU_BLOCK and x.dtype == torch.bfloat16 and w_gu.dtype == torch.bfloat16
+            and x.shape[0] <= TC_MAX_TOKENS and err is not None):
+        y = gemm_tc(x, w_gu, x.dtype, err, swiglu=True)
         if y is not None:
             return y
-    return silu_mul(linear(x, w_gu, x.dtype))
+    return silu_mul(linear(x, w_gu, x.dtype, err), block=block)
 
 
 # ---------------------------------------------------------------------------

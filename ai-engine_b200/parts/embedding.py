@@ -51,5 +51,5 @@ class LMHead(Part):
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()
 
-    def forward(self, h):
-        return ops.linear(h, self.weight, torch.float32)
+    def forward(self, h, err=None):
+        return ops.linear(h, self.weight, torch.float32, err)

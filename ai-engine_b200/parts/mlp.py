@@ -18,6 +18,7 @@ class SwiGLU(FeedForward):
         self.hidden = int(spec.params["hidden_size"])
         self.inter = int(spec.params["intermediate_size"])
         self.w_gu = self.w_down = None
+        self.block = 0
 
     def tensor_specs(self):
         t = self.spec.tensors
@@ -29,12 +30,20 @@ class SwiGLU(FeedForward):
         t = self.spec.tensors
         g, u = source.get(t["gate"]), source.get(t["up"])
         dt = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
-        self.w_gu = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
+        # bfloat16: 64 gate rows then their 64 up rows, tile by tile, so that a 128-row
+        # weight tile of the tensor-core kernel holds both halves of 64 outputs
+        self.block = ops.TC_SWIGLU_BLOCK if (dt == torch.bfloat16 and self.inter % ops.TC_SWIGLU_BLOCK == 0) else 0
+        if self.block:
+            b = self.block
+            self.w_gu = torch.stack([g.view(-1, b, self.hidden), u.view(-1, b, self.hidden)], dim=1) \
+                .reshape(2 * self.inter, self.hidden).contiguous()
+        else:
+            self.w_gu = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
         self.w_down = source.get(t["down"])
 
     def weight_bytes(self):
         return sum(w.numel() * w.element_size() for w in (self.w_gu, self.w_down))
 
     def forward(self, h, ctx):
-        a = ops.linear_swiglu(h, self.w_gu)
-        return ops.linear(a, self.w_down, torch.float32)     # the branch joins the residual in float32
+        a = ops.linear_swiglu(h, self.w_gu, self.block, ctx.err if ctx is not None else None)
+        return ops.linear(a, self.w_down, torch.float32, ctx.err if ctx is not None else None)     # the branch joins the residual in float32

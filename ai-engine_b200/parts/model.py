@@ -115,7 +115,7 @@ class Model:
         if ctx.num_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         h = self.final_norm.forward(x, pending, rows=ctx.logit_rows, write_back=False)
-        return self.lm_head.forward(h)
+        return self.lm_head.forward(h, ctx.err)
 
 
 def tensor_specs_of(spec: ModelSpec) -> List[TensorSpec]:

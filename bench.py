@@ -196,6 +196,45 @@ def time_prefill(torch, model, tokens, pk):
                 frac=flops / (best * 1e-3) / (pk["bf16_tflops"] * 1e12))
 
 
+def time_gemms(torch, tokens):
+    """Each projection of the model alone at `tokens` rows: the library product and the
+    tcgen05 kernel (with several split-K settings for small steps), L2 flushed between runs."""
+    from ai_engine_b200.kernels import ops
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    shapes = {"qkv": (6144, 4096), "o": (4096, 4096), "gate_up": (28672, 4096), "down": (4096, 14336),
+              "lm_head": (128256, 4096)}
+    out = {}
+    for name, (N, K) in shapes.items():
+        T = 1 if name == "lm_head" and tokens > 64 else tokens
+        x = torch.randn(T, K, device="cuda").bfloat16()
+        w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+        impls = {"library": lambda: torch.mm(x, w.t()), "tcgen05": lambda: ops.gemm_tc(x, w, torch.bfloat16, err)}
+        for s_ in (1, 2, 4, 8):
+            if T <= 64 and s_ > 1:
+                impls[f"tcgen05_s{s_}"] = (lambda s_=s_: ops.gemm_tc(x, w, torch.bfloat16, err, splits=s_))
+        row = {}
+        for iname, fn in impls.items():
+            for _ in range(3):
+                fn()
+            ts = []
+            for _ in range(10):
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                fn()
+                b.record()
+                torch.cuda.synchronize()
+                ts.append(a.elapsed_time(b) * 1e3)
+            us = sorted(ts)[len(ts) // 2]
+            row[iname] = dict(us=round(us, 1), tb_s=round((N * K * 2 + T * (K + N) * 2) / us / 1e6, 2),
+                              tflops=round(2.0 * T * N * K / us / 1e6, 1))
+        out[f"{name}[{T}x{N}x{K}]"] = row
+    assert int(err.item()) == 0
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -206,7 +245,7 @@ def main():
                     help="run fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "gemm"], default=None,
                     help="time one part only and print its numbers (for profiling)")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -224,6 +263,10 @@ def main():
 
     warmup = max(a.warmup, 3)
     pk = peaks()
+    if a.only == "gemm":
+        for k, v in time_gemms(torch, a.batch).items():
+            print(k, json.dumps(v))
+        return 0
     cfg = dict(LLAMA3_8B)
     cfg["num_hidden_layers"] = a.layers
     model, _ = random_model(cfg, seed=0, dtype="bf16")

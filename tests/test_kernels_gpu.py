@@ -73,6 +73,10 @@ def test_silu_mul(dtype, T, F):
     out = ops().silu_mul(gu)
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     assert (out.double() - want).abs().max() <= tol * max(1.0, float(want.abs().max()))
+    if F % 8 == 0:      # groups of 8 gate columns followed by their 8 up columns
+        inter = torch.stack([gu[:, :F].reshape(T, -1, 8), gu[:, F:].reshape(T, -1, 8)], dim=2).reshape(T, 2 * F)
+        out2 = ops().silu_mul(inter.contiguous(), block=8)
+        assert torch.equal(out2, out)
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 1, 1), (5, 70, 33), (64, 64, 16), (130, 257, 1000), (3, 128256, 64)])
@@ -383,47 +387,3 @@ def test_sampling_distribution_and_large_vocab():
     # the walk is monotone: a larger draw never lands on a more likely token
     vals = [float(base[t]) for t in out]
     assert all(vals[i] >= vals[i + 1] - 1e-6 for i in range(N - 1))
-
-
-SMALL_M_SHAPES = [  # M, N, K
-    (1, 4096, 4096), (8, 6144, 4096), (8, 4096, 14336), (3, 128256, 4096), (16, 48, 256), (9, 272, 192),
-    (5, 16, 32), (8, 3072, 1024), (13, 2048, 8192),
-]
-
-
-@pytest.mark.parametrize("M,N,K", SMALL_M_SHAPES)
-@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_gemm_small_m_weight_streaming(M, N, K, out_dtype):
-    torch.manual_seed(M + N)
-    x = torch.randn(M, K, device=DEV).bfloat16()
-    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
-    out = ops().gemm_small_m(x, w, out_dtype)
-    assert out is not None and out.dtype == out_dtype and out.shape == (M, N)
-    want = x.double() @ w.double().T
-    tol = (3e-5 if out_dtype == torch.float32 else 1e-2) * max(1.0, float(want.abs().max()))
-    assert (out.double() - want).abs().max() <= tol
-    one = ops().gemm_small_m(x[M // 2:M // 2 + 1].contiguous(), w, out_dtype)     # batch does not matter
-    assert torch.equal(one[0], out[M // 2])
-
-
-@pytest.mark.parametrize("M,F,K", [(8, 14336, 4096), (1, 8192, 2048), (16, 272, 192), (7, 64, 64), (12, 1024, 4096)])
-def test_gemm_small_m_swiglu_epilogue(M, F, K):
-    torch.manual_seed(F)
-    x = torch.randn(M, K, device=DEV).bfloat16()
-    w = (torch.randn(2 * F, K, device=DEV) * 0.05).bfloat16()
-    out = ops().linear_swiglu(x, w)
-    g, u = x.double() @ w[:F].double().T, x.double() @ w[F:].double().T
-    want = g * torch.sigmoid(g) * u
-    assert out.shape == (M, F) and out.dtype == torch.bfloat16
-    assert (out.double() - want).abs().max() <= 1e-2 * max(1.0, float(want.abs().max()))
-
-
-def test_gemm_small_m_refuses_what_it_does_not_take():
-    x = torch.randn(17, 64, device=DEV).bfloat16()
-    w = torch.randn(32, 64, device=DEV).bfloat16()
-    assert ops().gemm_small_m(x, w, torch.bfloat16) is None                      # more than 16 tokens
-    assert ops().gemm_small_m(x[:4].contiguous(), w[:24].contiguous(), torch.bfloat16) is None   # N % 16
-    x2 = torch.randn(4, 80, device=DEV).bfloat16()
-    assert ops().gemm_small_m(x2, torch.randn(32, 80, device=DEV).bfloat16(), torch.bfloat16) is None  # K % 32
-    y = ops().linear(x2, torch.randn(32, 80, device=DEV).bfloat16())              # the library product stands in
-    assert y.shape == (4, 32)

@@ -60,14 +60,15 @@ extern "C" int aie_embed_gather(const int* ids, const void* table, int table_dty
 
 // ---------------------------------------------------------------------------
 // Residual add + RMSNorm (crates/ai-engine-runtime/src/arch/rmsnorm.rs:29-42):
-//   s = x[row] (+ delta[row]);  ms = mean(s^2);  r = 1/sqrt(ms + eps);
+//   s = x[row] (+ delta[row], or the sum of `parts` deltas `part_stride` elements apart);  ms = mean(s^2);  r = 1/sqrt(ms + eps);
 //   out[i] = (s * r) * w          with eps inside the root and the weight last.
 // `rows` (optional) picks input rows; `write_back` stores s into x.
 // ---------------------------------------------------------------------------
 template <typename A, typename W, typename O>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const A* __restrict__ delta,
                                    const W* __restrict__ w, O* __restrict__ out,
-                                   const int* __restrict__ rows, int D, float eps, int write_back) {
+                                   const int* __restrict__ rows, int D, float eps, int write_back,
+                                   int parts, size_t part_stride) {
     extern __shared__ float srow[];   // D floats + 32
     float* red = srow + D;
     const int o = blockIdx.x;
@@ -76,7 +77,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const A* __restrict__ 
     float ss = 0.f;
     for (int i = threadIdx.x; i < D; i += blockDim.x) {
         float s = xr[i];
-        if (delta) s += to_f32<A>(delta[r * D + i]);
+        if (delta)
+            for (int p = 0; p < parts; ++p) s += to_f32<A>(delta[p * part_stride + r * D + i]);
         srow[i] = s;
         ss += s * s;
     }
@@ -96,7 +98,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const A* __restrict__ 
 template <typename A, typename W, typename O>
 __global__ void __launch_bounds__(1024)
 add_rmsnorm_row_kernel(float* __restrict__ x, const A* __restrict__ delta, const W* __restrict__ w,
-                       O* __restrict__ out, const int* __restrict__ rows, int D, float eps, int write_back) {
+                       O* __restrict__ out, const int* __restrict__ rows, int D, float eps, int write_back,
+                       int parts, size_t part_stride) {
     __shared__ float red[32];
     pdl_launch_dependents();
     pdl_wait();
@@ -108,11 +111,13 @@ add_rmsnorm_row_kernel(float* __restrict__ x, const A* __restrict__ delta, const
     if (on) {
         s = reinterpret_cast<const float4*>(x + r * D)[i];
         if (delta) {
-            const float4 dl = load4<A>(delta + r * D + 4 * i);
-            s.x += dl.x;
-            s.y += dl.y;
-            s.z += dl.z;
-            s.w += dl.w;
+            for (int p = 0; p < parts; ++p) {       // parts of a split product, added in order
+                const float4 dl = load4<A>(delta + p * part_stride + r * D + 4 * i);
+                s.x += dl.x;
+                s.y += dl.y;
+                s.z += dl.z;
+                s.w += dl.w;
+            }
         }
     }
     float ss = s.x * s.x;
@@ -131,14 +136,14 @@ add_rmsnorm_row_kernel(float* __restrict__ x, const A* __restrict__ delta, const
 
 template <typename A, typename W>
 static int launch_rmsnorm_o(float* x, const void* delta, const void* w, void* out, int out_dtype,
-                            const int* rows, int n, int D, float eps, int write_back,
-                            cudaStream_t stream) {
+                            const int* rows, int n, int D, float eps, int write_back, int parts,
+                            size_t part_stride, cudaStream_t stream) {
     if (D % 4 == 0 && D <= 4096) {
         const int threads = ((D / 4) + 31) / 32 * 32;
         if (out_dtype == AIE_F32)
-            launch_pdl(add_rmsnorm_row_kernel<A, W, float>, dim3(n), dim3(threads), 0, stream, x, (const A*)delta, (const W*)w, (float*)out, rows, D, eps, write_back);
+            launch_pdl(add_rmsnorm_row_kernel<A, W, float>, dim3(n), dim3(threads), 0, stream, x, (const A*)delta, (const W*)w, (float*)out, rows, D, eps, write_back, parts, part_stride);
         else if (out_dtype == AIE_BF16)
-            launch_pdl(add_rmsnorm_row_kernel<A, W, bf16>, dim3(n), dim3(threads), 0, stream, x, (const A*)delta, (const W*)w, (bf16*)out, rows, D, eps, write_back);
+            launch_pdl(add_rmsnorm_row_kernel<A, W, bf16>, dim3(n), dim3(threads), 0, stream, x, (const A*)delta, (const W*)w, (bf16*)out, rows, D, eps, write_back, parts, part_stride);
         else
             return AIE_BAD_ARG;
         AIE_LAUNCH_CHECK();
@@ -149,11 +154,11 @@ static int launch_rmsnorm_o(float* x, const void* delta, const void* w, void* ou
     if (out_dtype == AIE_F32) {
         auto k = add_rmsnorm_kernel<A, W, float>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k<<<n, threads, smem, stream>>>(x, (const A*)delta, (const W*)w, (float*)out, rows, D, eps, write_back);
+        k<<<n, threads, smem, stream>>>(x, (const A*)delta, (const W*)w, (float*)out, rows, D, eps, write_back, parts, part_stride);
     } else if (out_dtype == AIE_BF16) {
         auto k = add_rmsnorm_kernel<A, W, bf16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k<<<n, threads, smem, stream>>>(x, (const A*)delta, (const W*)w, (bf16*)out, rows, D, eps, write_back);
+        k<<<n, threads, smem, stream>>>(x, (const A*)delta, (const W*)w, (bf16*)out, rows, D, eps, write_back, parts, part_stride);
     } else
         return AIE_BAD_ARG;
     AIE_LAUNCH_CHECK();
@@ -161,10 +166,12 @@ static int launch_rmsnorm_o(float* x, const void* delta, const void* w, void* ou
 
 extern "C" int aie_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void* w,
                                int w_dtype, void* out, int out_dtype, const int* rows, int n, int D,
-                               float eps, int write_back, cudaStream_t stream) {
+                               float eps, int write_back, int parts, long long part_stride,
+                               cudaStream_t stream) {
     if (n <= 0) return 0;
     if (delta == nullptr) delta_dtype = AIE_F32;
-#define GO(A, W) return launch_rmsnorm_o<A, W>(x, delta, w, out, out_dtype, rows, n, D, eps, write_back, stream)
+    if (parts < 1) return AIE_BAD_ARG;
+#define GO(A, W) return launch_rmsnorm_o<A, W>(x, delta, w, out, out_dtype, rows, n, D, eps, write_back, parts, (size_t)part_stride, stream)
     if (delta_dtype == AIE_F32 && w_dtype == AIE_F32) GO(float, float);
     if (delta_dtype == AIE_F32 && w_dtype == AIE_BF16) GO(float, bf16);
     if (delta_dtype == AIE_BF16 && w_dtype == AIE_F32) GO(bf16, float);

@@ -105,10 +105,15 @@ template <> __device__ __forceinline__ void tc_store<bf16>(bf16* p, float v) { *
 
 template <int BN> struct TcSmem {
     static constexpr int stage_bytes = TC_BM * TC_BK * 2 + BN * TC_BK * 2;
-    // few tokens: short rings so that three CTAs share an SM and hide each other's start and end;
-    // many tokens: one CTA per SM with as deep a ring as fits
-    static constexpr int stages = BN <= 32 ? 4 : (BN <= 64 ? 4 : (BN <= 128 ? 6 : 4));
-    static constexpr int bytes = stages * stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int max_stages = BN <= 64 ? 8 : (BN <= 128 ? 6 : 4);     // what 227 KB hold
+    // the ring depth is chosen per launch: a grid of at most one CTA per SM takes the deepest ring
+    // (one CTA must keep its SM's share of the memory system busy); a larger grid takes a short ring
+    // so that several CTAs share an SM and cover each other's start and end
+    static constexpr int tile_bytes = BN * TC_BM * 4;      // the float32 tile staged for joining parts
+    // [alignment slack | 1024 bytes of barriers | ring of stages, reused for the staged tile]
+    static constexpr int bytes_for(int stages) {
+        return 2048 + (stages * stage_bytes > tile_bytes ? stages * stage_bytes : tile_bytes);
+    }
 };
 
 #define TC_EPI_STORE 0
@@ -135,21 +140,25 @@ __device__ __forceinline__ float ld_peer(unsigned addr, unsigned rank) {
 template <int BN, int EPI, typename OT>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               OT* __restrict__ C, int T, int N, int K, int ldc, int kb_per_split, unsigned* err) {
-    constexpr int STAGES = TcSmem<BN>::stages;
+               OT* __restrict__ C, int T, int N, int K, int ldc, int kb_per_split, int STAGES, int raw_parts,
+               unsigned* err) {
     constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
     extern __shared__ unsigned char tc_raw[];
-    unsigned char* base = reinterpret_cast<unsigned char*>(((size_t)tc_raw + 1023) & ~(size_t)1023);
-    unsigned long long* full = reinterpret_cast<unsigned long long*>(base + STAGES * TcSmem<BN>::stage_bytes);
-    unsigned long long* empty = full + STAGES;
-    unsigned long long* accum = empty + STAGES;
+    unsigned char* bars = reinterpret_cast<unsigned char*>(((size_t)tc_raw + 1023) & ~(size_t)1023);
+    unsigned char* base = bars + 1024;                    // the ring, 1024-byte aligned
+    unsigned long long* full = reinterpret_cast<unsigned long long*>(bars);
+    unsigned long long* empty = full + 8;
+    unsigned long long* accum = empty + 8;
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(accum + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* tile_s = reinterpret_cast<float*>(base);      // [BN][128] partial tile, after the ring is idle
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * TC_BM, t0 = blockIdx.y * BN;
-    const int parts = gridDim.z;                          // = cluster size along z
+    // parts of K: joined inside a cluster (parts == cluster size), or left to the consumer
+    // (raw_parts: part z is stored as it is at C + z * T * ldc and the next kernel adds them)
+    const int parts = raw_parts ? 1 : gridDim.z;
+    if (raw_parts) C += (size_t)blockIdx.z * T * ldc;
     const int kb_total = (K + TC_BK - 1) / TC_BK;
     const int kb_begin = blockIdx.z * kb_per_split;
     const int kb_end = min(kb_begin + kb_per_split, kb_total);
@@ -259,36 +268,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
 
     if (parts > 1 || EPI != TC_EPI_STORE) {
-        // join the parts: every CTA of the cluster has its tile in shared memory
+        // join the parts: every CTA of the cluster has its tile in shared memory; each CTA sums
+        // and stores its share of the tile's tokens, reading the others' tiles in rank order
         __syncwarp();
         if (parts > 1) cluster_sync_all(); else __syncthreads();
-        if (cluster_rank() == 0 && warp >= 2 && !*abort_flag) {
+        if (warp >= 2 && !*abort_flag) {
             const int e = tid - 64;                        // 0 .. 127
             const unsigned tile_addr = tc_smem(tile_s);
-            if (EPI == TC_EPI_STORE) {
-                for (int idx = e; idx < BN * TC_BM; idx += 128) {
-                    const int tt = idx / TC_BM, r = idx % TC_BM;
-                    float acc = tile_s[idx];
-                    for (int p = 1; p < parts; ++p) acc += ld_peer(tile_addr + idx * 4, p);
-                    if (t0 + tt < T && n0 + r < N) tc_store<OT>(C + (size_t)(t0 + tt) * ldc + n0 + r, acc);
-                }
-            } else {
-                // rows 0..63 of the tile are gate rows, rows 64..127 their up rows; output column f
-                const int f0 = blockIdx.x * (TC_BM / 2), F = N / 2;
-                for (int idx = e; idx < BN * (TC_BM / 2); idx += 128) {
-                    const int tt = idx / (TC_BM / 2), j = idx % (TC_BM / 2);
-                    float g = tile_s[tt * TC_BM + j], u = tile_s[tt * TC_BM + 64 + j];
-                    for (int p = 1; p < parts; ++p) {
+            const int rank = (int)cluster_rank();
+            const int tokens = min(BN, T - t0);
+            constexpr int COLS = EPI == TC_EPI_STORE ? TC_BM : TC_BM / 2;      // outputs per token
+            const int total = tokens * COLS;
+            const int share = (total + parts - 1) / parts;
+            const int f0 = blockIdx.x * COLS, width = EPI == TC_EPI_STORE ? N : N / 2;
+            for (int idx = rank * share + e; idx < min((rank + 1) * share, total); idx += 128) {
+                const int tt = idx / COLS, j = idx % COLS;
+                float out;
+                if (EPI == TC_EPI_STORE) {
+                    float acc = 0.f;
+                    for (int p = 0; p < parts; ++p) acc += ld_peer(tile_addr + (tt * TC_BM + j) * 4, p);
+                    out = acc;
+                } else {     // rows 0..63 of the tile are gate rows, rows 64..127 their up rows
+                    float g = 0.f, u = 0.f;
+                    for (int p = 0; p < parts; ++p) {
                         g += ld_peer(tile_addr + (tt * TC_BM + j) * 4, p);
                         u += ld_peer(tile_addr + (tt * TC_BM + 64 + j) * 4, p);
                     }
-                    const float sv = g * (1.0f / (1.0f + expf(-g)));
-                    if (t0 + tt < T && f0 + j < F) tc_store<OT>(C + (size_t)(t0 + tt) * ldc + f0 + j, sv * u);
+                    out = g * (1.0f / (1.0f + expf(-g))) * u;
                 }
+                if (f0 + j < width) tc_store<OT>(C + (size_t)(t0 + tt) * ldc + f0 + j, out);
             }
         }
         __syncwarp();
-        if (parts > 1) cluster_sync_all();       // peers keep their tiles until rank 0 has read them
+        if (parts > 1) cluster_sync_all();       // every CTA keeps its tile until the others have read it
     }
 
     // leave together; on an abort, give copies in flight a bounded time to land first
@@ -339,22 +351,26 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_
 
 template <int BN, int EPI, typename OT>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, int ldc,
-                     int splits, unsigned* err, cudaStream_t st) {
+                     int splits, int raw_parts, unsigned* err, cudaStream_t st) {
     const int kb_total = (K + TC_BK - 1) / TC_BK;
     const int kbps = (kb_total + splits - 1) / splits;
     auto kern = gemm_tc_kernel<BN, EPI, OT>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN>::bytes);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((N + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, splits);
+    const long long ctas = (long long)cfg.gridDim.x * cfg.gridDim.y * cfg.gridDim.z;
+    int stages = ctas <= 148 ? TcSmem<BN>::max_stages : (TcSmem<BN>::max_stages >= 8 ? 4 : TcSmem<BN>::max_stages);
+    if (stages > kbps) stages = kbps < 2 ? 2 : kbps;
+    const int smem = TcSmem<BN>::bytes_for(stages);
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN>::bytes_for(TcSmem<BN>::max_stages));
     cfg.blockDim = dim3(TC_THREADS);
-    cfg.dynamicSmemBytes = TcSmem<BN>::bytes;
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     int na = 0;
     attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    attr[na].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
     ++na;
-    if (splits > 1) {      // the parts of one output tile are one cluster
+    if (splits > 1 && !raw_parts) {      // the parts of one output tile are one cluster
         attr[na].id = cudaLaunchAttributeClusterDimension;
         attr[na].val.clusterDim.x = 1;
         attr[na].val.clusterDim.y = 1;
@@ -363,18 +379,20 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int 
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, mx, (OT*)C, T, N, K, ldc, kbps, err);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, mx, (OT*)C, T, N, K, ldc, kbps, stages, raw_parts, err);
     return (int)e;
 }
 
-// bn: token tile (16, 32, 64, 128, 256).  splits: parts of K, 1 .. 8 (a cluster).
+// bn: token tile (16, 32, 64, 128, 256).  splits: parts of K: 1 .. 8 joined in a cluster, or, with
+// raw_parts (float32 output only, no swiglu), any number stored one after the other: C is [splits, T, N].
 // swiglu: W is [2F, K] in 128-row tiles of 64 gate rows + their 64 up rows (N = 2F), C is [T, F].
 // Requires K % 8 == 0 (16-byte rows) and 16-byte aligned X and W.
 extern "C" int aie_gemm_tc(const void* X, const void* W, void* C, int out_dtype, int T, int N, int K, int ldc,
-                           int bn, int splits, int swiglu, unsigned* err, cudaStream_t stream) {
+                           int bn, int splits, int swiglu, int raw_parts, unsigned* err, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ((size_t)X & 15) || ((size_t)W & 15)) return AIE_UNSUPPORTED;
-    if (splits < 1 || splits > 8) return AIE_BAD_ARG;
+    if (splits < 1 || (!raw_parts && splits > 8) || splits > 65535) return AIE_BAD_ARG;
+    if (raw_parts && (swiglu || out_dtype != AIE_F32)) return AIE_BAD_ARG;
     if (out_dtype != AIE_BF16 && out_dtype != AIE_F32) return AIE_BAD_ARG;
     if (swiglu && N % 128) return AIE_UNSUPPORTED;
     if ((T + bn - 1) / bn > 65535) return AIE_UNSUPPORTED;
@@ -385,11 +403,11 @@ extern "C" int aie_gemm_tc(const void* X, const void* W, void* C, int out_dtype,
     if (rc) return rc;
 #define GO(BNV)                                                                                                   \
     if (swiglu)                                                                                                   \
-        rc = out_dtype == AIE_BF16 ? launch_tc<BNV, TC_EPI_SWIGLU, bf16>(mw, mx, C, T, N, K, ldc, splits, err, stream)  \
-                                   : launch_tc<BNV, TC_EPI_SWIGLU, float>(mw, mx, C, T, N, K, ldc, splits, err, stream); \
+        rc = out_dtype == AIE_BF16 ? launch_tc<BNV, TC_EPI_SWIGLU, bf16>(mw, mx, C, T, N, K, ldc, splits, raw_parts, err, stream)  \
+                                   : launch_tc<BNV, TC_EPI_SWIGLU, float>(mw, mx, C, T, N, K, ldc, splits, raw_parts, err, stream); \
     else                                                                                                          \
-        rc = out_dtype == AIE_BF16 ? launch_tc<BNV, TC_EPI_STORE, bf16>(mw, mx, C, T, N, K, ldc, splits, err, stream)   \
-                                   : launch_tc<BNV, TC_EPI_STORE, float>(mw, mx, C, T, N, K, ldc, splits, err, stream)
+        rc = out_dtype == AIE_BF16 ? launch_tc<BNV, TC_EPI_STORE, bf16>(mw, mx, C, T, N, K, ldc, splits, raw_parts, err, stream)   \
+                                   : launch_tc<BNV, TC_EPI_STORE, float>(mw, mx, C, T, N, K, ldc, splits, raw_parts, err, stream)
     switch (bn) {
         case 16: GO(16); break;
         case 32: GO(32); break;

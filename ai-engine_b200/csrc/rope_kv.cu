@@ -11,8 +11,11 @@
 // (the reference writes them token by token, crates/ai-engine-candle/src/paged/attention.rs:59-83).
 #include "common.cuh"
 
-template <typename A, typename C>
-__global__ void rope_kv_write_kernel(const A* __restrict__ qkv, A* __restrict__ q_out,
+// I: dtype of qkv (the compute dtype, or float32 parts of a split product that are added here);
+// A: dtype of q_out; C: dtype of the cache.
+template <typename I, typename A, typename C>
+__global__ void rope_kv_write_kernel(const I* __restrict__ qkv, int parts, size_t part_stride,
+                                     A* __restrict__ q_out,
                                      C* __restrict__ k_pages, C* __restrict__ v_pages,
                                      const int* __restrict__ positions,
                                      const int* __restrict__ token_req,
@@ -27,7 +30,12 @@ __global__ void rope_kv_write_kernel(const A* __restrict__ qkv, A* __restrict__ 
     const int t = blockIdx.x, slot_h = blockIdx.y;
     const int pos = positions[t];
     const int half = rot_dim / 2;
-    const A* x = qkv + (size_t)t * (H + 2 * K) * d + (size_t)slot_h * d;
+    const I* x = qkv + (size_t)t * (H + 2 * K) * d + (size_t)slot_h * d;
+    auto in = [&](int e) {
+        float v = to_f32<I>(x[e]);
+        for (int p = 1; p < parts; ++p) v += to_f32<I>(x[p * part_stride + e]);
+        return v;
+    };
     const bool is_q = slot_h < H, is_v = slot_h >= H + K;
     if (!is_q && !write) return;     // the pages are another run's: q only
     A* qo = nullptr;
@@ -46,14 +54,14 @@ __global__ void rope_kv_write_kernel(const A* __restrict__ qkv, A* __restrict__ 
         ko = (is_v ? v_pages : k_pages) + (((size_t)page * K + kh) * P + (pos % P)) * d;
     }
     if (is_v) {
-        for (int e = threadIdx.x; e < d; e += blockDim.x) ko[e] = from_f32<C>(to_f32<A>(x[e]));
+        for (int e = threadIdx.x; e < d; e += blockDim.x) ko[e] = from_f32<C>(in(e));
         return;
     }
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         const float ang = (float)pos * inv_freq[i];
         float sn, cs;
         sincosf(ang, &sn, &cs);
-        const float x1 = to_f32<A>(x[i]), x2 = to_f32<A>(x[i + half]);
+        const float x1 = in(i), x2 = in(i + half);
         const float o1 = x1 * cs - x2 * sn;
         const float o2 = x1 * sn + x2 * cs;
         if (is_q) {
@@ -65,14 +73,14 @@ __global__ void rope_kv_write_kernel(const A* __restrict__ qkv, A* __restrict__ 
         }
     }
     for (int e = rot_dim + threadIdx.x; e < d; e += blockDim.x) {      // elements that are not rotated
-        const float v = to_f32<A>(x[e]);
+        const float v = in(e);
         if (is_q) qo[e] = from_f32<A>(v);
         else ko[e] = from_f32<C>(v);
     }
 }
 
-extern "C" int aie_rope_kv_write(const void* qkv, void* q_out, void* k_pages, void* v_pages,
-                                 int dtype, const int* positions, const int* token_req,
+extern "C" int aie_rope_kv_write(const void* qkv, int in_dtype, int parts, long long part_stride,
+                                 void* q_out, void* k_pages, void* v_pages, int dtype, const int* positions, const int* token_req,
                                  const int* block_table, int bt_width, int num_pages, int P, int T,
                                  int H, int K, int d, int rot_dim, const float* inv_freq,
                                  int write, unsigned* err, cudaStream_t stream) {
@@ -81,15 +89,20 @@ extern "C" int aie_rope_kv_write(const void* qkv, void* q_out, void* k_pages, vo
     if (H + 2 * K > 65535) return AIE_UNSUPPORTED;
     const dim3 grid(T, H + 2 * K);
     const int threads = d >= 128 ? 64 : 32;
-    if (dtype == AIE_F32)
-        launch_pdl(rope_kv_write_kernel<float, float>, grid, dim3(threads), 0, stream,
-            (const float*)qkv, (float*)q_out, (float*)k_pages, (float*)v_pages, positions, token_req,
-            block_table, bt_width, num_pages, P, H, K, d, rot_dim, inv_freq, write, err);
-    else if (dtype == AIE_BF16)
-        launch_pdl(rope_kv_write_kernel<bf16, bf16>, grid, dim3(threads), 0, stream,
-            (const bf16*)qkv, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, positions, token_req,
-            block_table, bt_width, num_pages, P, H, K, d, rot_dim, inv_freq, write, err);
+    if (parts < 1 || (parts > 1 && in_dtype != AIE_F32)) return AIE_BAD_ARG;
+#define ARGS positions, token_req, block_table, bt_width, num_pages, P, H, K, d, rot_dim, inv_freq, write, err
+    cudaError_t e;
+    if (dtype == AIE_F32 && in_dtype == AIE_F32)
+        e = launch_pdl(rope_kv_write_kernel<float, float, float>, grid, dim3(threads), 0, stream, (const float*)qkv,
+                       parts, (size_t)part_stride, (float*)q_out, (float*)k_pages, (float*)v_pages, ARGS);
+    else if (dtype == AIE_BF16 && in_dtype == AIE_BF16)
+        e = launch_pdl(rope_kv_write_kernel<bf16, bf16, bf16>, grid, dim3(threads), 0, stream, (const bf16*)qkv,
+                       parts, (size_t)part_stride, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, ARGS);
+    else if (dtype == AIE_BF16 && in_dtype == AIE_F32)
+        e = launch_pdl(rope_kv_write_kernel<float, bf16, bf16>, grid, dim3(threads), 0, stream, (const float*)qkv,
+                       parts, (size_t)part_stride, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, ARGS);
     else
         return AIE_BAD_ARG;
-    AIE_LAUNCH_CHECK();
+#undef ARGS
+    return (int)e;
 }

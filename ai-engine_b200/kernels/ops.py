@@ -60,14 +60,20 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
                 write_back: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """s = x (+ delta); out = (s / sqrt(mean(s^2) + eps)) * weight.  `x` is the
-    float32 residual stream and receives s when `write_back`; `rows` picks rows."""
+    float32 residual stream and receives s when `write_back`; `rows` picks rows.
+    `delta` may be [parts, T, D]: the parts of a split product, added here in order."""
     _dev(x, delta, weight, rows)
     if x.dtype != torch.float32:
         raise KernelError("add_rmsnorm: the residual stream must be float32")
     D = x.shape[-1]
     if weight.shape != (D,):
         raise KernelError(f"add_rmsnorm: weight shape {tuple(weight.shape)} != ({D},)")
-    if delta is not None and delta.shape != x.shape:
+    parts, part_stride = 1, 0
+    if delta is not None and delta.dim() == 3:        # [parts, T, D]: parts of a split product
+        parts, part_stride = delta.shape[0], delta.stride(0)
+        if delta.shape[1:] != x.shape:
+            raise KernelError("add_rmsnorm: delta parts differ in shape from x")
+    elif delta is not None and delta.shape != x.shape:
         raise KernelError("add_rmsnorm: delta shape differs from x")
     n = x.shape[0] if rows is None else rows.shape[0]
     if out is None:
@@ -76,7 +82,8 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
     check(lib.aie_add_rmsnorm(_p(x), _p(delta), c_int(dtype_code(delta) if delta is not None else 0),
                               _p(weight), c_int(dtype_code(weight)), _p(out),
                               c_int(dtype_code(out)), _p(rows), c_int(n), c_int(D), c_float(eps),
-                              c_int(1 if (write_back and rows is None) else 0), _stream()),
+                              c_int(1 if (write_back and rows is None) else 0), c_int(parts),
+                              c_longlong(part_stride), _stream()),
           "add_rmsnorm")
     return out
 
@@ -135,22 +142,27 @@ def tc_tile(T: int) -> int:
 
 
 def tc_splits(T: int, N: int, K: int, bn: int) -> int:
-    """Parts to cut K into (one cluster of CTAs per output tile, at most 8) so that about
-    three CTAs per SM are in flight, never fewer than 4 K blocks per part."""
+    """Parts to cut K into.  A weight with fewer 128-row tiles than the machine has SMs is
+    cut so that the grid comes close to one CTA per SM (each with a deep ring of stages and
+    at least 8 K blocks); a weight with more tiles is not cut."""
     tiles = ((N + 127) // 128) * ((T + bn - 1) // bn)
     kb = (K + 63) // 64
-    want = max(1, (3 * 148) // tiles)
-    return max(1, min(want, kb // 4 if kb >= 4 else 1, 8))
+    if tiles >= 148:
+        return 1
+    return max(1, min(148 // tiles, kb // 8 if kb >= 8 else 1))
 
 
 TC_SWIGLU_BLOCK = 64     # gate/up rows per half of a 128-row weight tile
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, err: torch.Tensor,
-            bn: Optional[int] = None, splits: Optional[int] = None, swiglu: bool = False):
+            bn: Optional[int] = None, splits: Optional[int] = None, swiglu: bool = False,
+            raw_parts: bool = False):
     """bfloat16 x . w^T on tcgen05 tensor cores fed by TMA; None when the sizes are not
     taken (K not a multiple of 8).  swiglu: w is the fused gate/up weight [2F, K] in tiles
-    of 64 gate rows + their 64 up rows; the result is silu(gate) * up, [T, F]."""
+    of 64 gate rows + their 64 up rows; the result is silu(gate) * up, [T, F].
+    raw_parts: the parts of a split K are not joined: the result is float32
+    [splits, T, N] and whoever reads it adds the parts (the norm and rotary kernels do)."""
     T, K = x.shape
     N = w.shape[0]
     if K % 8 or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or (swiglu and N % 128):
@@ -158,15 +170,33 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, err: torch
     _dev(x, w, err)
     bn = bn or tc_tile(T)
     splits = splits or tc_splits(T, N, K, bn)
-    out = torch.empty((T, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
+    if swiglu:
+        splits = 1 if raw_parts else min(splits, 8)
+    if raw_parts and splits > 1:
+        out = torch.empty((splits, T, N), dtype=torch.float32, device=x.device)
+    else:
+        raw_parts = False
+        splits = min(splits, 8)              # joined inside a cluster of at most 8 CTAs
+        out = torch.empty((T, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
     lib = library("gemm_tc.cu")
     check(lib.aie_gemm_tc(_p(x), _p(w), _p(out), c_int(dtype_code(out)), c_int(T), c_int(N), c_int(K),
-                          c_int(out.stride(0)), c_int(bn), c_int(splits), c_int(1 if swiglu else 0),
-                          _p(err), _stream()), "gemm_tc")
+                          c_int(out.stride(-2)), c_int(bn), c_int(splits), c_int(1 if swiglu else 0),
+                          c_int(1 if raw_parts else 0), _p(err), _stream()), "gemm_tc")
     return out
 
 
 TC_MAX_TOKENS = 64       # up to here the tcgen05 kernel of this package; above, the library product
+
+
+def linear_parts(x: torch.Tensor, w: torch.Tensor, err: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x . w^T for a consumer that adds in float32 (the next norm, the rotary kernel): float32
+    [T, N], or [parts, T, N] when a small bfloat16 step cut K and left the parts unjoined."""
+    if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= TC_MAX_TOKENS
+            and err is not None):
+        y = gemm_tc(x, w, torch.float32, err, raw_parts=True)
+        if y is not None:
+            return y
+    return linear(x, w, torch.float32, err)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
@@ -212,19 +242,23 @@ def rope_kv_write(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     """Rotate q and k by position, write k and v to their pages; returns q [T, H, d].
     k_pages / v_pages: [num_pages, K, page, d] of one layer."""
     _dev(qkv, k_pages, v_pages, positions, token_req, block_table, inv_freq, err)
-    T = qkv.shape[0]
-    if qkv.shape[1] != (H + 2 * K) * d:
+    parts, part_stride = 1, 0
+    if qkv.dim() == 3:            # [parts, T, width] float32: parts of a split product, added here
+        parts, part_stride = qkv.shape[0], qkv.stride(0)
+    T = qkv.shape[-2]
+    if qkv.shape[-1] != (H + 2 * K) * d:
         raise KernelError("rope_kv_write: qkv width differs from (H + 2K) * d")
     num_pages, Kp, P, dp = k_pages.shape
     if (Kp, dp) != (K, d) or v_pages.shape != k_pages.shape:
         raise KernelError("rope_kv_write: page shape does not fit (K, d)")
-    if k_pages.dtype != qkv.dtype:
-        raise KernelError("rope_kv_write: cache dtype differs from the activations'")
+    if qkv.dtype != k_pages.dtype and qkv.dtype != torch.float32:
+        raise KernelError("rope_kv_write: qkv must be in the cache's dtype or float32")
     rot = inv_freq.shape[0] * 2
     if q_out is None:
-        q_out = torch.empty((T, H, d), dtype=qkv.dtype, device=qkv.device)
+        q_out = torch.empty((T, H, d), dtype=k_pages.dtype, device=qkv.device)
     lib = library("rope_kv.cu")
-    check(lib.aie_rope_kv_write(_p(qkv), _p(q_out), _p(k_pages), _p(v_pages), c_int(dtype_code(qkv)),
+    check(lib.aie_rope_kv_write(_p(qkv), c_int(dtype_code(qkv)), c_int(parts), c_longlong(part_stride),
+                                _p(q_out), _p(k_pages), _p(v_pages), c_int(dtype_code(k_pages)),
                                 _p(positions), _p(token_req), _p(block_table),
                                 c_int(block_table.shape[1]), c_int(num_pages), c_int(P), c_int(T),
                                 c_int(H), c_int(K), c_int(d), c_int(rot), _p(inv_freq),

@@ -69,7 +69,7 @@ class Part:
 class Mixer(Part):
     """Mixes information across a request's tokens.  forward(h [T, hidden],
     ctx, cache) -> [T, hidden], float32 or the compute dtype (the next norm adds it to
-    the float32 residual stream).  A part whose forward reads
+    the float32 residual stream); float32 [parts, T, hidden] is taken too and summed there.  A part whose forward reads
     the step's host-side arrays (ctx.h_*) sets `host_side = True`; a model with such
     a part is never replayed from a captured CUDA graph."""
 

@@ -46,4 +46,4 @@ class SwiGLU(FeedForward):
 
     def forward(self, h, ctx):
         a = ops.linear_swiglu(h, self.w_gu, self.block, ctx.err if ctx is not None else None)
-        return ops.linear(a, self.w_down, torch.float32, ctx.err if ctx is not None else None)     # the branch joins the residual in float32
+        return ops.linear_parts(a, self.w_down, ctx.err if ctx is not None else None)   # joins the residual in float32

@@ -103,3 +103,27 @@ def test_linear_picks_the_kernel_by_step_size():
         assert y.dtype == torch.float32 and (y.double() - want).abs().max() <= 3e-5 * max(1.0, float(want.abs().max()))
     x = torch.randn(4, 100, device=DEV).bfloat16()          # K % 8 != 0: the library product stands in
     assert ops.linear(x, torch.randn(32, 100, device=DEV).bfloat16(), None, err).shape == (4, 32)
+
+
+def test_raw_parts_are_summed_by_the_norm_and_rotary_kernels():
+    """A split product may leave its parts unjoined: [parts, T, N] float32; the consumer adds them."""
+    import plain_llama as pl
+    from ai_engine_b200.kernels import ops
+
+    torch.manual_seed(9)
+    T, K, D = 8, 4096, 512
+    x = torch.randn(T, K, device=DEV).bfloat16()
+    w = (torch.randn(D, K, device=DEV) * 0.05).bfloat16()
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    parts = ops.gemm_tc(x, w, torch.float32, err, splits=4, raw_parts=True)
+    assert parts.shape == (4, T, D) and parts.dtype == torch.float32
+    want = x.double() @ w.double().T
+    assert (parts.double().sum(0) - want).abs().max() <= 3e-5 * float(want.abs().max())
+    resid = torch.randn(T, D, device=DEV)
+    nw = (1 + 0.1 * torch.randn(D, device=DEV)).bfloat16()
+    r2 = resid.clone()
+    h = ops.add_rmsnorm(r2, parts, nw, 1e-5, torch.bfloat16)
+    s = resid.double() + want
+    assert (r2.double() - s).abs().max() <= 1e-4
+    assert (h.double() - pl.rms_norm(s.cpu(), nw.double().cpu(), 1e-5).to(DEV)).abs().max() <= 3e-2
+    assert int(err.item()) == 0

@@ -120,7 +120,7 @@ def time_decode(torch, aie, model, batch, prompt_len, steps, warmup, ctx_cap):
         out = one(i)
     tokens = out.cpu().tolist()
     torch.cuda.synchronize()
-    l0 = LAUNCHES[0]
+    l0, g0 = LAUNCHES[0], runner.graph_launches
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for i in range(steps):
@@ -129,7 +129,7 @@ def time_decode(torch, aie, model, batch, prompt_len, steps, warmup, ctx_cap):
     torch.cuda.synchronize()
     ms = start.elapsed_time(end) / steps
     runner.check_errors()
-    launches = LAUNCHES[0] - l0
+    launches = LAUNCHES[0] - l0 + runner.graph_launches - g0      # launched afresh + replayed from graphs
     ctx_tokens = batch * (prompt_len + warmup + steps / 2.0)
     bytes_step = model.step_weight_bytes() + cache.kv_bytes_per_token() * ctx_tokens
     del cache, runner

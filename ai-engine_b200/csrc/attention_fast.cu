@@ -56,7 +56,7 @@ extern "C" int aie_paged_attention_decode(const void* q, const void* k_pages, co
 // ---------------------------------------------------------------------------
 #include "attention_prefill.cuh"
 
-// tiles: [n_tiles][2] = (request row, offset of the 64-token tile within the request's tokens)
+// tiles: [n_tiles][2] = (request row, offset of the 128-token tile within the request's tokens)
 extern "C" int aie_paged_attention_prefill(const void* q, const void* k_pages, const void* v_pages, void* out,
                                            const int* tiles, int n_tiles, const int* q_start, const int* q_len,
                                            const int* ctx_len, const int* block_table, int bt_width,

@@ -1,8 +1,8 @@
-// bfloat16 paged attention for portions of prompts: tiles of 64 query tokens of one
+// bfloat16 paged attention for portions of prompts: tiles of 128 query tokens of one
 // head against 64-key tiles of the request's cache, tensor-core products
 // (mma.sync m16n8k16, bf16 in, float32 accumulate), online softmax in float32.
 //
-// One CTA of four warps owns one (request, 64-token tile, query head); each warp
+// One CTA of eight warps owns one (request, 128-token tile, query head); each warp
 // owns 16 query rows.  Keys and values are gathered page by page through the block
 // table into shared memory with 16-byte cp.async copies (two buffers: the next tile
 // loads while this one is multiplied), in an XOR-swizzled layout that ldmatrix
@@ -14,9 +14,9 @@
 #pragma once
 #include "common.cuh"
 
-#define PF_M 64
+#define PF_M 128
 #define PF_N 64
-#define PF_WARPS 4
+#define PF_WARPS 8
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) {
     return (unsigned)__cvta_generic_to_shared(p);
@@ -65,7 +65,7 @@ paged_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_page
     constexpr int CH = D / 8;       // 16-byte chunks per row
     constexpr int KS = D / 16;      // k-steps of q.k
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);            // [64][D]
+    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);            // [128][D]
     bf16* k_s = q_s + PF_M * D;                                // [2][64][D]
     bf16* v_s = k_s + 2 * PF_N * D;                            // [2][64][D]
     int* row_s = reinterpret_cast<int*>(v_s + 2 * PF_N * D);   // [2][64] page rows of the tile's keys

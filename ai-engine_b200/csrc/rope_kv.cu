@@ -23,11 +23,13 @@ __global__ void rope_kv_write_kernel(const I* __restrict__ qkv, int parts, size_
                                      int num_pages, int P, int H, int K, int d, int rot_dim,
                                      const float* __restrict__ inv_freq, int write,
                                      unsigned* err) {
-    // one block per (token, head slot): slots [0, H) are q heads, [H, H+K) k heads,
-    // [H+K, H+2K) v heads; threads walk the head's rotated pairs, then its other elements
+    // one warp per (token, head slot): slots [0, H) are q heads, [H, H+K) k heads,
+    // [H+K, H+2K) v heads; lanes walk the head's rotated pairs, then its other elements
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x, slot_h = blockIdx.y;
+    const int t = blockIdx.x, slot_h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (slot_h >= H + 2 * K) return;
+    const int lane = threadIdx.x & 31;
     const int pos = positions[t];
     const int half = rot_dim / 2;
     const I* x = qkv + (size_t)t * (H + 2 * K) * d + (size_t)slot_h * d;
@@ -47,17 +49,17 @@ __global__ void rope_kv_write_kernel(const I* __restrict__ qkv, int parts, size_
         const int pidx = pos / P;
         const int page = (pidx < bt_width && pos >= 0) ? block_table[(size_t)row * bt_width + pidx] : -1;
         if (page < 0 || page >= num_pages) {
-            if (threadIdx.x == 0) atomicOr(err, AIE_DEV_PAGE_OOB);
+            if (lane == 0) atomicOr(err, AIE_DEV_PAGE_OOB);
             return;
         }
         const int kh = is_v ? slot_h - H - K : slot_h - H;
         ko = (is_v ? v_pages : k_pages) + (((size_t)page * K + kh) * P + (pos % P)) * d;
     }
     if (is_v) {
-        for (int e = threadIdx.x; e < d; e += blockDim.x) ko[e] = from_f32<C>(in(e));
+        for (int e = lane; e < d; e += 32) ko[e] = from_f32<C>(in(e));
         return;
     }
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    for (int i = lane; i < half; i += 32) {
         const float ang = (float)pos * inv_freq[i];
         float sn, cs;
         sincosf(ang, &sn, &cs);
@@ -72,7 +74,7 @@ __global__ void rope_kv_write_kernel(const I* __restrict__ qkv, int parts, size_
             ko[i + half] = from_f32<C>(o2);
         }
     }
-    for (int e = rot_dim + threadIdx.x; e < d; e += blockDim.x) {      // elements that are not rotated
+    for (int e = rot_dim + lane; e < d; e += 32) {      // elements that are not rotated
         const float v = in(e);
         if (is_q) qo[e] = from_f32<A>(v);
         else ko[e] = from_f32<C>(v);
@@ -86,9 +88,11 @@ extern "C" int aie_rope_kv_write(const void* qkv, int in_dtype, int parts, long 
                                  int write, unsigned* err, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (rot_dim % 2 || rot_dim > d || rot_dim < 0) return AIE_BAD_ARG;
-    if (H + 2 * K > 65535) return AIE_UNSUPPORTED;
-    const dim3 grid(T, H + 2 * K);
-    const int threads = d >= 128 ? 64 : 32;
+    // few tokens: one warp per block, so that the work spreads over the machine; many: 8 warps
+    const int warps = T >= 256 ? 8 : 1;
+    if ((H + 2 * K + warps - 1) / warps > 65535) return AIE_UNSUPPORTED;
+    const dim3 grid(T, (H + 2 * K + warps - 1) / warps);
+    const int threads = 32 * warps;
     if (parts < 1 || (parts > 1 && in_dtype != AIE_F32)) return AIE_BAD_ARG;
 #define ARGS positions, token_req, block_table, bt_width, num_pages, P, H, K, d, rot_dim, inv_freq, write, err
     cudaError_t e;

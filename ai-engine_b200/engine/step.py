@@ -19,6 +19,8 @@ from typing import List, Optional, Sequence
 import numpy as np
 import torch
 
+from ..kernels.ops import PREFILL_TILE
+
 
 @dataclass
 class StepEntry:
@@ -123,7 +125,7 @@ class StepContext:
         self.max_decode_len = int((ctx_len[is_dec] + 1).max()) if self.n_decode else 0
         if bucket_width and self.n_decode:
             self.max_decode_len = width * cache.page_size      # a property of the layout, not of the step
-        tiles = [(r, o) for r in range(R) if q_len[r] != 1 for o in range(0, int(q_len[r]), 64)]
+        tiles = [(r, o) for r in range(R) if q_len[r] != 1 for o in range(0, int(q_len[r]), PREFILL_TILE)]
         arrays = [token_ids.astype(np.int32), positions, token_req, dec.astype(np.int32), other,
                   np.asarray(tiles, dtype=np.int32).reshape(-1), q_start, q_len, ctx_len, slots,
                   np.asarray(rows, dtype=np.int32)] + [tb.reshape(-1) for tb in tables]

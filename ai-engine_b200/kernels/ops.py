@@ -188,15 +188,17 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, err: torch
 TC_MAX_TOKENS = 64       # up to here the tcgen05 kernel of this package; above, the library product
 
 
-def linear_parts(x: torch.Tensor, w: torch.Tensor, err: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x . w^T for a consumer that adds in float32 (the next norm, the rotary kernel): float32
-    [T, N], or [parts, T, N] when a small bfloat16 step cut K and left the parts unjoined."""
+def linear_parts(x: torch.Tensor, w: torch.Tensor, err: Optional[torch.Tensor] = None,
+                 out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """x . w^T for a consumer that can add parts (the next norm, the rotary kernel): float32
+    [parts, T, N] when a small bfloat16 step cut K and left the parts unjoined, else [T, N]
+    in `out_dtype`."""
     if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= TC_MAX_TOKENS
             and err is not None):
         y = gemm_tc(x, w, torch.float32, err, raw_parts=True)
         if y is not None:
             return y
-    return linear(x, w, torch.float32, err)
+    return linear(x, w, out_dtype, err)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
@@ -326,10 +328,13 @@ def paged_attention_decode(q, k_pages, v_pages, dec_tokens, positions, token_req
                                          _stream()), "paged_attention_decode")
 
 
+PREFILL_TILE = 128       # query tokens per CTA of the tensor-core attention kernel
+
+
 def paged_attention_prefill(q, k_pages, v_pages, tiles, q_start, q_len, ctx_len, block_table,
                             scale: float, window: int, err, out) -> None:
     """bfloat16 tensor-core attention for requests that bring more than one token.
-    `tiles`: int32 [n, 2] = (request row, offset of a 64-token tile in its tokens).
+    `tiles`: int32 [n, 2] = (request row, offset of a PREFILL_TILE-token tile in its tokens).
     Head sizes 64 and 128."""
     _dev(q, k_pages, v_pages, tiles, q_start, q_len, ctx_len, block_table, err, out)
     T, H, d = q.shape

@@ -64,8 +64,7 @@ class GQAAttention(Mixer):
         return KVRequest(self.K, self.d, self.window)
 
     def forward(self, h, ctx, cache):
-        qkv = ops.linear_parts(h, self.w_qkv, ctx.err) if h.dtype == torch.bfloat16 \
-            else ops.linear(h, self.w_qkv, self.env.dtype, ctx.err)
+        qkv = ops.linear_parts(h, self.w_qkv, ctx.err, self.env.dtype)
         inv_freq = self.rope.inv_freq if self.rope is not None else self._no_rope
         q = ops.rope_kv_write(qkv, cache.k_pages, cache.v_pages, ctx.positions, ctx.token_req,
                               cache.block_table, inv_freq, self.H, self.K, self.d, ctx.err,

@@ -233,7 +233,7 @@ def test_paged_attention_prefill_tensor_cores(shape):
     out = torch.full_like(s["q"], float("nan"))
     i32 = lambda a: torch.tensor(a, device=DEV, dtype=torch.int32)
     q_start = np.concatenate([[0], np.cumsum(q_lens)[:-1]])
-    tiles = [(r, o) for r, n in enumerate(q_lens) for o in range(0, n, 64)]
+    tiles = [(r, o) for r, n in enumerate(q_lens) for o in range(0, n, ops().PREFILL_TILE)]
     ops().paged_attention_prefill(s["q"], s["k_pages"], s["v_pages"], i32(tiles), i32(q_start), i32(q_lens),
                                   i32([n - ql for n, ql in zip(lens, q_lens)]), s["bt"], scale, window, e, out)
     want = attention_reference(s, H, K, d, scale, window)

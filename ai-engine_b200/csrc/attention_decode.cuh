@@ -8,11 +8,30 @@
 #define DEC_WARPS 4
 #define DEC_TILE 16          // keys a warp stages and consumes at a time
 #define DEC_MAX_PAGES 2048   // block-table entries of one CTA's part of the keys
+#define DEC_HEADS 8          // query heads of one kv head that a CTA takes (rows of the 16-row MMA)
 
 __device__ __forceinline__ void dec_cp_async16(void* dst, const void* src, bool pred) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
     const int n = pred ? 16 : 0;   // 0 source bytes: the destination is zero-filled
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void dec_ldsm_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"((unsigned)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void dec_ldsm_x4_t(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"((unsigned)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void dec_mma(float* c, unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                        unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned dec_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
 }
 
 // Shared memory of the decode kernel for head size D with NST stages per warp.
@@ -21,28 +40,35 @@ template <int D, int NST> struct DecodeSmem {
     static constexpr size_t bytes = DEC_WARPS * NST * stage_bytes + DEC_MAX_PAGES * sizeof(int);
 };
 
-template <int D, int GC, int NST>
+// row r, 16-byte chunk c of a [16][D] bf16 tile, XOR-swizzled so that ldmatrix reads without conflicts
+template <int D> __device__ __forceinline__ bf16* dec_at(bf16* base, int row, int chunk) {
+    return base + row * D + ((chunk ^ (row & 7)) << 3);
+}
+
+// The query heads are rows 0 .. ng-1 of a 16-row mma.sync tile (rows up to 15 are padding): per
+// 16-key tile, q.k is 2 x D/16 multiplies and p.v is D/8, both bf16 in / float32 accumulate.
+template <int D, int NST>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
                     const bf16* __restrict__ v_pages, bf16* __restrict__ out,
                     float* __restrict__ part_o, float* __restrict__ part_lse,
                     const int* __restrict__ dec_tokens, const int* __restrict__ positions,
                     const int* __restrict__ token_req, const int* __restrict__ block_table,
-                    int bt_width, int num_pages, int P, int H, int K, int G, int window,
-                    float scale, int S, unsigned* err) {
-    constexpr int EPL = D / 8;      // elements of a key each of its 8 lanes holds
-    constexpr int NCH = EPL / 8;    // 16-byte chunks per lane
-    constexpr int VPL = D / 32;     // output elements per lane
+                    int bt_width, int num_pages, int P, int H, int K, int G, int GC, int window,
+                    float scale, int S, int* __restrict__ counters, unsigned* err) {
     constexpr int CH = D / 8;       // 16-byte chunks per row
     constexpr int KPL = 32 / CH;    // keys one round of 32 copies covers
+    constexpr int KS = D / 16;      // k-steps of q.k
     static_assert(D % 64 == 0, "head size of the fast path");
     extern __shared__ __align__(128) unsigned char dec_smem[];
-    __shared__ float p_s[DEC_WARPS][DEC_TILE][GC];
     __shared__ int ok_s[DEC_WARPS][NST][DEC_TILE];
-    __shared__ float mrg_m[DEC_WARPS][GC], mrg_l[DEC_WARPS][GC];
+    __shared__ float mrg_m[DEC_WARPS][DEC_HEADS], mrg_l[DEC_WARPS][DEC_HEADS];
 
+    // Everything up to the first use of q reads only what earlier steps left (the step's index
+    // arrays, the block table, keys and values of earlier tokens), so it runs before
+    // griddepcontrol.wait, while the kernel that writes q and this token's key is still running.
     pdl_launch_dependents();
-    pdl_wait();
+    bool waited = false;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int s = blockIdx.x, di = blockIdx.z;
     const int gchunks = (G + GC - 1) / GC;
@@ -51,7 +77,7 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     const int t = dec_tokens[di];
     const int pos = positions[t], row = token_req[t];
     const int hbase = kvh * G + g0;
-    const int sub = lane & 7, kg = lane >> 3;
+    const int qrow = lane >> 2, qcol = (lane & 3) * 2;      // this lane's row and column pair of an MMA tile
 
     bf16* stage0 = reinterpret_cast<bf16*>(dec_smem) + (size_t)warp * NST * 2 * DEC_TILE * D;
     int* bt_s = reinterpret_cast<int*>(dec_smem + DEC_WARPS * NST * DecodeSmem<D, NST>::stage_bytes);
@@ -72,30 +98,7 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         for (int i = tid; i < npg && i < DEC_MAX_PAGES; i += DEC_WARPS * 32)
             bt_s[i] = (pg0 + i < bt_width) ? bt[pg0 + i] : -1;
     }
-
-    // this lane's slice of every query head, float32
-    float qr[GC][EPL];
-#pragma unroll
-    for (int g = 0; g < GC; ++g) {
-        const bf16* qp = q + ((size_t)t * H + hbase + (g < ng ? g : 0)) * D;
-#pragma unroll
-        for (int j = 0; j < NCH; ++j) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(qp + (sub + 8 * j) * 8);
-            const bf16* e = reinterpret_cast<const bf16*>(&raw);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) qr[g][j * 8 + i] = g < ng ? __bfloat162float(e[i]) : 0.f;
-        }
-    }
     __syncthreads();
-
-    float m[GC], l[GC], acc[GC][VPL];
-#pragma unroll
-    for (int g = 0; g < GC; ++g) {
-        m[g] = -INFINITY;
-        l[g] = 0.f;
-#pragma unroll
-        for (int e = 0; e < VPL; ++e) acc[g][e] = 0.f;
-    }
 
     const int first = tile_begin + warp;
     const int n_my = first < tile_end ? (tile_end - first + DEC_WARPS - 1) / DEC_WARPS : 0;
@@ -105,6 +108,10 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         if (i < n_my) {
             const int st = i % NST;
             const int kbase = lo + (first + i * DEC_WARPS) * DEC_TILE;
+            if (!waited && kbase + DEC_TILE > pos) {      // this tile holds the token written in this step
+                pdl_wait();
+                waited = true;
+            }
             int prow = -1;
             if (lane < DEC_TILE) {
                 const int key = kbase + lane;
@@ -124,8 +131,8 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
                 const int kidx = kq + r * KPL;
                 const int pr = __shfl_sync(0xffffffffu, prow, kidx);
                 const size_t off = (size_t)(pr >= 0 ? pr : 0) * D + cc * 8;
-                dec_cp_async16(ks + kidx * D + cc * 8, k_pages + off, pr >= 0);
-                dec_cp_async16(vs + kidx * D + cc * 8, v_pages + off, pr >= 0);
+                dec_cp_async16(dec_at<D>(ks, kidx, cc), k_pages + off, pr >= 0);
+                dec_cp_async16(dec_at<D>(vs, kidx, cc), v_pages + off, pr >= 0);
             }
         }
         asm volatile("cp.async.commit_group;\n" ::);
@@ -133,102 +140,104 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
 
 #pragma unroll
     for (int i = 0; i < NST - 1; ++i) issue(i);
+    if (!waited) {
+        pdl_wait();
+        waited = true;
+    }
+
+    // q as the A operand: row = head, rows >= ng (and 8..15) are zero
+    unsigned qa[KS][2];
+    {
+        const bf16* qp = q + ((size_t)t * H + hbase + (qrow < ng ? qrow : 0)) * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const unsigned lo2 = *reinterpret_cast<const unsigned*>(qp + ks * 16 + qcol);
+            const unsigned hi2 = *reinterpret_cast<const unsigned*>(qp + ks * 16 + 8 + qcol);
+            qa[ks][0] = qrow < ng ? lo2 : 0u;
+            qa[ks][1] = qrow < ng ? hi2 : 0u;
+        }
+    }
+    float m_run = -INFINITY, l_run = 0.f;      // of row qrow (valid when qrow < ng)
+    float o[D / 8][4];
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
 
     for (int i = 0; i < n_my; ++i) {
         issue(i + NST - 1);
         asm volatile("cp.async.wait_group %0;\n" ::"n"(NST - 1));
         __syncwarp();
         const int st = i % NST;
-        const bf16* ks = stage0 + (size_t)st * 2 * DEC_TILE * D;
-        const bf16* vs = ks + DEC_TILE * D;
+        bf16* ks_t = stage0 + (size_t)st * 2 * DEC_TILE * D;
+        bf16* vs_t = ks_t + DEC_TILE * D;
 
-        float sc[DEC_TILE / 4][GC];
-        float tmax[GC];
+        // scores of the 16 keys: two 8-key column tiles
+        float sc[2][4];
 #pragma unroll
-        for (int g = 0; g < GC; ++g) tmax[g] = -INFINITY;
+        for (int j = 0; j < 2; ++j)
 #pragma unroll
-        for (int it = 0; it < DEC_TILE / 4; ++it) {
-            const int kidx = it * 4 + kg;
-            const bool valid = ok_s[warp][st][kidx] != 0;
-            float dot[GC];
+            for (int e = 0; e < 4; ++e) sc[j][e] = 0.f;
+        const int mid = lane >> 3;
 #pragma unroll
-            for (int g = 0; g < GC; ++g) dot[g] = 0.f;
-#pragma unroll
-            for (int j = 0; j < NCH; ++j) {
-                const uint4 raw = *reinterpret_cast<const uint4*>(ks + kidx * D + (sub + 8 * j) * 8);
-                const bf16* e = reinterpret_cast<const bf16*>(&raw);
-#pragma unroll
-                for (int x = 0; x < 8; ++x) {
-                    const float kv = __bfloat162float(e[x]);
-#pragma unroll
-                    for (int g = 0; g < GC; ++g) dot[g] = fmaf(qr[g][j * 8 + x], kv, dot[g]);
-                }
-            }
-#pragma unroll
-            for (int g = 0; g < GC; ++g) {
-                float d = dot[g];
-                d += __shfl_xor_sync(0xffffffffu, d, 1);
-                d += __shfl_xor_sync(0xffffffffu, d, 2);
-                d += __shfl_xor_sync(0xffffffffu, d, 4);
-                sc[it][g] = valid ? d * scale : -INFINITY;
-                tmax[g] = fmaxf(tmax[g], sc[it][g]);
-            }
+        for (int ks = 0; ks < KS; ++ks) {
+            unsigned b0, b1, b2, b3;
+            dec_ldsm_x4(b0, b1, b2, b3, dec_at<D>(ks_t, (mid >> 1) * 8 + (lane & 7), ks * 2 + (mid & 1)));
+            dec_mma(sc[0], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+            dec_mma(sc[1], qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
         }
+        float tmax = -INFINITY;
 #pragma unroll
-        for (int g = 0; g < GC; ++g) {
-            float tm = tmax[g];
-            tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 8));
-            tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 16));
-            const float m_new = fmaxf(m[g], tm);
-            const float corr = (m[g] == -INFINITY) ? 0.f : __expf(m[g] - m_new);
-            float psum = 0.f;
+        for (int j = 0; j < 2; ++j)
 #pragma unroll
-            for (int it = 0; it < DEC_TILE / 4; ++it) {
-                const float p = (sc[it][g] == -INFINITY) ? 0.f : __expf(sc[it][g] - m_new);
-                psum += p;
-                if (sub == 0) p_s[warp][it * 4 + kg][g] = p;
+            for (int e = 0; e < 2; ++e) {
+                const bool valid = ok_s[warp][st][j * 8 + qcol + e] != 0;
+                sc[j][e] = valid ? sc[j][e] * scale : -INFINITY;
+                tmax = fmaxf(tmax, sc[j][e]);
             }
-            psum += __shfl_xor_sync(0xffffffffu, psum, 8);
-            psum += __shfl_xor_sync(0xffffffffu, psum, 16);
-            l[g] = l[g] * corr + psum;
-            m[g] = m_new;
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+        const float m_new = fmaxf(m_run, tmax);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float corr = (m_run == -INFINITY) ? 0.f : __expf(m_run - m_use);
+        float p[2][2], psum = 0.f;
 #pragma unroll
-            for (int e = 0; e < VPL; ++e) acc[g][e] *= corr;
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                p[j][e] = __expf(sc[j][e] - m_use);       // exp(-inf) = 0 for a key that is not there
+                psum += p[j][e];
+            }
+        psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+        psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+        l_run = l_run * corr + psum;
+        m_run = m_new;
+        const unsigned pa0 = dec_pack(p[0][0], p[0][1]), pa2 = dec_pack(p[1][0], p[1][1]);
+#pragma unroll
+        for (int jd = 0; jd < D / 8; jd += 2) {
+            o[jd][0] *= corr;
+            o[jd][1] *= corr;
+            o[jd + 1][0] *= corr;
+            o[jd + 1][1] *= corr;
+            unsigned b0, b1, b2, b3;
+            dec_ldsm_x4_t(b0, b1, b2, b3, dec_at<D>(vs_t, (mid & 1) * 8 + (lane & 7), jd + (mid >> 1)));
+            dec_mma(o[jd], pa0, 0u, pa2, 0u, b0, b1);
+            dec_mma(o[jd + 1], pa0, 0u, pa2, 0u, b2, b3);
         }
-        __syncwarp();
-#pragma unroll
-        for (int kk = 0; kk < DEC_TILE; ++kk) {
-            float v[VPL];
-            if (VPL == 4) {
-                const uint2 raw = *reinterpret_cast<const uint2*>(vs + kk * D + lane * VPL);
-                const bf16* e = reinterpret_cast<const bf16*>(&raw);
-#pragma unroll
-                for (int x = 0; x < VPL; ++x) v[x] = __bfloat162float(e[x]);
-            } else {
-                const unsigned raw = *reinterpret_cast<const unsigned*>(vs + kk * D + lane * VPL);
-                const bf16* e = reinterpret_cast<const bf16*>(&raw);
-#pragma unroll
-                for (int x = 0; x < VPL; ++x) v[x] = __bfloat162float(e[x]);
-            }
-#pragma unroll
-            for (int g = 0; g < GC; ++g) {
-                const float p = p_s[warp][kk][g];     // 0 for a key that is not there (its row is zero too)
-#pragma unroll
-                for (int e = 0; e < VPL; ++e) acc[g][e] = fmaf(p, v[e], acc[g][e]);
-            }
-        }
-        __syncwarp();      // the stage and p_s are free again
+        __syncwarp();      // the stage is free again
     }
     asm volatile("cp.async.wait_group 0;\n" ::);
     __syncthreads();
 
     // merge the warps of the CTA (the staging memory is free now: reuse it for the partial outputs)
-    float* mrg_o = reinterpret_cast<float*>(dec_smem);      // [DEC_WARPS][GC][D]
+    float* mrg_o = reinterpret_cast<float*>(dec_smem);      // [DEC_WARPS][DEC_HEADS][D]
+    if (qrow < DEC_HEADS) {
+        if ((lane & 3) == 0) { mrg_m[warp][qrow] = m_run; mrg_l[warp][qrow] = l_run; }
 #pragma unroll
-    for (int g = 0; g < GC; ++g) {
-        if (lane == 0) { mrg_m[warp][g] = m[g]; mrg_l[warp][g] = l[g]; }
-#pragma unroll
-        for (int e = 0; e < VPL; ++e) mrg_o[((size_t)warp * GC + g) * D + lane * VPL + e] = acc[g][e];
+        for (int jd = 0; jd < D / 8; ++jd) {
+            mrg_o[((size_t)warp * DEC_HEADS + qrow) * D + jd * 8 + qcol] = o[jd][0];
+            mrg_o[((size_t)warp * DEC_HEADS + qrow) * D + jd * 8 + qcol + 1] = o[jd][1];
+        }
     }
     __syncthreads();
     for (int idx = tid; idx < ng * D; idx += DEC_WARPS * 32) {
@@ -241,16 +250,48 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         for (int w = 0; w < DEC_WARPS; ++w) {
             const float f = (mrg_m[w][g] == -INFINITY) ? 0.f : __expf(mrg_m[w][g] - M);
             L += mrg_l[w][g] * f;
-            A += mrg_o[((size_t)w * GC + g) * D + e] * f;
+            A += mrg_o[((size_t)w * DEC_HEADS + g) * D + e] * f;
         }
-        const float o = L > 0.f ? A / L : 0.f;
+        const float ov = L > 0.f ? A / L : 0.f;
         const int h = hbase + g;
         if (S == 1) {
-            out[((size_t)t * H + h) * D + e] = __float2bfloat16_rn(o);
+            out[((size_t)t * H + h) * D + e] = __float2bfloat16_rn(ov);
         } else {
             const size_t pi = ((size_t)di * H + h) * S + s;
-            part_o[pi * D + e] = o;
+            part_o[pi * D + e] = ov;
             if (e == 0) part_lse[pi] = L > 0.f ? M + __logf(L) : -INFINITY;
+        }
+    }
+    if (S > 1 && counters != nullptr) {
+        // the CTA that finishes last among the S parts of this (request, kv head, head chunk)
+        // joins them: out = sum_s w_s * part_o[s] / sum_s w_s with w_s = exp(lse_s - max lse)
+        __shared__ int last_s;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            int* c = counters + (size_t)di * gridDim.y + blockIdx.y;
+            const int ticket = atomicAdd(c, 1);
+            last_s = ticket == S - 1;
+            if (last_s) *c = 0;                       // ready for the next launch
+        }
+        __syncthreads();
+        if (last_s) {
+            __threadfence();
+            for (int idx = tid; idx < ng * D; idx += DEC_WARPS * 32) {
+                const int g = idx / D, e = idx % D;
+                const int h = hbase + g;
+                const size_t base = ((size_t)di * H + h) * S;
+                float M = -INFINITY;
+                for (int sp = 0; sp < S; ++sp) M = fmaxf(M, __ldcg(part_lse + base + sp));
+                float A = 0.f, W = 0.f;
+                for (int sp = 0; sp < S; ++sp) {
+                    const float lse = __ldcg(part_lse + base + sp);
+                    const float w = (lse == -INFINITY) ? 0.f : __expf(lse - M);
+                    W += w;
+                    A += w * __ldcg(part_o + (base + sp) * D + e);
+                }
+                out[((size_t)t * H + h) * D + e] = __float2bfloat16_rn(W > 0.f ? A / W : 0.f);
+            }
         }
     }
 }
@@ -282,23 +323,12 @@ template <int D>
 static int launch_decode(int GC, dim3 grid, cudaStream_t st, const bf16* q, const bf16* kp, const bf16* vp,
                          bf16* out, float* po, float* pl, const int* dt, const int* pos, const int* tr,
                          const int* bt, int btw, int np, int P, int H, int K, int G, int window, float scale,
-                         int S, unsigned* err) {
+                         int S, int* counters, unsigned* err) {
+    if (GC < 1 || GC > DEC_HEADS) return AIE_UNSUPPORTED;
     constexpr int NST = D >= 128 ? 3 : 4;
     constexpr size_t smem = DecodeSmem<D, NST>::bytes;
-#define GO(GCV)                                                                                                   \
-    do {                                                                                                          \
-        auto kern = paged_decode_kernel<D, GCV, NST>;                                                             \
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                       \
-        launch_pdl(kern, grid, dim3(DEC_WARPS * 32), smem, st, q, kp, vp, out, po, pl, dt, pos, tr, bt, btw, np, \
-                   P, H, K, G, window, scale, S, err);                                                            \
-    } while (0)
-    switch (GC) {
-        case 1: GO(1); break;
-        case 2: GO(2); break;
-        case 3: GO(3); break;
-        case 4: GO(4); break;
-        default: return AIE_UNSUPPORTED;
-    }
-#undef GO
-    return 0;
+    auto kern = paged_decode_kernel<D, NST>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return (int)launch_pdl(kern, grid, dim3(DEC_WARPS * 32), smem, st, q, kp, vp, out, po, pl, dt, pos, tr, bt, btw, np,
+                           P, H, K, G, GC, window, scale, S, counters, err);
 }

@@ -25,7 +25,7 @@ extern "C" int aie_paged_attention_decode_noalloc(const void* q, const void* k_p
     if (K <= 0 || H <= 0 || H % K || S < 1) return AIE_BAD_ARG;
     if (d != 64 && d != 128) return AIE_UNSUPPORTED;
     const int G = H / K;
-    const int GC = G >= 4 ? 4 : G;
+    const int GC = G >= DEC_HEADS ? DEC_HEADS : G;
     const int gchunks = (G + GC - 1) / GC;
     if (K * gchunks > 65535 || n_dec > 65535) return AIE_UNSUPPORTED;
     if ((bt_width + S - 1) / S + 2 > DEC_MAX_PAGES) return AIE_UNSUPPORTED;   // more splits needed
@@ -55,11 +55,11 @@ extern "C" int aie_paged_attention_decode_noalloc(const void* q, const void* k_p
     if (d == 64)
         rc = launch_decode<64>(GC, grid, stream, (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages,
                                (bf16*)out, part_o, part_lse, dec_tokens, positions, token_req, block_table,
-                               bt_width, num_pages, P, H, K, G, window, scale, S, err);
+                               bt_width, num_pages, P, H, K, G, window, scale, S, nullptr, err);
     else
         rc = launch_decode<128>(GC, grid, stream, (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages,
                                 (bf16*)out, part_o, part_lse, dec_tokens, positions, token_req, block_table,
-                                bt_width, num_pages, P, H, K, G, window, scale, S, err);
+                                bt_width, num_pages, P, H, K, G, window, scale, S, nullptr, err);
     if (rc) return rc;
     if (S > 1) {
         // every (token, head, part) slot of the scratch that this reduce reads was

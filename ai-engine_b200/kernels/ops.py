@@ -301,31 +301,47 @@ def decode_splits(n_dec: int, kv_heads: int, group: int, max_keys: int, bt_width
     """How many parts to cut each decode request's keys into so that the grid fills
     the machine (two CTAs fit on each of the 148 SMs), with parts of at least 128
     keys, and no part spanning more block-table entries than a CTA keeps."""
-    ctas = n_dec * kv_heads * ((group + 3) // 4)
+    ctas = n_dec * kv_heads * ((group + 7) // 8)
     want = max(1, (2 * 148) // ctas)          # rounded down: one full wave, no short second one
     s = max(1, min(want, (max_keys + 127) // 128, 64))
     return max(s, (bt_width + 1999) // 2000)
 
 
+_DECODE_COUNTERS = {}        # device -> zeroed int32 tickets of the decode kernel (they return to zero)
+
+
+def _decode_counters(device, n: int):
+    t = _DECODE_COUNTERS.get(device)
+    if t is None or t.numel() < n:
+        t = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
+        _DECODE_COUNTERS[device] = t
+    return t
+
+
 def paged_attention_decode(q, k_pages, v_pages, dec_tokens, positions, token_req, block_table,
-                           scale: float, window: int, splits: int, err, out) -> None:
+                           scale: float, window: int, splits: int, err, out,
+                           join_in_kernel: bool = False) -> None:
     """bfloat16 split-KV attention for the tokens in `dec_tokens` (requests that bring
-    one token).  Head sizes 64 and 128.  Uses scratch for the parts when splits > 1."""
+    one token).  Head sizes 64 and 128.  Uses scratch for the parts when splits > 1; they are
+    joined by a second kernel, or (join_in_kernel) by whichever CTA finishes last — measured
+    slightly slower in a decode step, kept for callers that want one launch."""
     _dev(q, k_pages, v_pages, dec_tokens, positions, token_req, block_table, err, out)
     T, H, d = q.shape
     num_pages, K, P, _ = k_pages.shape
     n = dec_tokens.shape[0]
-    part_o = part_lse = None
+    part_o = part_lse = counters = None
     if splits > 1:
         part_o = torch.empty((n, H, splits, d), dtype=torch.float32, device=q.device)
         part_lse = torch.empty((n, H, splits), dtype=torch.float32, device=q.device)
+        if join_in_kernel:
+            counters = _decode_counters(q.device, n * K * ((H // K + 7) // 8))
     lib = library("attention_fast.cu")
     check(lib.aie_paged_attention_decode(_p(q), _p(k_pages), _p(v_pages), _p(out), _p(part_o),
                                          _p(part_lse), _p(dec_tokens), c_int(n), _p(positions),
                                          _p(token_req), _p(block_table), c_int(block_table.shape[1]),
                                          c_int(num_pages), c_int(P), c_int(H), c_int(K), c_int(d),
-                                         c_int(window), c_float(scale), c_int(splits), _p(err),
-                                         _stream()), "paged_attention_decode")
+                                         c_int(window), c_float(scale), c_int(splits), _p(counters),
+                                         _p(err), _stream()), "paged_attention_decode")
 
 
 PREFILL_TILE = 128       # query tokens per CTA of the tensor-core attention kernel

@@ -186,11 +186,13 @@ DECODE_SHAPES = [  # H, K, d, P, lens (one query each, the last token), window, 
     (4, 1, 64, 16, [1, 40, 700], 0, 1),
     (32, 8, 128, 16, [1024, 3, 517, 90], 0, 4),
     (6, 2, 64, 8, [33, 257], 0, 3),
-    (5, 1, 128, 16, [300, 31], 0, 2),          # a group of 5: two CTAs per kv head
+    (5, 1, 128, 16, [300, 31], 0, 2),          # a group of 5
     (8, 1, 64, 32, [129], 0, 7),               # more splits than 32-key tiles in places
     (2, 2, 128, 4, [64, 65, 1], 0, 1),
     (8, 2, 128, 16, [900, 40], 100, 3),        # window
     (24, 8, 128, 16, [2100], 0, 16),
+    (16, 1, 64, 16, [77, 400], 0, 2),          # a group of 16: two CTAs of 8 heads per kv head
+    (10, 1, 128, 8, [530], 0, 5),              # a group of 10: 8 + 2
 ]
 
 
@@ -207,9 +209,16 @@ def test_paged_attention_decode_split_kv(shape):
     want = attention_reference(s, H, K, d, scale, window)
     assert int(e.item()) == 0 and not torch.isnan(out).any()
     assert (out.double() - want).abs().max() <= 2e-2
-    plain = ops().paged_attention_plain(s["q"], s["k_pages"], s["v_pages"], s["positions"], s["token_req"],
-                                        s["bt"], scale, window, e)
-    assert (out.float() - plain.float()).abs().max() <= 1e-2
+    # the parts joined by the CTA that finishes last instead of by a second kernel: the same sums
+    out2 = torch.full_like(s["q"], float("nan"))
+    ops().paged_attention_decode(s["q"], s["k_pages"], s["v_pages"], dec, s["positions"], s["token_req"],
+                                 s["bt"], scale, window, splits, e, out2, join_in_kernel=True)
+    assert torch.equal(out2, out)
+    # and again: the tickets of the first call are back at zero
+    out3 = torch.full_like(s["q"], float("nan"))
+    ops().paged_attention_decode(s["q"], s["k_pages"], s["v_pages"], dec, s["positions"], s["token_req"],
+                                 s["bt"], scale, window, splits, e, out3, join_in_kernel=True)
+    assert torch.equal(out3, out)
 
 
 PREFILL_SHAPES = [  # H, K, d, P, lens, q_lens, window

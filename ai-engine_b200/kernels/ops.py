@@ -143,13 +143,14 @@ def tc_tile(T: int) -> int:
 
 def tc_splits(T: int, N: int, K: int, bn: int) -> int:
     """Parts to cut K into.  A weight with fewer 128-row tiles than the machine has SMs is
-    cut so that the grid comes close to one CTA per SM (each with a deep ring of stages and
-    at least 8 K blocks); a weight with more tiles is not cut."""
+    cut so that the grid comes close to three CTAs per SM (what fits beside each other with
+    4-stage rings), each part at least 4 K blocks of 64; measured with `bench.py --only gemm`:
+    more, shorter CTAs beat fewer with deep rings.  A weight with more tiles is not cut."""
     tiles = ((N + 127) // 128) * ((T + bn - 1) // bn)
     kb = (K + 63) // 64
     if tiles >= 148:
         return 1
-    return max(1, min(148 // tiles, kb // 8 if kb >= 8 else 1))
+    return max(1, min((3 * 148) // tiles, kb // 4 if kb >= 4 else 1))
 
 
 TC_SWIGLU_BLOCK = 64     # gate/up rows per half of a 128-row weight tile

@@ -211,9 +211,9 @@ def time_gemms(torch, tokens):
         x = torch.randn(T, K, device="cuda").bfloat16()
         w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
         impls = {"library": lambda: torch.mm(x, w.t()), "tcgen05": lambda: ops.gemm_tc(x, w, torch.bfloat16, err)}
-        for s_ in (1, 2, 4, 8):
-            if T <= 64 and s_ > 1:
-                impls[f"tcgen05_s{s_}"] = (lambda s_=s_: ops.gemm_tc(x, w, torch.bfloat16, err, splits=s_))
+        for s_ in (2, 3, 4, 6, 9, 13):       # K cut into parts that are left for the consumer to add
+            if T <= 64 and N < 148 * 128:
+                impls[f"tcgen05_p{s_}"] = (lambda s_=s_: ops.gemm_tc(x, w, torch.float32, err, splits=s_, raw_parts=True))
         row = {}
         for iname, fn in impls.items():
             for _ in range(3):

@@ -396,3 +396,44 @@ def test_sampling_distribution_and_large_vocab():
     # the walk is monotone: a larger draw never lands on a more likely token
     vals = [float(base[t]) for t in out]
     assert all(vals[i] >= vals[i + 1] - 1e-6 for i in range(N - 1))
+
+
+@pytest.mark.parametrize("kind", ["decode", "prefill"])
+def test_fast_kernels_find_a_far_key_and_respect_a_window_edge(kind):
+    """One key far back matches the query exactly (score far above the rest): the output must be its
+    value; with a window that ends one key after it, it must not be seen at all."""
+    H, K, d, P, n, far = 8, 2, 128, 16, 700, 37
+    q_len = 1 if kind == "decode" else 5
+    s = paged_setup(torch.bfloat16, H, K, d, P, [n], [q_len], seed=21)
+    pg, sl = int(s["bt"][0, far // P]), far % P
+    s["q"][:] = s["q"] * 0.05
+    s["k_pages"][pg, :, sl] = 0
+    for h in range(H):      # the far key of each kv head points along the sum of its heads' queries
+        s["k_pages"][pg, h // (H // K), sl] += (s["q"][q_len - 1, h].float() * 400).bfloat16()
+    s["ks"][0][far] = s["k_pages"][pg, :, sl]
+    i32 = lambda a: torch.tensor(a, device=DEV, dtype=torch.int32)
+
+    def run(window):
+        out = torch.full_like(s["q"], float("nan"))
+        e = err_word()
+        if kind == "decode":
+            ops().paged_attention_decode(s["q"], s["k_pages"], s["v_pages"], i32([0]), s["positions"], s["token_req"],
+                                         s["bt"], 1.0, window, 3, e, out)
+        else:
+            ops().paged_attention_prefill(s["q"], s["k_pages"], s["v_pages"], i32([[0, 0]]), i32([0]), i32([q_len]),
+                                          i32([n - q_len]), s["bt"], 1.0, window, e, out)
+        assert int(e.item()) == 0
+        return out
+
+    out = run(0)
+    want = attention_reference(s, H, K, d, 1.0, 0)
+    assert (out.double() - want).abs().max() <= 2e-2
+    assert (out[q_len - 1, 0].float() - s["v_pages"][pg, 0, sl].float()).abs().max() < 0.1
+    # the last query sits at n - 1: a window of n - 1 - far keys ends just after the far key
+    w = n - 1 - far
+    out_w = run(w)
+    want_w = attention_reference(s, H, K, d, 1.0, w)
+    assert (out_w.double() - want_w).abs().max() <= 2e-2
+    assert (out_w[q_len - 1, 0].float() - s["v_pages"][pg, 0, sl].float()).abs().max() > 0.3
+    out_w1 = run(w + 1)             # one key wider: the far key is back
+    assert (out_w1[q_len - 1, 0].float() - s["v_pages"][pg, 0, sl].float()).abs().max() < 0.1

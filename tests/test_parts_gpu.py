@@ -256,3 +256,126 @@ def test_windowed_layers_have_pages_of_their_own_and_give_them_back(dtype):
     wg = [g for g, grp in enumerate(cache.groups) if grp.request.window][0]
     assert cache.book.high_water(wg) <= (42 + W) // 8 + 2       # never the whole sequence
     assert cache.book.high_water(1 - wg) == (150 + 7) // 8
+
+
+def _step_ctx(cache, slot, start, n, device=DEV):
+    """A StepContext for one request bringing tokens [start, start + n) (token ids unused)."""
+    from ai_engine_b200.engine.step import StepContext, StepEntry
+
+    err = torch.zeros(1, dtype=torch.int32, device=device)
+    return StepContext([StepEntry(slot, start, [0] * n, [])], cache, torch.device(device), err), err
+
+
+@pytest.mark.parametrize("dtype,H,K,d,window", [(torch.float32, 4, 2, 16, 0), (torch.bfloat16, 6, 2, 64, 0),
+                                                (torch.float32, 5, 1, 32, 11), (torch.bfloat16, 8, 8, 128, 0)])
+def test_attention_part_alone_over_its_cache(dtype, H, K, d, window):
+    """GQAAttention with a rotary encoding, fed in three portions (the last one a single token),
+    against plain attention on the whole sequence."""
+    from ai_engine_b200.cache import PagedCache
+    from ai_engine_b200.parts import BuildEnv, GQAAttention, PartSpec, RotaryEncoding
+
+    torch.manual_seed(H * d)
+    D, S = 96, 45
+    e = env(dtype, D)
+    rope = RotaryEncoding(PartSpec("rotary", dict(rot_dim=d, theta=500000.0, scaling=None)), e)
+    rope.load(None)
+    e.position_encodings["rope"] = rope
+    part = GQAAttention(PartSpec("gqa_attention", dict(hidden_size=D, num_heads=H, num_kv_heads=K, head_dim=d,
+                                                        window=window, scale=None, position_encoding="rope"),
+                                 dict(q="q", k="k", v="v", o="o")), e)
+    # scores with a standard deviation near 1.5 whatever the head size (as in the tiny configurations),
+    # outputs of order 1: bfloat16 rounding then stays inside the bf16 tolerance
+    g = (1.5 / D) ** 0.5 / d ** 0.25
+    ts = {"q": (torch.randn(H * d, D) * g).to(dtype), "k": (torch.randn(K * d, D) * g).to(dtype),
+          "v": (torch.randn(K * d, D) * 0.1).to(dtype), "o": (torch.randn(D, H * d) * 0.06).to(dtype)}
+    part.load(source(ts, part.tensor_specs(), dtype))
+    cache = PagedCache([(part.cache_request(), None, None)], 8, 12, 2, 96, dtype, DEV)
+    slot = cache.admit()
+    h = torch.randn(S, D).to(dtype)
+    outs, at = [], 0
+    for n in (30, 14, 1):
+        assert cache.ensure(slot, at + n)
+        ctx, err = _step_ctx(cache, slot, at, n)
+        y = part.forward(h[at:at + n].to(DEV).contiguous(), ctx, cache.layer_cache(0, ctx)).float()
+        outs.append((y.sum(0) if y.dim() == 3 else y).cpu())      # unjoined parts of a split product
+        assert int(err.item()) == 0
+        at += n
+        cache.advance(slot, at)
+    got = torch.cat(outs)
+    cfg = dict(heads=H, kv_heads=K, head_dim=d)
+    want = pl.attention(h.double(), ts["q"].double(), ts["k"].double(), ts["v"].double(), ts["o"].double(),
+                        torch.arange(S), cfg, pl.inv_freq_default(d, 500000.0), window or None)
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    err_rows = (got.double() - want).abs().amax(dim=1)
+    assert err_rows.max() <= tol, f"first wrong token {int((err_rows > tol).nonzero()[0])}: {float(err_rows.max())}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_and_head_parts(dtype):
+    from ai_engine_b200.parts import LMHead, PartSpec, TokenEmbedding
+
+    V, D = 333, 72
+    e = env(dtype, D)
+    emb = TokenEmbedding(PartSpec("token_embedding", dict(vocab_size=V, hidden_size=D), dict(weight="E")), e)
+    head = LMHead(PartSpec("lm_head", dict(vocab_size=V, hidden_size=D), dict(weight="E")), e)     # tied
+    table = (torch.randn(V, D) * 0.1).to(dtype)
+    src = source({"E": table}, emb.tensor_specs(), dtype)
+    emb.load(src)
+    head.load(src)
+    assert emb.weight.data_ptr() == head.weight.data_ptr()          # one device copy serves both
+    ids = torch.tensor([0, 5, 332, 5], dtype=torch.int32, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    x = emb.forward(ids, err)
+    assert x.dtype == torch.float32 and torch.equal(x.cpu(), pl.embed(ids.long().cpu(), table.float()))
+    h = torch.randn(3, D).to(dtype)
+    logits = head.forward(h.to(DEV), err)
+    want = h.double() @ table.double().T
+    assert logits.dtype == torch.float32
+    assert (logits.double().cpu() - want).abs().max() <= (1e-5 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_prenorm_block_alone(dtype):
+    """The block arrangement from its parts against plain decoder_layer: two residuals, the branch
+    outputs added inside the following norm."""
+    from ai_engine_b200.cache import PagedCache
+    from ai_engine_b200.parts import BuildEnv, LayerSpec, PartSpec, RotaryEncoding
+    from ai_engine_b200.parts.model import Layer
+
+    torch.manual_seed(4)
+    D, H, K, d, F, S = 64, 4, 2, 16, 192, 21
+    e = env(dtype, D)
+    rope = RotaryEncoding(PartSpec("rotary", dict(rot_dim=d, theta=10000.0, scaling=None)), e)
+    rope.load(None)
+    e.position_encodings["rope"] = rope
+    p = "model.layers.0."
+    spec = LayerSpec("prenorm", {
+        "mixer_norm": PartSpec("rmsnorm", dict(size=D, eps=1e-5), dict(weight=p + "input_layernorm.weight")),
+        "mixer": PartSpec("gqa_attention", dict(hidden_size=D, num_heads=H, num_kv_heads=K, head_dim=d, window=0,
+                                                scale=None, position_encoding="rope"),
+                          dict(q=p + "self_attn.q_proj.weight", k=p + "self_attn.k_proj.weight",
+                               v=p + "self_attn.v_proj.weight", o=p + "self_attn.o_proj.weight")),
+        "ffn_norm": PartSpec("rmsnorm", dict(size=D, eps=1e-5), dict(weight=p + "post_attention_layernorm.weight")),
+        "ffn": PartSpec("swiglu", dict(hidden_size=D, intermediate_size=F),
+                        dict(gate=p + "mlp.gate_proj.weight", up=p + "mlp.up_proj.weight", down=p + "mlp.down_proj.weight"))})
+    layer = Layer(spec, e)
+    specs = [s for part in layer.parts.values() for s in part.tensor_specs()]
+    from ai_engine_b200.weights import random_tensors
+    ts = dict(random_tensors(specs, 3, dtype, "cpu", std=0.1, norm_std=0.1))
+    src = source(ts, specs, dtype)
+    for part in layer.parts.values():
+        part.load(src)
+    cache = PagedCache([(layer.mixer.cache_request(), None, None)], 8, 8, 1, 64, dtype, DEV)
+    slot = cache.admit()
+    cache.ensure(slot, S)
+    ctx, err = _step_ctx(cache, slot, 0, S)
+    x0 = torch.randn(S, D)
+    x = x0.clone().to(DEV)
+    x, pending = layer.block.forward(x, None, ctx, cache.layer_cache(0, ctx))
+    delta = pending.float().sum(0) if pending.dim() == 3 else pending.float()
+    got = (x + delta).double().cpu()
+    cfg = dict(heads=H, kv_heads=K, head_dim=d, eps=1e-5)
+    want = pl.decoder_layer(x0.double(), {k: v.double() for k, v in ts.items()}, 0, torch.arange(S), cfg,
+                            pl.inv_freq_default(d, 10000.0))
+    assert int(err.item()) == 0
+    assert (got - want).abs().max() <= (1e-4 if dtype == torch.float32 else 5e-2)

@@ -109,6 +109,7 @@ class Engine:
         self.eos_ids = set(spec.eos_token_ids)
         self.requests: Dict[int, _Request] = {}
         self._next_id = 0
+        self._since_check = 0
         self.counters = dict(steps=0, h2d_bytes=0, d2h_bytes=0, batch_tokens=0, batch_requests=0)
 
     # -- requests ------------------------------------------------------------------
@@ -156,13 +157,15 @@ class Engine:
         if sampled:
             ids = self.sampler.sample(logits, [r.params for r in sampled],
                                       [len(r.tokens) - r.prompt_len for r in sampled])
-            packed = torch.cat([ids, self.runner.err]).cpu()      # one read: tokens + error word
-            tokens = packed[:-1].tolist()
-            if int(packed[-1]):
-                self.runner.check_errors()
-            self.counters["d2h_bytes"] += packed.numel() * 4
-        else:
+            tokens = ids.cpu().tolist()                 # the step's result: one read
+            self.counters["d2h_bytes"] += len(tokens) * 4
+        # the device error word is read when nothing else is (no tokens), every 16th step, and
+        # whenever a request is about to end
+        self._since_check += 1
+        ending = any(len(r.tokens) - r.prompt_len + 1 >= r.params.max_tokens for r in sampled)
+        if not sampled or ending or self._since_check >= 16:
             self.runner.check_errors()
+            self._since_check = 0
             self.counters["d2h_bytes"] += 4
         self.scheduler.commit(plan)
         for req, tok in zip(sampled, tokens):
@@ -193,6 +196,7 @@ class Engine:
         rids = [self.add_request(p, s) for p, s in zip(prompts, sampling)]
         while self.scheduler.has_work():
             self.step()
+        self.runner.check_errors()
         return [self.requests.pop(r).output for r in rids]
 
     def forward_tokens(self, entries: Sequence[StepEntry]) -> torch.Tensor:

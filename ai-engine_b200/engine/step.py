@@ -94,12 +94,17 @@ class StepContext:
         slots = np.array([e.slot for e in entries], dtype=np.int32)
         q_start = np.zeros(R, dtype=np.int32)
         np.cumsum(q_len[:-1], out=q_start[1:])
-        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        if T == R:        # every request brings one token: no ragged arithmetic needed
+            token_ids = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=R)
+            token_req = np.arange(R, dtype=np.int32)
+            positions = ctx_len
+        else:
+            token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+            token_req = np.repeat(np.arange(R, dtype=np.int32), q_len)
+            positions = (np.arange(T, dtype=np.int32) - np.repeat(q_start, q_len)
+                         + np.repeat(ctx_len, q_len)).astype(np.int32)
         if token_ids.min() < 0 or token_ids.max() > 2**31 - 1:
             raise StepError("token ids must be non-negative 32-bit integers")
-        token_req = np.repeat(np.arange(R, dtype=np.int32), q_len)
-        positions = (np.arange(T, dtype=np.int32) - np.repeat(q_start, q_len)
-                     + np.repeat(ctx_len, q_len)).astype(np.int32)
         rows: List[int] = []
         for r, e in enumerate(entries):
             for w in e.want:
@@ -118,14 +123,20 @@ class StepContext:
         tables = cache.fill_block_tables(slots.tolist(), width)
 
         # requests that bring one token (decode) and the tokens of all others
-        is_dec = q_len == 1
-        dec = q_start[is_dec]
-        other = np.nonzero(np.repeat(~is_dec, q_len))[0].astype(np.int32)
-        self.n_decode = int(dec.shape[0])
-        self.max_decode_len = int((ctx_len[is_dec] + 1).max()) if self.n_decode else 0
+        if T == R:
+            dec, other = q_start, np.empty(0, dtype=np.int32)
+            self.n_decode = R
+            self.max_decode_len = self.max_total_len
+        else:
+            is_dec = q_len == 1
+            dec = q_start[is_dec]
+            other = np.nonzero(np.repeat(~is_dec, q_len))[0].astype(np.int32)
+            self.n_decode = int(dec.shape[0])
+            self.max_decode_len = int((ctx_len[is_dec] + 1).max()) if self.n_decode else 0
         if bucket_width and self.n_decode:
             self.max_decode_len = width * cache.page_size      # a property of the layout, not of the step
-        tiles = [(r, o) for r in range(R) if q_len[r] != 1 for o in range(0, int(q_len[r]), PREFILL_TILE)]
+        tiles = [] if T == R else [(r, o) for r in range(R) if q_len[r] != 1
+                                   for o in range(0, int(q_len[r]), PREFILL_TILE)]
         arrays = [token_ids.astype(np.int32), positions, token_req, dec.astype(np.int32), other,
                   np.asarray(tiles, dtype=np.int32).reshape(-1), q_start, q_len, ctx_len, slots,
                   np.asarray(rows, dtype=np.int32)] + [tb.reshape(-1) for tb in tables]

@@ -34,10 +34,19 @@ class Sampler:
 
     def __init__(self, device):
         self.device = device
+        self._greedy = {}          # n -> device tensors of an all-greedy step (nothing to upload)
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                draw_index: Sequence[int]) -> torch.Tensor:
         n = len(params)
+        if all(p.temperature == 0 for p in params):
+            g = self._greedy.get(n)
+            if g is None:
+                z = torch.zeros(n, dtype=torch.float32, device=self.device)
+                g = (z, torch.zeros(n, dtype=torch.int32, device=self.device),
+                     torch.ones(n, dtype=torch.float32, device=self.device))
+                self._greedy[n] = g
+            return sample_rows(logits, g[0], g[1], g[2], g[0])
         packed = np.zeros((4, n), dtype=np.float32)
         for i, (p, k) in enumerate(zip(params, draw_index)):
             packed[0, i] = p.temperature

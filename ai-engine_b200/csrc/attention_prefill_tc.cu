@@ -1,0 +1,373 @@
+// bfloat16 paged attention for portions of prompts on the fifth-generation tensor cores
+// (head size 128): scores and outputs live in tensor memory, operands come from shared memory
+// filled by TMA, softmax is float32 in registers.
+//
+// One CTA owns 128 query tokens of one head.  For each tile of 128 keys:
+//   warp 0 (one lane)  loads the key and value tile page by page with TMA (one box of [page, 64]
+//                      per page and half of the head; the pool of a layer is one matrix of
+//                      [pages * kv_heads * page, 128] rows), 128-byte swizzled, two buffers;
+//   warp 1 (one lane)  issues S = Q . K^T (8 x tcgen05.mma of K = 16) into tensor memory, later
+//                      O += P . V (8 x tcgen05.mma; V is the MN-major operand: its rows are keys),
+//                      and commits to the mbarriers the others wait on;
+//   warps 2-5          one thread per query row: read the row of S (tcgen05.ld), mask (causal,
+//                      end of the sequence, window), running maximum and sum in float32, rescale
+//                      the row of O in tensor memory when the maximum moved, write P as bf16 into
+//                      shared memory in the swizzled K-major layout the product reads.
+// The value rows of keys past the sequence's last token are zeroed in shared memory before the
+// last tile's P . V, so a probability of 0 never meets what an unwritten cache slot holds.
+// Every wait is bounded (see tc_common.cuh); a wait that runs out raises the device error word.
+// Formula: crates/ai-engine-runtime/src/arch/attention.rs:148-157,177-196,203-224.
+#include "tc_common.cuh"
+
+#define AT_M 128          // query rows per CTA
+#define AT_N 128          // keys per tile
+#define AT_D 128          // head size
+#define AT_THREADS 192
+#define AT_HALF_BYTES (128 * 64 * 2)      // one [128 x 64] bf16 swizzle atom column: 16 KB
+
+struct AtSmem {
+    // [alignment slack | 1024 B barriers | Q 32 KB | P 32 KB | K 2 x 32 KB | V 2 x 32 KB]
+    static constexpr int q_off = 1024, p_off = q_off + 2 * AT_HALF_BYTES, k_off = p_off + 2 * AT_HALF_BYTES,
+                         v_off = k_off + 4 * AT_HALF_BYTES, end = v_off + 4 * AT_HALF_BYTES;
+    static constexpr int bytes = 1024 + end;
+};
+
+// shared-memory descriptor of an MN-major operand: rows of 64 elements (128 bytes) along MN,
+// groups of 8 K-rows 1024 bytes apart, blocks of 64 MN elements `lbo` bytes apart
+__device__ __forceinline__ unsigned long long umma_desc_mn(const void* tile, unsigned lbo_bytes) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((tc_smem(tile) >> 4) & 0x3FFFu);
+    d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+
+#define AT_LD16(v, taddr)                                                                                             \
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n" \
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),  \
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]) \
+                 : "r"(taddr))
+#define AT_ST16(v, taddr)                                                                                             \
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" \
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), \
+                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory")
+
+__global__ void __launch_bounds__(AT_THREADS)
+paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
+                        const int* __restrict__ tiles, int n_tiles, const int* __restrict__ q_start,
+                        const int* __restrict__ q_len, const int* __restrict__ ctx_len,
+                        const int* __restrict__ block_table, int bt_width, int num_pages, int P, int H, int K,
+                        int window, float scale, unsigned* err) {
+    extern __shared__ unsigned char at_raw[];
+    unsigned char* sm = reinterpret_cast<unsigned char*>(((size_t)at_raw + 1023) & ~(size_t)1023);
+    unsigned long long* q_full = reinterpret_cast<unsigned long long*>(sm);
+    unsigned long long* kv_full = q_full + 1;      // [2]
+    unsigned long long* kv_empty = kv_full + 2;    // [2]
+    unsigned long long* s_full = kv_empty + 2;
+    unsigned long long* p_ready = s_full + 1;
+    unsigned long long* o_done = p_ready + 1;
+    unsigned long long* v_fixed = o_done + 1;
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(v_fixed + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    unsigned char* q_s = sm + AtSmem::q_off;
+    unsigned char* p_s = sm + AtSmem::p_off;
+    unsigned char* k_s = sm + AtSmem::k_off;
+    unsigned char* v_s = sm + AtSmem::v_off;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile_i = n_tiles - 1 - (int)blockIdx.x;      // later tiles hold more keys: start them first
+    const int r = tiles[2 * tile_i], q_off = tiles[2 * tile_i + 1];
+    const int h = blockIdx.y, kvh = h / (H / K);
+    const int t0 = q_start[r] + q_off;
+    const int rows_valid = min(AT_M, q_len[r] - q_off);
+    const int p0 = ctx_len[r] + q_off;                 // position of the tile's first query
+    const int p_last = p0 + rows_valid - 1;            // and of its last valid one
+    int lo_min = 0;
+    if (window > 0 && p0 - window + 1 > 0) lo_min = p0 - window + 1;
+    const int kt_lo = lo_min / AT_N, kt_hi = p_last / AT_N;
+    const int n_kt = kt_hi - kt_lo + 1;
+    const int ppt = AT_N / P;                          // pages per key tile
+
+    if (tid == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&kv_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
+        }
+        mbar_init(s_full, 1);
+        mbar_init(p_ready, 4);          // one arrival per softmax warp
+        mbar_init(o_done, 1);
+        mbar_init(v_fixed, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {    // tensor memory: columns [0, 128) scores, [128, 256) outputs
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(tmem_slot)), "r"(256));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + 128;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // queries of this tile: rows t0 .. t0 + 127 of q [T, H * 128], columns of head h
+            mbar_expect_tx(q_full, 2 * AT_HALF_BYTES);
+            tma_load_2d(q_s, &map_q, q_full, h * AT_D, t0);
+            tma_load_2d(q_s + AT_HALF_BYTES, &map_q, q_full, h * AT_D + 64, t0);
+            const int* bt = block_table + (size_t)r * bt_width;
+            for (int j = 0; j < n_kt; ++j) {
+                const int st = j & 1;
+                if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1, abort_flag, err)) break;
+                const int kbase = (kt_lo + j) * AT_N;
+                // count the pages that exist, then load them
+                int n_ok = 0;
+                for (int i = 0; i < ppt; ++i) {
+                    const int key0 = kbase + i * P, pidx = key0 / P;
+                    const int page = (key0 <= p_last && pidx < bt_width) ? bt[pidx] : -1;
+                    if (page >= 0 && page < num_pages) ++n_ok;
+                    else if (key0 <= p_last && key0 + P - 1 >= lo_min) atomicOr(err, AIE_DEV_PAGE_OOB);
+                }
+                if (n_ok > 0) mbar_expect_tx(&kv_full[st], (unsigned)n_ok * 4u * (unsigned)P * 128u);
+                else mbar_arrive_plain(&kv_full[st]);
+                unsigned char* kd = k_s + st * 2 * AT_HALF_BYTES;
+                unsigned char* vd = v_s + st * 2 * AT_HALF_BYTES;
+                for (int i = 0; i < ppt; ++i) {
+                    const int key0 = kbase + i * P, pidx = key0 / P;
+                    const int page = (key0 <= p_last && pidx < bt_width) ? bt[pidx] : -1;
+                    if (page < 0 || page >= num_pages) continue;
+                    const int row = (page * K + kvh) * P;
+                    const int off = i * P * 128;       // rows of this page inside a [128 x 64] atom column
+                    tma_load_2d(kd + off, &map_k, &kv_full[st], 0, row);
+                    tma_load_2d(kd + AT_HALF_BYTES + off, &map_k, &kv_full[st], 64, row);
+                    tma_load_2d(vd + off, &map_v, &kv_full[st], 0, row);
+                    tma_load_2d(vd + AT_HALF_BYTES + off, &map_v, &kv_full[st], 64, row);
+                }
+            }
+        }
+        __syncwarp();
+        // the last tile: zero the value rows of keys past the sequence's end (whole warp)
+        {
+            const int j = n_kt - 1, st = j & 1;
+            const int kbase = kt_hi * AT_N;
+            const int first_bad = p_last + 1 - kbase;          // rows [first_bad, 128) are not keys
+            bool ok = true;
+            if (first_bad < AT_N) {
+                if (lane == 0) ok = mbar_wait(&kv_full[st], (j >> 1) & 1, abort_flag, err);
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (ok) {
+                    unsigned char* vd = v_s + st * 2 * AT_HALF_BYTES;
+                    const int n_bad = AT_N - first_bad;
+                    for (int i = lane; i < n_bad * 16; i += 32) {      // 16 chunks of 16 bytes per row (two halves)
+                        const int row = first_bad + i / 16, c = i % 16;
+                        *reinterpret_cast<uint4*>(vd + (c / 8) * AT_HALF_BYTES + row * 128 + (c % 8) * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive_plain(v_fixed);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const unsigned idesc_s = umma_idesc(AT_N), idesc_o = umma_idesc(AT_D, true);
+            bool ok = mbar_wait(q_full, 0, abort_flag, err);
+            for (int j = 0; j < n_kt && ok; ++j) {
+                const int st = j & 1;
+                ok = mbar_wait(&kv_full[st], (j >> 1) & 1, abort_flag, err);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                unsigned char* kd = k_s + st * 2 * AT_HALF_BYTES;
+                unsigned char* vd = v_s + st * 2 * AT_HALF_BYTES;
+                // S = Q . K^T over d = 128: two halves of 64, four steps of 16 each
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const unsigned long long da = umma_desc(q_s + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
+                    const unsigned long long db = umma_desc(kd + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
+                    umma(tmem_s, da, db, idesc_s, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(s_full);
+                // wait for P (and, for the last tile, for the zeroed value rows)
+                ok = mbar_wait(p_ready, j & 1, abort_flag, err);
+                if (!ok) break;
+                if (j == n_kt - 1) ok = mbar_wait(v_fixed, 0, abort_flag, err);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                // O += P . V over 128 keys: 8 steps of 16 keys; P is K-major (two halves of 64 keys),
+                // V is MN-major: 16 keys = two groups of 8 rows, the two d-halves AT_HALF_BYTES apart
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const unsigned long long da = umma_desc(p_s + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
+                    const unsigned long long db = umma_desc_mn(vd + ks * 2 * 1024, AT_HALF_BYTES);
+                    umma(tmem_o, da, db, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                }
+                umma_commit(&kv_empty[st]);
+                umma_commit(o_done);
+            }
+        }
+    } else {
+        // softmax: thread = query row
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const int qpos = p0 + row;
+        const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_kt; ++j) {
+            if (lane == 0) ok = mbar_wait(s_full, j & 1, abort_flag, err);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int kbase = (kt_lo + j) * AT_N;
+            const bool edge = (kbase + AT_N - 1 > p0) || (window > 0 && kbase < p_last - window + 1 + AT_M);
+            // pass 1: the row's maximum
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int c0 = 0; c0 < AT_N; c0 += 16) {
+                unsigned v[16];
+                AT_LD16(v, tmem_s + lane_addr + c0);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float s = __uint_as_float(v[i]) * scale;
+                    if (edge) {
+                        const int key = kbase + c0 + i;
+                        bool vis = key <= qpos;
+                        if (window > 0) vis = vis && key > qpos - window;
+                        if (!vis) s = -INFINITY;
+                    }
+                    tmax = fmaxf(tmax, s);
+                }
+            }
+            const float m_new = fmaxf(m_run, tmax);
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            const float corr = (m_run == -INFINITY) ? 0.f : __expf(m_run - m_use);
+            // the previous P . V must have landed before O is touched or P is overwritten
+            if (j > 0) {
+                if (lane == 0) ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, err);
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                if (__any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll
+                    for (int c0 = 0; c0 < AT_D; c0 += 16) {
+                        unsigned v[16];
+                        AT_LD16(v, tmem_o + lane_addr + c0);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                        AT_ST16(v, tmem_o + lane_addr + c0);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                }
+            }
+            // pass 2: probabilities, their sum, P as bf16 in the K-major swizzled layout
+            float psum = 0.f;
+#pragma unroll
+            for (int c0 = 0; c0 < AT_N; c0 += 16) {
+                unsigned v[16];
+                AT_LD16(v, tmem_s + lane_addr + c0);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                unsigned pk[8];
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    float s0 = __uint_as_float(v[i]) * scale, s1 = __uint_as_float(v[i + 1]) * scale;
+                    if (edge) {
+                        const int key = kbase + c0 + i;
+                        bool v0 = key <= qpos, v1 = key + 1 <= qpos;
+                        if (window > 0) { v0 = v0 && key > qpos - window; v1 = v1 && key + 1 > qpos - window; }
+                        if (!v0) s0 = -INFINITY;
+                        if (!v1) s1 = -INFINITY;
+                    }
+                    const float e0 = __expf(s0 - m_use), e1 = __expf(s1 - m_use);
+                    psum += e0 + e1;
+                    __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
+                    pk[i >> 1] = *reinterpret_cast<unsigned*>(&b);
+                }
+                // keys c0 .. c0+15 of this row: two 16-byte chunks of half c0 / 64
+                unsigned char* half = p_s + (c0 >> 6) * AT_HALF_BYTES + row * 128;
+                const int ch = (c0 & 63) >> 3;
+                *reinterpret_cast<uint4*>(half + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *reinterpret_cast<uint4*>(half + (((ch + 1) ^ (row & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            }
+            l_run = l_run * corr + psum;
+            m_run = m_new;
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_plain(p_ready);
+        }
+        // the last P . V, then the row of O
+        if (ok) {
+            if (lane == 0) ok = mbar_wait(o_done, (n_kt - 1) & 1, abort_flag, err);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        }
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            bf16* dst = out + ((size_t)(t0 + row) * H + h) * AT_D;
+#pragma unroll
+            for (int c0 = 0; c0 < AT_D; c0 += 16) {
+                unsigned v[16];
+                AT_LD16(v, tmem_o + lane_addr + c0);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (row < rows_valid) {
+                    unsigned pk[8];
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2) {
+                        __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+                        pk[i >> 1] = *reinterpret_cast<unsigned*>(&b);
+                    }
+                    *reinterpret_cast<uint4*>(dst + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    *reinterpret_cast<uint4*>(dst + c0 + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (*abort_flag && tid == 0) {      // give copies in flight a bounded time to land
+        for (int s = 0; s < 2; ++s)
+            for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(&kv_full[s], 0) && !mbar_try_wait(&kv_full[s], 1); ++i) {}
+    }
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(256));
+    }
+}
+
+// q, out: [T, H, 128] bf16; k_pages, v_pages: [num_pages, K, P, 128] bf16 of one layer;
+// tiles: [n_tiles][2] = (request row, offset of the 128-token tile within the request's tokens).
+// Takes head size 128, page sizes that divide 128 and layers without a window; refuses the rest
+// (AIE_UNSUPPORTED): they take the mma.sync kernel.
+extern "C" int aie_paged_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                              const int* tiles, int n_tiles, const int* q_start, const int* q_len,
+                                              const int* ctx_len, const int* block_table, int bt_width,
+                                              int num_pages, int P, int T, int H, int K, int d, int window,
+                                              float scale, unsigned* err, cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (K <= 0 || H % K) return AIE_BAD_ARG;
+    if (d != AT_D || P <= 0 || P > 128 || 128 % P || H > 65535 || window > 0) return AIE_UNSUPPORTED;
+    if (((size_t)q & 15) || ((size_t)k_pages & 15) || ((size_t)v_pages & 15)) return AIE_UNSUPPORTED;
+    CUtensorMap mq, mk, mv;
+    int rc = tc_make_map_2d(&mq, q, (unsigned long long)T, (unsigned long long)H * d, (unsigned long long)H * d * 2, AT_M, 64);
+    if (rc) return rc;
+    const unsigned long long rows = (unsigned long long)num_pages * K * P;
+    rc = tc_make_map_2d(&mk, k_pages, rows, d, (unsigned long long)d * 2, P, 64);
+    if (rc) return rc;
+    rc = tc_make_map_2d(&mv, v_pages, rows, d, (unsigned long long)d * 2, P, 64);
+    if (rc) return rc;
+    cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AtSmem::bytes);
+    paged_prefill_tc_kernel<<<dim3(n_tiles, H), AT_THREADS, AtSmem::bytes, stream>>>(
+        mq, mk, mv, (bf16*)out, tiles, n_tiles, q_start, q_len, ctx_len, block_table, bt_width, num_pages, P, H, K,
+        window, scale, err);
+    AIE_LAUNCH_CHECK();
+}

@@ -29,7 +29,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a",
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden"]
 
 CUDA_SOURCES = ["elementwise.cu", "rope_kv.cu", "attention_plain.cu", "gemm_f32.cu",
-                "sampling.cu", "attention_fast.cu", "attention_decode_noalloc.cu", "gemm_tc.cu"]
+                "sampling.cu", "attention_fast.cu", "attention_decode_noalloc.cu", "gemm_tc.cu", "attention_prefill_tc.cu"]
 
 
 class BuildError(RuntimeError):

@@ -33,71 +33,11 @@
 // Every wait is bounded: after WAIT_LIMIT polls a thread raises the CTA's abort
 // flag and the device error word, the other roles leave their loops, copies in
 // flight are waited for (bounded), tensor memory is freed and the CTA returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tc_common.cuh"
 
 #define TC_BM 128           // weight rows per tile (the MMA's M)
 #define TC_BK 64            // K elements per stage (128 bytes: one swizzle row)
 #define TC_THREADS 192
-#define TC_WAIT_LIMIT (1u << 24)
-
-__device__ __forceinline__ unsigned tc_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(tc_smem(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(tc_smem(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
-                 : "=r"(ok) : "r"(tc_smem(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false when it gave up or when another role has aborted.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag,
-                                          unsigned* err) {
-    for (unsigned i = 0; i < TC_WAIT_LIMIT; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    atomicOr(err, AIE_DEV_WAIT_TIMEOUT);
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, unsigned long long* bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                 ::"r"(tc_smem(dst)), "l"(map), "r"(tc_smem(bar)), "r"(x), "r"(y) : "memory");
-}
-
-// K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle, groups of
-// 8 rows 1024 bytes apart (what the TMA load with SWIZZLE_128B writes).
-__device__ __forceinline__ unsigned long long umma_desc(const void* tile) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((tc_smem(tile) >> 4) & 0x3FFFu);   // start address / 16
-    d |= (unsigned long long)1 << 16;                             // leading byte offset / 16 (unused under swizzle)
-    d |= (unsigned long long)(1024 >> 4) << 32;                   // stride byte offset / 16: next group of 8 rows
-    d |= (unsigned long long)1 << 46;                             // descriptor version of sm_100
-    d |= (unsigned long long)2 << 61;                             // SWIZZLE_128B
-    return d;
-}
-// bf16 x bf16 -> f32, both operands K-major, M = 128, N = n
-__device__ __forceinline__ unsigned umma_idesc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
-}
-__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc,
-                                     unsigned accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}\n"
-                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
-                 : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc_smem(bar)) : "memory");
-}
 
 template <typename OT> __device__ __forceinline__ void tc_store(OT* p, float v);
 template <> __device__ __forceinline__ void tc_store<float>(float* p, float v) { *p = v; }
@@ -318,35 +258,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
 }
 
-// ---------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
 // a [rows, K] bf16 row-major matrix, tiles of [box_rows, 64], 128-byte swizzle, zeros outside
 static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return AIE_UNSUPPORTED;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : AIE_BAD_ARG;
+    return tc_make_map_2d(map, ptr, (unsigned long long)rows, (unsigned long long)K, (unsigned long long)K * 2,
+                          box_rows, TC_BK);
 }
 
 template <int BN, int EPI, typename OT>

@@ -365,11 +365,34 @@ def paged_attention_prefill(q, k_pages, v_pages, tiles, q_start, q_len, ctx_len,
           "paged_attention_prefill")
 
 
+def paged_attention_prefill_tc(q, k_pages, v_pages, tiles, q_start, q_len, ctx_len, block_table,
+                               scale: float, window: int, err, out) -> bool:
+    """The tcgen05 version of paged_attention_prefill (scores and outputs in tensor memory,
+    operands by TMA).  Takes head size 128, page sizes that divide 128, no window; returns
+    False when it does not take the sizes (nothing was launched)."""
+    _dev(q, k_pages, v_pages, tiles, q_start, q_len, ctx_len, block_table, err, out)
+    T, H, d = q.shape
+    num_pages, K, P, _ = k_pages.shape
+    if d != 128 or window > 0 or P > 128 or 128 % P:
+        return False
+    lib = library("attention_prefill_tc.cu")
+    rc = lib.aie_paged_attention_prefill_tc(_p(q), _p(k_pages), _p(v_pages), _p(out), _p(tiles),
+                                            c_int(tiles.shape[0]), _p(q_start), _p(q_len), _p(ctx_len),
+                                            _p(block_table), c_int(block_table.shape[1]),
+                                            c_int(num_pages), c_int(P), c_int(T), c_int(H), c_int(K),
+                                            c_int(d), c_int(window), c_float(scale), _p(err), _stream())
+    if rc == -2:
+        return False
+    check(rc, "paged_attention_prefill_tc")
+    return True
+
+
 def paged_attention(q, k_pages, v_pages, ctx, block_table, scale: float, window: int):
     """Attention of a step's query tokens over the cache.  float32 takes the plain
     kernel.  bfloat16 with a head size of 64 or 128: requests that bring one token
-    take the split-KV decode kernel, the others the tensor-core kernel for portions
-    of prompts; other head sizes take the plain kernel."""
+    take the split-KV decode kernel, the others a tensor-core kernel for portions of
+    prompts (tcgen05 for head size 128 without a window, else mma.sync); other head sizes
+    take the plain kernel."""
     T, H, d = q.shape
     K = k_pages.shape[1]
     fast = q.dtype == torch.bfloat16 and d in (64, 128)
@@ -384,6 +407,8 @@ def paged_attention(q, k_pages, v_pages, ctx, block_table, scale: float, window:
                                decode_splits(ctx.n_decode, K, H // K, keys, block_table.shape[1]),
                                ctx.err, out)
     if ctx.n_decode < ctx.R:
-        paged_attention_prefill(q, k_pages, v_pages, ctx.prefill_tiles, ctx.q_start, ctx.q_len,
-                                ctx.ctx_len, block_table, scale, window, ctx.err, out)
+        if not paged_attention_prefill_tc(q, k_pages, v_pages, ctx.prefill_tiles, ctx.q_start, ctx.q_len,
+                                          ctx.ctx_len, block_table, scale, window, ctx.err, out):
+            paged_attention_prefill(q, k_pages, v_pages, ctx.prefill_tiles, ctx.q_start, ctx.q_len,
+                                    ctx.ctx_len, block_table, scale, window, ctx.err, out)
     return out

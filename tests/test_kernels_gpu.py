@@ -251,6 +251,51 @@ def test_paged_attention_prefill_tensor_cores(shape):
     assert err.max() <= 2e-2, f"first wrong token {int((err > 2e-2).nonzero()[0])} of {sum(q_lens)}: {float(err.max())}"
 
 
+PREFILL_TC_SHAPES = [  # H, K, P, lens, q_lens  (head size 128, no window)
+    (4, 2, 16, [5, 40], [5, 7]),
+    (32, 8, 16, [300, 130, 64], [300, 2, 64]),
+    (6, 2, 8, [257, 65], [129, 65]),           # a portion that starts mid-page and mid-tile
+    (5, 1, 4, [700], [63]),
+    (2, 2, 32, [1100], [1100]),
+    (3, 3, 16, [200], [2]),
+    (4, 1, 64, [191, 192, 193], [191, 128, 2]),
+    (8, 2, 128, [128, 129, 384], [128, 129, 128]),
+]
+
+
+@pytest.mark.parametrize("shape", PREFILL_TC_SHAPES)
+def test_paged_attention_prefill_tcgen05(shape):
+    H, K, P, lens, q_lens = shape
+    d = 128
+    s = paged_setup(torch.bfloat16, H, K, d, P, lens, q_lens, seed=H + P + len(lens))
+    scale = 1.0 / math.sqrt(d)
+    e = err_word()
+    out = torch.full_like(s["q"], float("nan"))
+    i32 = lambda a: torch.tensor(a, device=DEV, dtype=torch.int32)
+    q_start = np.concatenate([[0], np.cumsum(q_lens)[:-1]])
+    tiles = [(r, o) for r, n in enumerate(q_lens) for o in range(0, n, 128)]
+    took = ops().paged_attention_prefill_tc(s["q"], s["k_pages"], s["v_pages"], i32(tiles), i32(q_start), i32(q_lens),
+                                            i32([n - ql for n, ql in zip(lens, q_lens)]), s["bt"], scale, 0, e, out)
+    assert took
+    torch.cuda.synchronize()
+    assert int(e.item()) == 0, "a bounded wait ran out or a page was missing"
+    want = attention_reference(s, H, K, d, scale, 0)
+    assert not torch.isnan(out).any()
+    err = (out.double() - want).abs().amax(dim=(1, 2))
+    assert err.max() <= 2e-2, f"first wrong token {int((err > 2e-2).nonzero()[0])} of {sum(q_lens)}: {float(err.max())}"
+
+
+def test_prefill_tcgen05_refuses_what_it_does_not_take():
+    s = paged_setup(torch.bfloat16, 4, 2, 64, 16, [40], [40], seed=1)
+    i32 = lambda a: torch.tensor(a, device=DEV, dtype=torch.int32)
+    out = torch.zeros_like(s["q"])
+    args = (s["q"], s["k_pages"], s["v_pages"], i32([[0, 0]]), i32([0]), i32([40]), i32([0]), s["bt"], 0.125)
+    assert not ops().paged_attention_prefill_tc(*args, 0, err_word(), out)          # head size 64
+    s = paged_setup(torch.bfloat16, 4, 2, 128, 16, [40], [40], seed=1)
+    args = (s["q"], s["k_pages"], s["v_pages"], i32([[0, 0]]), i32([0]), i32([40]), i32([0]), s["bt"], 0.09)
+    assert not ops().paged_attention_prefill_tc(*args, 7, err_word(), torch.zeros_like(s["q"]))   # a window
+
+
 def test_mixed_step_decode_and_prefill_kernels_side_by_side():
     """A mixed step: requests 0 and 2 bring one token, request 1 brings five."""
     H, K, d, P = 8, 2, 64, 16

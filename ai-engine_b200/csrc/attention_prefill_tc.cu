@@ -3,16 +3,20 @@
 // filled by TMA, softmax is float32 in registers.
 //
 // One CTA owns 128 query tokens of one head.  For each tile of 128 keys:
-//   warp 0 (one lane)  loads the key and value tile page by page with TMA (one box of [page, 64]
-//                      per page and half of the head; the pool of a layer is one matrix of
-//                      [pages * kv_heads * page, 128] rows), 128-byte swizzled, two buffers;
-//   warp 1 (one lane)  issues S = Q . K^T (8 x tcgen05.mma of K = 16) into tensor memory, later
-//                      O += P . V (8 x tcgen05.mma; V is the MN-major operand: its rows are keys),
-//                      and commits to the mbarriers the others wait on;
-//   warps 2-5          one thread per query row: read the row of S (tcgen05.ld), mask (causal,
-//                      end of the sequence, window), running maximum and sum in float32, rescale
-//                      the row of O in tensor memory when the maximum moved, write P as bf16 into
-//                      shared memory in the swizzled K-major layout the product reads.
+//   warp 0 (one lane)  loads the key tile and the value tile page by page with TMA (one box of
+//                      [page, 64] per page and half of the head; the pool of a layer is one matrix
+//                      of [pages * kv_heads * page, 128] rows), 128-byte swizzled, a ring of two
+//                      buffers for keys and one of two for values;
+//   warp 1 (one lane)  issues S = Q . K^T (8 x tcgen05.mma of K = 16) into one of two score
+//                      buffers in tensor memory — the scores of the next tile are computed while
+//                      the softmax of this one runs — later O += P . V (8 x tcgen05.mma; V is the
+//                      MN-major operand: its rows are keys), and commits to the mbarriers the
+//                      others wait on;
+//   warps 2-5          one thread per query row: read the row of S (tcgen05.ld, 128 columns in
+//                      flight at once), mask (causal, end of the sequence), running maximum and
+//                      sum in float32, rescale the row of O in tensor memory when the maximum
+//                      moved, write P as bf16 into shared memory in the swizzled K-major layout
+//                      the product reads.
 // The value rows of keys past the sequence's last token are zeroed in shared memory before the
 // last tile's P . V, so a probability of 0 never meets what an unwritten cache slot holds.
 // Every wait is bounded (see tc_common.cuh); a wait that runs out raises the device error word.
@@ -44,15 +48,22 @@ __device__ __forceinline__ unsigned long long umma_desc_mn(const void* tile, uns
     return d;
 }
 
-#define AT_LD16(v, taddr)                                                                                             \
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n" \
+// 32 consecutive columns of this thread's lane of tensor memory
+#define AT_LD32(v, taddr)                                                                                             \
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                            \
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n" \
                  : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),  \
-                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]) \
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), \
+                   "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), \
+                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]) \
                  : "r"(taddr))
-#define AT_ST16(v, taddr)                                                                                             \
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" \
+#define AT_ST32(v, taddr)                                                                                             \
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "                                                      \
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" \
                  ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), \
-                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory")
+                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),     \
+                   "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),   \
+                   "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory")
 
 __global__ void __launch_bounds__(AT_THREADS)
 paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -60,14 +71,16 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const int* __restrict__ tiles, int n_tiles, const int* __restrict__ q_start,
                         const int* __restrict__ q_len, const int* __restrict__ ctx_len,
                         const int* __restrict__ block_table, int bt_width, int num_pages, int P, int H, int K,
-                        int window, float scale, unsigned* err) {
+                        float scale, unsigned* err) {
     extern __shared__ unsigned char at_raw[];
     unsigned char* sm = reinterpret_cast<unsigned char*>(((size_t)at_raw + 1023) & ~(size_t)1023);
     unsigned long long* q_full = reinterpret_cast<unsigned long long*>(sm);
-    unsigned long long* kv_full = q_full + 1;      // [2]
-    unsigned long long* kv_empty = kv_full + 2;    // [2]
-    unsigned long long* s_full = kv_empty + 2;
-    unsigned long long* p_ready = s_full + 1;
+    unsigned long long* k_full = q_full + 1;       // [2]
+    unsigned long long* k_empty = k_full + 2;      // [2]
+    unsigned long long* v_full = k_empty + 2;      // [2]
+    unsigned long long* v_empty = v_full + 2;      // [2]
+    unsigned long long* s_full = v_empty + 2;      // [2]
+    unsigned long long* p_ready = s_full + 2;
     unsigned long long* o_done = p_ready + 1;
     unsigned long long* v_fixed = o_done + 1;
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(v_fixed + 1);
@@ -85,19 +98,18 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int rows_valid = min(AT_M, q_len[r] - q_off);
     const int p0 = ctx_len[r] + q_off;                 // position of the tile's first query
     const int p_last = p0 + rows_valid - 1;            // and of its last valid one
-    int lo_min = 0;
-    if (window > 0 && p0 - window + 1 > 0) lo_min = p0 - window + 1;
-    const int kt_lo = lo_min / AT_N, kt_hi = p_last / AT_N;
-    const int n_kt = kt_hi - kt_lo + 1;
+    const int n_kt = p_last / AT_N + 1;                // key tiles 0 .. n_kt - 1
     const int ppt = AT_N / P;                          // pages per key tile
 
     if (tid == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&kv_full[s], 1);
-            mbar_init(&kv_empty[s], 1);
+            mbar_init(&k_full[s], 1);
+            mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1);
+            mbar_init(&v_empty[s], 1);
+            mbar_init(&s_full[s], 1);
         }
-        mbar_init(s_full, 1);
         mbar_init(p_ready, 4);          // one arrival per softmax warp
         mbar_init(o_done, 1);
         mbar_init(v_fixed, 1);
@@ -105,14 +117,14 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
-    if (warp == 1) {    // tensor memory: columns [0, 128) scores, [128, 256) outputs
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(tmem_slot)), "r"(256));
+    if (warp == 1) {    // tensor memory: columns [0, 128) and [128, 256) scores, [256, 384) outputs
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(tmem_slot)), "r"(512));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + 128;
+    const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + 256;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -121,32 +133,36 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             tma_load_2d(q_s, &map_q, q_full, h * AT_D, t0);
             tma_load_2d(q_s + AT_HALF_BYTES, &map_q, q_full, h * AT_D + 64, t0);
             const int* bt = block_table + (size_t)r * bt_width;
-            for (int j = 0; j < n_kt; ++j) {
+            bool ok = true;
+            for (int j = 0; j < n_kt && ok; ++j) {
                 const int st = j & 1;
-                if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1, abort_flag, err)) break;
-                const int kbase = (kt_lo + j) * AT_N;
-                // count the pages that exist, then load them
+                const int kbase = j * AT_N;
+                // the pages of this tile that exist
                 int n_ok = 0;
                 for (int i = 0; i < ppt; ++i) {
                     const int key0 = kbase + i * P, pidx = key0 / P;
                     const int page = (key0 <= p_last && pidx < bt_width) ? bt[pidx] : -1;
                     if (page >= 0 && page < num_pages) ++n_ok;
-                    else if (key0 <= p_last && key0 + P - 1 >= lo_min) atomicOr(err, AIE_DEV_PAGE_OOB);
+                    else if (key0 <= p_last) atomicOr(err, AIE_DEV_PAGE_OOB);
                 }
-                if (n_ok > 0) mbar_expect_tx(&kv_full[st], (unsigned)n_ok * 4u * (unsigned)P * 128u);
-                else mbar_arrive_plain(&kv_full[st]);
-                unsigned char* kd = k_s + st * 2 * AT_HALF_BYTES;
-                unsigned char* vd = v_s + st * 2 * AT_HALF_BYTES;
-                for (int i = 0; i < ppt; ++i) {
-                    const int key0 = kbase + i * P, pidx = key0 / P;
-                    const int page = (key0 <= p_last && pidx < bt_width) ? bt[pidx] : -1;
-                    if (page < 0 || page >= num_pages) continue;
-                    const int row = (page * K + kvh) * P;
-                    const int off = i * P * 128;       // rows of this page inside a [128 x 64] atom column
-                    tma_load_2d(kd + off, &map_k, &kv_full[st], 0, row);
-                    tma_load_2d(kd + AT_HALF_BYTES + off, &map_k, &kv_full[st], 64, row);
-                    tma_load_2d(vd + off, &map_v, &kv_full[st], 0, row);
-                    tma_load_2d(vd + AT_HALF_BYTES + off, &map_v, &kv_full[st], 64, row);
+                for (int kv = 0; kv < 2 && ok; ++kv) {      // keys first: the scores need them sooner
+                    unsigned long long* full = kv ? &v_full[st] : &k_full[st];
+                    unsigned long long* empty = kv ? &v_empty[st] : &k_empty[st];
+                    ok = mbar_wait(empty, ((j >> 1) & 1) ^ 1, abort_flag, err);
+                    if (!ok) break;
+                    if (n_ok > 0) mbar_expect_tx(full, (unsigned)n_ok * 2u * (unsigned)P * 128u);
+                    else mbar_arrive_plain(full);
+                    unsigned char* dst = (kv ? v_s : k_s) + st * 2 * AT_HALF_BYTES;
+                    const CUtensorMap* map = kv ? &map_v : &map_k;
+                    for (int i = 0; i < ppt; ++i) {
+                        const int key0 = kbase + i * P, pidx = key0 / P;
+                        const int page = (key0 <= p_last && pidx < bt_width) ? bt[pidx] : -1;
+                        if (page < 0 || page >= num_pages) continue;
+                        const int row = (page * K + kvh) * P;
+                        const int off = i * P * 128;       // rows of this page inside a [128 x 64] atom column
+                        tma_load_2d(dst + off, map, full, 0, row);
+                        tma_load_2d(dst + AT_HALF_BYTES + off, map, full, 64, row);
+                    }
                 }
             }
         }
@@ -154,11 +170,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         // the last tile: zero the value rows of keys past the sequence's end (whole warp)
         {
             const int j = n_kt - 1, st = j & 1;
-            const int kbase = kt_hi * AT_N;
-            const int first_bad = p_last + 1 - kbase;          // rows [first_bad, 128) are not keys
+            const int first_bad = p_last + 1 - j * AT_N;       // rows [first_bad, 128) are not keys
             bool ok = true;
             if (first_bad < AT_N) {
-                if (lane == 0) ok = mbar_wait(&kv_full[st], (j >> 1) & 1, abort_flag, err);
+                if (lane == 0) ok = mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, err);
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (ok) {
                     unsigned char* vd = v_s + st * 2 * AT_HALF_BYTES;
@@ -176,37 +191,47 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     } else if (warp == 1) {
         if (lane == 0) {
             const unsigned idesc_s = umma_idesc(AT_N), idesc_o = umma_idesc(AT_D, true);
-            bool ok = mbar_wait(q_full, 0, abort_flag, err);
-            for (int j = 0; j < n_kt && ok; ++j) {
-                const int st = j & 1;
-                ok = mbar_wait(&kv_full[st], (j >> 1) & 1, abort_flag, err);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                unsigned char* kd = k_s + st * 2 * AT_HALF_BYTES;
-                unsigned char* vd = v_s + st * 2 * AT_HALF_BYTES;
-                // S = Q . K^T over d = 128: two halves of 64, four steps of 16 each
+            auto issue_scores = [&](int j) {       // S[j & 1] = Q . K(j)^T over d = 128: 8 steps of 16
+                unsigned char* kd = k_s + (j & 1) * 2 * AT_HALF_BYTES;
+                const unsigned d = tmem_s + (unsigned)((j & 1) * AT_N);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const unsigned long long da = umma_desc(q_s + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
                     const unsigned long long db = umma_desc(kd + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
-                    umma(tmem_s, da, db, idesc_s, ks > 0 ? 1u : 0u);
+                    umma(d, da, db, idesc_s, ks > 0 ? 1u : 0u);
                 }
-                umma_commit(s_full);
-                // wait for P (and, for the last tile, for the zeroed value rows)
+                umma_commit(&k_empty[j & 1]);
+                umma_commit(&s_full[j & 1]);
+            };
+            bool ok = mbar_wait(q_full, 0, abort_flag, err);
+            if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag, err);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                issue_scores(0);
+            }
+            for (int j = 0; j < n_kt && ok; ++j) {
+                const int st = j & 1;
+                if (j + 1 < n_kt) {         // the next tile's scores, while this tile's softmax runs
+                    ok = mbar_wait(&k_full[st ^ 1], ((j + 1) >> 1) & 1, abort_flag, err);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    issue_scores(j + 1);
+                }
                 ok = mbar_wait(p_ready, j & 1, abort_flag, err);
-                if (!ok) break;
-                if (j == n_kt - 1) ok = mbar_wait(v_fixed, 0, abort_flag, err);
+                if (ok) ok = mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, err);
+                if (ok && j == n_kt - 1) ok = mbar_wait(v_fixed, 0, abort_flag, err);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 // O += P . V over 128 keys: 8 steps of 16 keys; P is K-major (two halves of 64 keys),
                 // V is MN-major: 16 keys = two groups of 8 rows, the two d-halves AT_HALF_BYTES apart
+                unsigned char* vd = v_s + st * 2 * AT_HALF_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const unsigned long long da = umma_desc(p_s + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
                     const unsigned long long db = umma_desc_mn(vd + ks * 2 * 1024, AT_HALF_BYTES);
                     umma(tmem_o, da, db, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
                 }
-                umma_commit(&kv_empty[st]);
+                umma_commit(&v_empty[st]);
                 umma_commit(o_done);
             }
         }
@@ -216,37 +241,45 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const int row = quarter * 32 + lane;
         const int qpos = p0 + row;
         const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
+        const float sl2 = scale * 1.4426950408889634f;      // scores in units of log2(e): exp2 below
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int j = 0; j < n_kt; ++j) {
-            if (lane == 0) ok = mbar_wait(s_full, j & 1, abort_flag, err);
+            if (lane == 0) ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, err);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const int kbase = (kt_lo + j) * AT_N;
-            const bool edge = (kbase + AT_N - 1 > p0) || (window > 0 && kbase < p_last - window + 1 + AT_M);
-            // pass 1: the row's maximum
+            const int kbase = j * AT_N;
+            const bool edge = kbase + AT_N - 1 > p0;     // the tile touches the diagonal or the sequence's end
+            const unsigned s_addr = tmem_s + lane_addr + (unsigned)((j & 1) * AT_N);
+            unsigned sv[AT_N];
+            AT_LD32((sv + 0), s_addr + 0);
+            AT_LD32((sv + 32), s_addr + 32);
+            AT_LD32((sv + 64), s_addr + 64);
+            AT_LD32((sv + 96), s_addr + 96);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
             float tmax = -INFINITY;
 #pragma unroll
-            for (int c0 = 0; c0 < AT_N; c0 += 16) {
-                unsigned v[16];
-                AT_LD16(v, tmem_s + lane_addr + c0);
-                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    float s = __uint_as_float(v[i]) * scale;
-                    if (edge) {
-                        const int key = kbase + c0 + i;
-                        bool vis = key <= qpos;
-                        if (window > 0) vis = vis && key > qpos - window;
-                        if (!vis) s = -INFINITY;
-                    }
-                    tmax = fmaxf(tmax, s);
-                }
+            for (int i = 0; i < AT_N; ++i) {
+                float x = __uint_as_float(sv[i]) * sl2;
+                if (edge && kbase + i > qpos) x = -INFINITY;
+                sv[i] = __float_as_uint(x);
+                tmax = fmaxf(tmax, x);
             }
             const float m_new = fmaxf(m_run, tmax);
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            const float corr = (m_run == -INFINITY) ? 0.f : __expf(m_run - m_use);
+            const float corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_use);
+            // probabilities (exp2 of the difference), their sum, packed to bf16 in place
+            float psum = 0.f;
+#pragma unroll
+            for (int i = 0; i < AT_N; i += 2) {
+                const float e0 = exp2f(__uint_as_float(sv[i]) - m_use), e1 = exp2f(__uint_as_float(sv[i + 1]) - m_use);
+                psum += e0 + e1;
+                __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
+                sv[i >> 1] = *reinterpret_cast<unsigned*>(&b);
+            }
+            l_run = l_run * corr + psum;
+            m_run = m_new;
             // the previous P . V must have landed before O is touched or P is overwritten
             if (j > 0) {
                 if (lane == 0) ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, err);
@@ -255,48 +288,24 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll
-                    for (int c0 = 0; c0 < AT_D; c0 += 16) {
-                        unsigned v[16];
-                        AT_LD16(v, tmem_o + lane_addr + c0);
+                    for (int c0 = 0; c0 < AT_D; c0 += 32) {
+                        unsigned ov[32];
+                        AT_LD32(ov, tmem_o + lane_addr + c0);
                         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-                        AT_ST16(v, tmem_o + lane_addr + c0);
+                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+                        AT_ST32(ov, tmem_o + lane_addr + c0);
                     }
                     asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
                 }
             }
-            // pass 2: probabilities, their sum, P as bf16 in the K-major swizzled layout
-            float psum = 0.f;
+            // P into shared memory, K-major swizzled: 16 chunks of 8 keys (16 bytes) per row
 #pragma unroll
-            for (int c0 = 0; c0 < AT_N; c0 += 16) {
-                unsigned v[16];
-                AT_LD16(v, tmem_s + lane_addr + c0);
-                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-                unsigned pk[8];
-#pragma unroll
-                for (int i = 0; i < 16; i += 2) {
-                    float s0 = __uint_as_float(v[i]) * scale, s1 = __uint_as_float(v[i + 1]) * scale;
-                    if (edge) {
-                        const int key = kbase + c0 + i;
-                        bool v0 = key <= qpos, v1 = key + 1 <= qpos;
-                        if (window > 0) { v0 = v0 && key > qpos - window; v1 = v1 && key + 1 > qpos - window; }
-                        if (!v0) s0 = -INFINITY;
-                        if (!v1) s1 = -INFINITY;
-                    }
-                    const float e0 = __expf(s0 - m_use), e1 = __expf(s1 - m_use);
-                    psum += e0 + e1;
-                    __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
-                    pk[i >> 1] = *reinterpret_cast<unsigned*>(&b);
-                }
-                // keys c0 .. c0+15 of this row: two 16-byte chunks of half c0 / 64
-                unsigned char* half = p_s + (c0 >> 6) * AT_HALF_BYTES + row * 128;
-                const int ch = (c0 & 63) >> 3;
-                *reinterpret_cast<uint4*>(half + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                *reinterpret_cast<uint4*>(half + (((ch + 1) ^ (row & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            for (int c = 0; c < 16; ++c) {
+                unsigned char* half = p_s + (c >> 3) * AT_HALF_BYTES + row * 128;
+                *reinterpret_cast<uint4*>(half + (((c & 7) ^ (row & 7)) << 4)) =
+                    make_uint4(sv[c * 4], sv[c * 4 + 1], sv[c * 4 + 2], sv[c * 4 + 3]);
             }
-            l_run = l_run * corr + psum;
-            m_run = m_new;
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
@@ -312,19 +321,22 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
             bf16* dst = out + ((size_t)(t0 + row) * H + h) * AT_D;
 #pragma unroll
-            for (int c0 = 0; c0 < AT_D; c0 += 16) {
-                unsigned v[16];
-                AT_LD16(v, tmem_o + lane_addr + c0);
+            for (int c0 = 0; c0 < AT_D; c0 += 32) {
+                unsigned ov[32];
+                AT_LD32(ov, tmem_o + lane_addr + c0);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
                 if (row < rows_valid) {
-                    unsigned pk[8];
 #pragma unroll
-                    for (int i = 0; i < 16; i += 2) {
-                        __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
-                        pk[i >> 1] = *reinterpret_cast<unsigned*>(&b);
+                    for (int i = 0; i < 32; i += 8) {
+                        unsigned pk[4];
+#pragma unroll
+                        for (int e = 0; e < 8; e += 2) {
+                            __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(ov[i + e]) * inv,
+                                                                     __uint_as_float(ov[i + e + 1]) * inv);
+                            pk[e >> 1] = *reinterpret_cast<unsigned*>(&b);
+                        }
+                        *reinterpret_cast<uint4*>(dst + c0 + i) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                     }
-                    *reinterpret_cast<uint4*>(dst + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                    *reinterpret_cast<uint4*>(dst + c0 + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
                 }
             }
         }
@@ -333,14 +345,16 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     if (*abort_flag && tid == 0) {      // give copies in flight a bounded time to land
-        for (int s = 0; s < 2; ++s)
-            for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(&kv_full[s], 0) && !mbar_try_wait(&kv_full[s], 1); ++i) {}
+        for (int s = 0; s < 2; ++s) {
+            for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(&k_full[s], 0) && !mbar_try_wait(&k_full[s], 1); ++i) {}
+            for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(&v_full[s], 0) && !mbar_try_wait(&v_full[s], 1); ++i) {}
+        }
     }
     __syncthreads();
     if (warp == 1) {
         __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(256));
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(512));
     }
 }
 
@@ -368,6 +382,6 @@ extern "C" int aie_paged_attention_prefill_tc(const void* q, const void* k_pages
     cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AtSmem::bytes);
     paged_prefill_tc_kernel<<<dim3(n_tiles, H), AT_THREADS, AtSmem::bytes, stream>>>(
         mq, mk, mv, (bf16*)out, tiles, n_tiles, q_start, q_len, ctx_len, block_table, bt_width, num_pages, P, H, K,
-        window, scale, err);
+        scale, err);
     AIE_LAUNCH_CHECK();
 }

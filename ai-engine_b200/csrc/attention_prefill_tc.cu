@@ -12,11 +12,13 @@
 //                      the softmax of this one runs — later O += P . V (8 x tcgen05.mma; V is the
 //                      MN-major operand: its rows are keys), and commits to the mbarriers the
 //                      others wait on;
-//   warps 2-5          one thread per query row: read the row of S (tcgen05.ld, 128 columns in
-//                      flight at once), mask (causal, end of the sequence), running maximum and
-//                      sum in float32, rescale the row of O in tensor memory when the maximum
-//                      moved, write P as bf16 into shared memory in the swizzled K-major layout
-//                      the product reads.
+//   warps 2-9          two threads per query row, 64 key columns each (warps w and w + 4 read the
+//                      same quarter of tensor memory): read their half of the row of S
+//                      (tcgen05.ld), mask on tiles that touch the diagonal or the sequence's end,
+//                      agree on the row's running maximum through shared memory, keep a partial
+//                      running sum each (float32), rescale their half of the row of O in tensor
+//                      memory when the maximum moved, write P as bf16 into shared memory in the
+//                      swizzled K-major layout the product reads.
 // The value rows of keys past the sequence's last token are zeroed in shared memory before the
 // last tile's P . V, so a probability of 0 never meets what an unwritten cache slot holds.
 // Every wait is bounded (see tc_common.cuh); a wait that runs out raises the device error word.
@@ -26,12 +28,13 @@
 #define AT_M 128          // query rows per CTA
 #define AT_N 128          // keys per tile
 #define AT_D 128          // head size
-#define AT_THREADS 192
+#define AT_THREADS 320      // loader warp, MMA warp, 8 softmax warps
 #define AT_HALF_BYTES (128 * 64 * 2)      // one [128 x 64] bf16 swizzle atom column: 16 KB
 
 struct AtSmem {
-    // [alignment slack | 1024 B barriers | Q 32 KB | P 32 KB | K 2 x 32 KB | V 2 x 32 KB]
-    static constexpr int q_off = 1024, p_off = q_off + 2 * AT_HALF_BYTES, k_off = p_off + 2 * AT_HALF_BYTES,
+    // [alignment slack | 4 KB: barriers (256 B), row maxima exchange (2 KB at 1024) | Q 32 KB | P 32 KB |
+    //  K 2 x 32 KB | V 2 x 32 KB]
+    static constexpr int q_off = 4096, p_off = q_off + 2 * AT_HALF_BYTES, k_off = p_off + 2 * AT_HALF_BYTES,
                          v_off = k_off + 4 * AT_HALF_BYTES, end = v_off + 4 * AT_HALF_BYTES;
     static constexpr int bytes = 1024 + end;
 };
@@ -83,7 +86,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     unsigned long long* p_ready = s_full + 2;
     unsigned long long* o_done = p_ready + 1;
     unsigned long long* v_fixed = o_done + 1;
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(v_fixed + 1);
+    unsigned long long* mx_bar = v_fixed + 1;      // the two halves of a row exchange their maxima
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(mx_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     unsigned char* q_s = sm + AtSmem::q_off;
     unsigned char* p_s = sm + AtSmem::p_off;
@@ -110,9 +114,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             mbar_init(&v_empty[s], 1);
             mbar_init(&s_full[s], 1);
         }
-        mbar_init(p_ready, 4);          // one arrival per softmax warp
+        mbar_init(p_ready, 8);          // one arrival per softmax warp
         mbar_init(o_done, 1);
         mbar_init(v_fixed, 1);
+        mbar_init(mx_bar, 8);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -236,44 +241,60 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             }
         }
     } else {
-        // softmax: thread = query row
-        const int quarter = warp & 3;
+        // softmax: two threads per query row; this one has key columns [64 * ch, 64 * ch + 64) of each
+        // tile and the same columns of the row of O
+        const int quarter = warp & 3, ch = (warp - 2) >> 2;
         const int row = quarter * 32 + lane;
         const int qpos = p0 + row;
         const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
         const float sl2 = scale * 1.4426950408889634f;      // scores in units of log2(e): exp2 below
-        float m_run = -INFINITY, l_run = 0.f;
+        float* m_x = reinterpret_cast<float*>(sm + 1024);    // [2 buffers][2 halves][128] floats
+        float m_run = -INFINITY, l_run = 0.f;                // l_run: this thread's share of the row's sum
         bool ok = true;
         for (int j = 0; j < n_kt; ++j) {
             if (lane == 0) ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, err);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const int kbase = j * AT_N;
-            const bool edge = kbase + AT_N - 1 > p0;     // the tile touches the diagonal or the sequence's end
-            const unsigned s_addr = tmem_s + lane_addr + (unsigned)((j & 1) * AT_N);
-            unsigned sv[AT_N];
+            const int kbase = j * AT_N + ch * 64;
+            const bool edge = j * AT_N + AT_N - 1 > p0;     // the tile touches the diagonal or the sequence's end
+            const unsigned s_addr = tmem_s + lane_addr + (unsigned)((j & 1) * AT_N + ch * 64);
+            unsigned sv[64];
             AT_LD32((sv + 0), s_addr + 0);
             AT_LD32((sv + 32), s_addr + 32);
-            AT_LD32((sv + 64), s_addr + 64);
-            AT_LD32((sv + 96), s_addr + 96);
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
             float tmax = -INFINITY;
+            if (edge) {
 #pragma unroll
-            for (int i = 0; i < AT_N; ++i) {
-                float x = __uint_as_float(sv[i]) * sl2;
-                if (edge && kbase + i > qpos) x = -INFINITY;
-                sv[i] = __float_as_uint(x);
-                tmax = fmaxf(tmax, x);
+                for (int i = 0; i < 64; ++i) {
+                    if (kbase + i > qpos) sv[i] = 0xff800000u;      // -inf: not visible
+                    tmax = fmaxf(tmax, __uint_as_float(sv[i]));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) tmax = fmaxf(tmax, __uint_as_float(sv[i]));
             }
+            // the row's maximum over both halves (a bounded exchange through shared memory)
+            m_x[(j & 1) * 256 + ch * 128 + row] = tmax;
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive_plain(mx_bar);
+                ok = mbar_wait(mx_bar, j & 1, abort_flag, err);
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            __syncwarp();
+            tmax = fmaxf(tmax, m_x[(j & 1) * 256 + (ch ^ 1) * 128 + row]) * sl2;
             const float m_new = fmaxf(m_run, tmax);
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
             const float corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_use);
-            // probabilities (exp2 of the difference), their sum, packed to bf16 in place
+            // probabilities exp2(s * sl2 - m), this thread's share of their sum, packed to bf16 in place
             float psum = 0.f;
 #pragma unroll
-            for (int i = 0; i < AT_N; i += 2) {
-                const float e0 = exp2f(__uint_as_float(sv[i]) - m_use), e1 = exp2f(__uint_as_float(sv[i + 1]) - m_use);
+            for (int i = 0; i < 64; i += 2) {
+                float e0, e1;
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(fmaf(__uint_as_float(sv[i]), sl2, -m_use)));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(fmaf(__uint_as_float(sv[i + 1]), sl2, -m_use)));
                 psum += e0 + e1;
                 __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
                 sv[i >> 1] = *reinterpret_cast<unsigned*>(&b);
@@ -288,30 +309,42 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll
-                    for (int c0 = 0; c0 < AT_D; c0 += 32) {
+                    for (int c0 = 0; c0 < 64; c0 += 32) {
                         unsigned ov[32];
-                        AT_LD32(ov, tmem_o + lane_addr + c0);
+                        AT_LD32(ov, tmem_o + lane_addr + ch * 64 + c0);
                         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
                         for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
-                        AT_ST32(ov, tmem_o + lane_addr + c0);
+                        AT_ST32(ov, tmem_o + lane_addr + ch * 64 + c0);
                     }
                     asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
                 }
             }
-            // P into shared memory, K-major swizzled: 16 chunks of 8 keys (16 bytes) per row
+            // P into shared memory, K-major swizzled: this thread's 8 chunks of 8 keys (16 bytes)
+            {
+                unsigned char* half = p_s + ch * AT_HALF_BYTES + row * 128;
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                unsigned char* half = p_s + (c >> 3) * AT_HALF_BYTES + row * 128;
-                *reinterpret_cast<uint4*>(half + (((c & 7) ^ (row & 7)) << 4)) =
-                    make_uint4(sv[c * 4], sv[c * 4 + 1], sv[c * 4 + 2], sv[c * 4 + 3]);
+                for (int c = 0; c < 8; ++c)
+                    *reinterpret_cast<uint4*>(half + ((c ^ (row & 7)) << 4)) =
+                        make_uint4(sv[c * 4], sv[c * 4 + 1], sv[c * 4 + 2], sv[c * 4 + 3]);
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_plain(p_ready);
         }
-        // the last P . V, then the row of O
+        // the row's sum over both halves, the last P . V, then this thread's half of the row of O
+        if (ok) {
+            m_x[(n_kt & 1) * 256 + ch * 128 + row] = l_run;
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive_plain(mx_bar);
+                ok = mbar_wait(mx_bar, n_kt & 1, abort_flag, err);
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            __syncwarp();
+            if (ok) l_run += m_x[(n_kt & 1) * 256 + (ch ^ 1) * 128 + row];
+        }
         if (ok) {
             if (lane == 0) ok = mbar_wait(o_done, (n_kt - 1) & 1, abort_flag, err);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -319,11 +352,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-            bf16* dst = out + ((size_t)(t0 + row) * H + h) * AT_D;
+            bf16* dst = out + ((size_t)(t0 + row) * H + h) * AT_D + ch * 64;
 #pragma unroll
-            for (int c0 = 0; c0 < AT_D; c0 += 32) {
+            for (int c0 = 0; c0 < 64; c0 += 32) {
                 unsigned ov[32];
-                AT_LD32(ov, tmem_o + lane_addr + c0);
+                AT_LD32(ov, tmem_o + lane_addr + ch * 64 + c0);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
                 if (row < rows_valid) {
 #pragma unroll

@@ -132,43 +132,50 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + 256;
 
     if (warp == 0) {
+        // the loader warp: every lane issues its own TMA boxes (a box is one page x half a head, 2 KB at
+        // page 16: issued by one thread alone they would dominate the kernel)
         if (lane == 0) {
             // queries of this tile: rows t0 .. t0 + 127 of q [T, H * 128], columns of head h
             mbar_expect_tx(q_full, 2 * AT_HALF_BYTES);
             tma_load_2d(q_s, &map_q, q_full, h * AT_D, t0);
             tma_load_2d(q_s + AT_HALF_BYTES, &map_q, q_full, h * AT_D + 64, t0);
-            const int* bt = block_table + (size_t)r * bt_width;
-            bool ok = true;
-            for (int j = 0; j < n_kt && ok; ++j) {
-                const int st = j & 1;
-                const int kbase = j * AT_N;
-                // the pages of this tile that exist
-                int n_ok = 0;
-                for (int i = 0; i < ppt; ++i) {
-                    const int key0 = kbase + i * P, pidx = key0 / P;
-                    const int page = (key0 <= p_last && pidx < bt_width) ? bt[pidx] : -1;
-                    if (page >= 0 && page < num_pages) ++n_ok;
-                    else if (key0 <= p_last) atomicOr(err, AIE_DEV_PAGE_OOB);
-                }
-                for (int kv = 0; kv < 2 && ok; ++kv) {      // keys first: the scores need them sooner
-                    unsigned long long* full = kv ? &v_full[st] : &k_full[st];
-                    unsigned long long* empty = kv ? &v_empty[st] : &k_empty[st];
+        }
+        const int* bt = block_table + (size_t)r * bt_width;
+        bool ok = true;
+        for (int j = 0; j < n_kt && ok; ++j) {
+            const int st = j & 1;
+            const int kbase = j * AT_N;
+            // the pages of this tile that exist (every lane counts: the loops below are uniform)
+            int n_ok = 0;
+            for (int i = 0; i < ppt; ++i) {
+                const int key0 = kbase + i * P, pidx = key0 / P;
+                const int page = (key0 <= p_last && pidx < bt_width) ? bt[pidx] : -1;
+                if (page >= 0 && page < num_pages) ++n_ok;
+                else if (key0 <= p_last && lane == 0) atomicOr(err, AIE_DEV_PAGE_OOB);
+            }
+            for (int kv = 0; kv < 2 && ok; ++kv) {      // keys first: the scores need them sooner
+                unsigned long long* full = kv ? &v_full[st] : &k_full[st];
+                unsigned long long* empty = kv ? &v_empty[st] : &k_empty[st];
+                if (lane == 0) {
                     ok = mbar_wait(empty, ((j >> 1) & 1) ^ 1, abort_flag, err);
-                    if (!ok) break;
-                    if (n_ok > 0) mbar_expect_tx(full, (unsigned)n_ok * 2u * (unsigned)P * 128u);
-                    else mbar_arrive_plain(full);
-                    unsigned char* dst = (kv ? v_s : k_s) + st * 2 * AT_HALF_BYTES;
-                    const CUtensorMap* map = kv ? &map_v : &map_k;
-                    for (int i = 0; i < ppt; ++i) {
-                        const int key0 = kbase + i * P, pidx = key0 / P;
-                        const int page = (key0 <= p_last && pidx < bt_width) ? bt[pidx] : -1;
-                        if (page < 0 || page >= num_pages) continue;
-                        const int row = (page * K + kvh) * P;
-                        const int off = i * P * 128;       // rows of this page inside a [128 x 64] atom column
-                        tma_load_2d(dst + off, map, full, 0, row);
-                        tma_load_2d(dst + AT_HALF_BYTES + off, map, full, 64, row);
+                    if (ok) {
+                        if (n_ok > 0) mbar_expect_tx(full, (unsigned)n_ok * 2u * (unsigned)P * 128u);
+                        else mbar_arrive_plain(full);
                     }
                 }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+                unsigned char* dst = (kv ? v_s : k_s) + st * 2 * AT_HALF_BYTES;
+                const CUtensorMap* map = kv ? &map_v : &map_k;
+                for (int op = lane; op < 2 * ppt; op += 32) {      // op = (page of the tile, half of the head)
+                    const int i = op >> 1, half = op & 1;
+                    const int key0 = kbase + i * P, pidx = key0 / P;
+                    const int page = (key0 <= p_last && pidx < bt_width) ? bt[pidx] : -1;
+                    if (page < 0 || page >= num_pages) continue;
+                    // rows of this page inside a [128 x 64] atom column
+                    tma_load_2d(dst + half * AT_HALF_BYTES + i * P * 128, map, full, half * 64, (page * K + kvh) * P);
+                }
+                __syncwarp();
             }
         }
         __syncwarp();

@@ -334,3 +334,22 @@ extern "C" int aie_gemm_tc(const void* X, const void* W, void* C, int out_dtype,
 #undef GO
     return rc;
 }
+
+// A wait that nothing will ever satisfy, with a short limit: shows that a bounded wait gives up,
+// raises the device error word (AIE_DEV_WAIT_TIMEOUT) and lets the kernel return.
+__global__ void tc_wait_selftest_kernel(unsigned* err, int polls) {
+    __shared__ unsigned long long bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        bool done = false;
+        for (int i = 0; i < polls && !done; ++i) done = mbar_try_wait(&bar, 0);
+        if (!done) atomicOr(err, AIE_DEV_WAIT_TIMEOUT);
+    }
+}
+
+extern "C" int aie_tc_wait_selftest(unsigned* err, int polls, cudaStream_t stream) {
+    if (polls < 1 || polls > (1 << 20)) return AIE_BAD_ARG;
+    tc_wait_selftest_kernel<<<1, 32, 0, stream>>>(err, polls);
+    AIE_LAUNCH_CHECK();
+}

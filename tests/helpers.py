@@ -16,7 +16,7 @@ TINY_A = dict(
     vocab_size=256, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
     max_position_embeddings=128)
 # qk_gain scales the q and k projections so that attention scores have a standard
-# deviation near 1.6 (0.0256 g^2 for A, 0.064 g^2 for B, 0.038 g^2 for C, 0.077 g^2 for D): single keys
+# deviation near 1.6 (0.0256 g^2 for A, 0.064 g^2 for B, 0.038 g^2 for C, 0.077 g^2 for D, 0.102 g^2 for E): single keys
 # stand out, and bfloat16 rounding of the scores stays within the bf16 tolerance.
 TINY_A_OPTS = dict(seed=0, norm_std=0.0, block_size=16, qk_gain=8.0)
 
@@ -47,8 +47,16 @@ TINY_D = dict(
                       original_max_position_embeddings=256))
 TINY_D_OPTS = dict(seed=3, norm_std=0.05, block_size=16, qk_gain=4.5)
 
+# head size 128: the tcgen05 attention kernel for prompts and the 128-wide decode kernel
+TINY_E = dict(
+    architectures=["LlamaForCausalLM"], hidden_size=256, intermediate_size=320,
+    num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+    vocab_size=260, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+    max_position_embeddings=2048)
+TINY_E_OPTS = dict(seed=4, norm_std=0.05, block_size=16, qk_gain=4.0)
+
 TINY = {"A": (TINY_A, TINY_A_OPTS), "B": (TINY_B, TINY_B_OPTS), "C": (TINY_C, TINY_C_OPTS),
-        "D": (TINY_D, TINY_D_OPTS)}
+        "D": (TINY_D, TINY_D_OPTS), "E": (TINY_E, TINY_E_OPTS)}
 
 # Tolerances (max abs difference of logits; logits here are O(0.1 .. 1)).
 # float32 engine against the float64 plain implementation: the reference's own

@@ -51,15 +51,15 @@ def assert_same_until_a_close_call(got, want, margins, tol):
     assert len(got) == len(want)
 
 
-@pytest.mark.parametrize("name,dtype", [("A", "fp32"), ("A", "bf16"), ("B", "fp32"), ("B", "bf16")])
+@pytest.mark.parametrize("name,dtype", [("A", "fp32"), ("A", "bf16"), ("B", "fp32"), ("B", "bf16"), ("E", "bf16")])
 def test_greedy_generation_matches_the_plain_implementation(tmp_path, name, dtype):
     import ai_engine_b200 as aie
 
     d = make_model_dir(tmp_path, name)
     vocab = TINY[name][0]["vocab_size"]
-    lens = (5, 17, 33) if name == "A" else (1, 9, 40, 120)
+    lens = (5, 17, 33) if name == "A" else ((1, 9, 40, 120) if name == "B" else (3, 150, 300, 64))
     prompts = [random_ids(n, vocab, 30 + n) for n in lens]
-    eng = engine(d, name, dtype, max_num_batched_tokens=16 if name == "B" else 64)
+    eng = engine(d, name, dtype, max_num_batched_tokens=16 if name == "B" else (200 if name == "E" else 64))
     outs = eng.generate(prompts, aie.SamplingParams(max_tokens=8, ignore_eos=True))
     tol = TOL_F32 if dtype == "fp32" else TOL_BF16
     for p, o in zip(prompts, outs):

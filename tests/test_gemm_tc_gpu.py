@@ -127,3 +127,30 @@ def test_raw_parts_are_summed_by_the_norm_and_rotary_kernels():
     assert (r2.double() - s).abs().max() <= 1e-4
     assert (h.double() - pl.rms_norm(s.cpu(), nw.double().cpu(), 1e-5).to(DEV)).abs().max() <= 3e-2
     assert int(err.item()) == 0
+
+
+def test_a_bounded_wait_gives_up_and_the_step_runner_reports_it():
+    """A barrier that nothing arrives at: the wait runs out after its limit, the kernel sets the
+    device error word and returns; the context stays usable and check_errors raises."""
+    from ctypes import c_int, c_void_p
+
+    from ai_engine_b200.engine.step import StepError, StepRunner
+    from ai_engine_b200.kernels.loader import library
+
+    class _Model:
+        device = torch.device(DEV)
+        dtype = torch.float32
+
+        def has_host_parts(self):
+            return False
+
+    runner = StepRunner(_Model(), cache=None)
+    lib = library("gemm_tc.cu")
+    assert lib.aie_tc_wait_selftest(c_void_p(runner.err.data_ptr()), c_int(2000),
+                                    c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
+    torch.cuda.synchronize()
+    assert int(runner.err.item()) & 4
+    with pytest.raises(StepError, match="bounded wait"):
+        runner.check_errors()
+    runner.check_errors()                       # the word was cleared
+    run(8, 256, 512)                            # and the device still works

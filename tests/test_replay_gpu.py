@@ -40,7 +40,7 @@ def whole(rep, rid, ids):
 
 
 CASES = [("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16"),
-         ("D", "float32"), ("D", "bfloat16")]
+         ("D", "float32"), ("D", "bfloat16"), ("E", "bfloat16")]
 
 
 @pytest.mark.parametrize("name,dtype", CASES)

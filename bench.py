@@ -235,6 +235,47 @@ def time_gemms(torch, tokens):
     return out
 
 
+LLAMA32_1B = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermediate_size=8192,
+                  num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
+                  vocab_size=128256, max_position_embeddings=131072, rope_theta=500000.0, rms_norm_eps=1e-5,
+                  tie_word_embeddings=True,
+                  rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                    original_max_position_embeddings=8192))
+LLAMA32_3B = dict(LLAMA32_1B, hidden_size=3072, num_hidden_layers=28, num_attention_heads=24, head_dim=128)
+
+
+def run_workload(torch, aie, name):
+    """The two serving workloads of the baseline's other configurations, through Engine.generate():
+    serving1b — Llama-3.2-1B shape, 64 concurrent requests, prompts uniform in [128, 4096], 256 tokens each;
+    long3b    — Llama-3.2-3B shape, one 32,768-token prompt in 2,048-token portions, then 512 greedy tokens."""
+    g = torch.Generator().manual_seed(0)
+    if name == "serving1b":
+        cfg, n, new = LLAMA32_1B, 64, 256
+        lens = torch.randint(128, 4097, (n,), generator=g).tolist()
+        opts = dict(max_num_seqs=64, kv_cache_blocks=(sum(lens) + n * new) // PAGE + 2 * n, max_num_batched_tokens=2048,
+                    max_seq_len=8192)
+    else:
+        cfg, n, new = LLAMA32_3B, 1, 512
+        lens = [32768]
+        opts = dict(max_num_seqs=1, kv_cache_blocks=(32768 + new) // PAGE + 4, max_num_batched_tokens=2048,
+                    max_seq_len=32768 + new)
+    eng = aie.Engine(cfg, dtype="bf16", random_weights=True, seed=0, block_size=PAGE, **opts)
+    prompts = [torch.randint(0, cfg["vocab_size"], (l,), generator=g).tolist() for l in lens]
+    sp = aie.SamplingParams(max_tokens=new, ignore_eos=True)
+    eng.generate([prompts[0][:64]], aie.SamplingParams(max_tokens=4, ignore_eos=True))      # warm-up: kernels, graphs
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = eng.generate(prompts, sp)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    st = eng.stats()
+    assert all(len(o) == new for o in outs)
+    return {"workload": name, "requests": n, "prompt_tokens": sum(lens), "generated_tokens": n * new,
+            "seconds": round(dt, 3), "generated_tok_s": round(n * new / dt, 1),
+            "total_tok_s": round((sum(lens) + n * new) / dt, 1), "steps": st["steps"],
+            "preemptions": st["preemptions"], "mean_batch_tokens": round(st["batch_tokens"] / max(st["steps"], 1), 1)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -245,6 +286,8 @@ def main():
                     help="run fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--workload", choices=["serving1b", "long3b"], default=None,
+                    help="run one of the serving workloads through Engine.generate() and print its numbers")
     ap.add_argument("--only", choices=["decode", "prefill", "gemm"], default=None,
                     help="time one part only and print its numbers (for profiling)")
     a = ap.parse_args()
@@ -263,6 +306,9 @@ def main():
 
     warmup = max(a.warmup, 3)
     pk = peaks()
+    if a.workload:
+        print(json.dumps(run_workload(torch, aie, a.workload)))
+        return 0
     if a.only == "gemm":
         for k, v in time_gemms(torch, a.batch).items():
             print(k, json.dumps(v))

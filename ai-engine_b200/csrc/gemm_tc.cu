@@ -192,7 +192,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 for (int j = 0; j < 16; ++j) v[j] = 0u;      // a part without K blocks (or an abort) adds nothing
             }
             if (direct) {
-                if (n0 + r < N && ok) {
+                if (n0 + r < N) {        // a part without K blocks stores zeros: its consumer adds every part
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int t = t0 + c0 + j;

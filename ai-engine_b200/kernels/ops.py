@@ -173,6 +173,9 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, err: torch
     splits = splits or tc_splits(T, N, K, bn)
     if swiglu:
         splits = 1 if raw_parts else min(splits, 8)
+    kb = (K + 63) // 64
+    splits = max(1, min(splits, kb))
+    splits = -(-kb // -(-kb // splits))      # no part without K blocks: 64 blocks in 9 parts of 8 are 8 parts
     if raw_parts and splits > 1:
         out = torch.empty((splits, T, N), dtype=torch.float32, device=x.device)
     else:

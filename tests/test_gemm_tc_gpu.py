@@ -129,6 +129,28 @@ def test_raw_parts_are_summed_by_the_norm_and_rotary_kernels():
     assert int(err.item()) == 0
 
 
+@pytest.mark.parametrize("T,N,K,splits", [(40, 6144, 4096, 9), (64, 256, 1024, 7), (1, 384, 640, 16), (8, 128, 64, 3),
+                                          (33, 200, 4096, None), (64, 6144, 4096, None), (64, 3072, 8192, None),
+                                          (17, 5120, 3072, None), (64, 2048, 2048, None)])
+def test_unjoined_parts_cover_k_exactly(T, N, K, splits):
+    """K blocks that do not divide into the asked number of parts (64 blocks in 9 parts): no part is left
+    unwritten, whatever the output buffer held before (it is filled with NaN first)."""
+    from ai_engine_b200.kernels import ops
+
+    torch.manual_seed(T + N)
+    x = torch.randn(T, K, device=DEV).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    poison = torch.full((32, T, N), float("nan"), device=DEV)      # the allocator hands this memory out next
+    del poison
+    parts = ops.gemm_tc(x, w, torch.float32, err, splits=splits, raw_parts=True) if splits else ops.linear_parts(x, w, err)
+    assert bool(torch.isfinite(parts).all()), "a part of the output was not written"
+    got = parts.sum(0) if parts.dim() == 3 else parts
+    want = x.double() @ w.double().T
+    assert (got.double() - want).abs().max() <= 3e-5 * max(1.0, float(want.abs().max())) * max(1.0, (K / 4096) ** 0.5)
+    assert int(err.item()) == 0
+
+
 def test_a_bounded_wait_gives_up_and_the_step_runner_reports_it():
     """A barrier that nothing arrives at: the wait runs out after its limit, the kernel sets the
     device error word and returns; the context stays usable and check_errors raises."""

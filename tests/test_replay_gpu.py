@@ -189,3 +189,51 @@ def test_trace_run_program(tmp_path):
     assert np.abs(s0 - ref[[0, 29]]).max() <= TOL_F32
     assert np.abs(s2[0] - ref[39]).max() <= TOL_F32
     assert np.abs(s2[1] - ref[2]).max() <= TOL_F32
+
+
+FULL_SIZE_LAYERS = {
+    "llama3_8b": dict(hidden_size=4096, intermediate_size=14336, num_attention_heads=32, num_key_value_heads=8,
+                      head_dim=128, tie_word_embeddings=False),
+    "llama32_3b": dict(hidden_size=3072, intermediate_size=8192, num_attention_heads=24, num_key_value_heads=8,
+                       head_dim=128, tie_word_embeddings=True,
+                       rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                         original_max_position_embeddings=8192)),
+    "llama32_1b": dict(hidden_size=2048, intermediate_size=8192, num_attention_heads=32, num_key_value_heads=8,
+                       head_dim=64, tie_word_embeddings=True,
+                       rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                         original_max_position_embeddings=8192)),
+}
+
+
+@pytest.mark.parametrize("name", sorted(FULL_SIZE_LAYERS))
+def test_full_size_layers(tmp_path, name):
+    """One layer with the layer sizes of Llama-3-8B, Llama-3.2-3B and Llama-3.2-1B (a reduced vocabulary keeps
+    the folder small): the kernel configurations that full-size models take — products cut along K, tcgen05
+    attention, grouped decode — against the plain implementation: a request whole, in portions and token by
+    token, with a second request's tokens in the same steps."""
+    import ai_engine_b200 as aie
+    from ai_engine_b200.engine.replay import Replayer
+
+    raw = dict(architectures=["LlamaForCausalLM"], num_hidden_layers=1, vocab_size=4096, rope_theta=500000.0,
+               rms_norm_eps=1e-5, max_position_embeddings=8192, **FULL_SIZE_LAYERS[name])
+    d = os.path.join(str(tmp_path), name)
+    aie.write_random_model(aie.LlamaConfig.from_dict(raw), d, seed=5, dtype="bfloat16")
+    ids, other = random_ids(200, 4096, 31), random_ids(70, 4096, 32)
+    ref, ref_other = plain_logits(d, ids, torch.float32), plain_logits(d, other, torch.float32)
+    scale = max(1.0, float(np.abs(ref).max()))
+    for dtype, tol in (("bfloat16", TOL_BF16 * scale), ("float32", 2e-3 * scale)):
+        rep = Replayer(d, dtype, max_tokens=320, block_size=16)
+        got = [rep.run_step([dict(id="x", tokens=ids[:150], want=list(range(150)))]).numpy()]
+        out = rep.run_step([dict(id="x", tokens=ids[150:190], want=list(range(40))),
+                            dict(id="y", tokens=other[:60], want=list(range(60)))]).numpy()
+        got.append(out[:40])
+        got_other = [out[40:]]
+        for k in range(10):
+            out = rep.run_step([dict(id="y", tokens=[other[60 + k]], want=[0]),
+                                dict(id="x", tokens=[ids[190 + k]], want=[0])]).numpy()
+            got_other.append(out[:1])
+            got.append(out[1:])
+        for what, g, r in (("x", got, ref), ("y", got_other, ref_other)):
+            err = np.abs(np.concatenate(g) - r).max(axis=1)
+            assert err.max() <= tol, (f"{dtype}, request {what}: first wrong token {int(np.argmax(err > tol))}: "
+                                      f"{err.max()} (logits up to {scale})")

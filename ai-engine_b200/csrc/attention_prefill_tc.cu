@@ -2,23 +2,27 @@
 // (head size 128): scores and outputs live in tensor memory, operands come from shared memory
 // filled by TMA, softmax is float32 in registers.
 //
-// One CTA owns 128 query tokens of one head.  For each tile of 128 keys:
-//   warp 0 (one lane)  loads the key tile and the value tile page by page with TMA (one box of
-//                      [page, 64] per page and half of the head; the pool of a layer is one matrix
-//                      of [pages * kv_heads * page, 128] rows), 128-byte swizzled, a ring of two
-//                      buffers for keys and one of two for values;
-//   warp 1 (one lane)  issues S = Q . K^T (8 x tcgen05.mma of K = 16) into one of two score
-//                      buffers in tensor memory — the scores of the next tile are computed while
-//                      the softmax of this one runs — later O += P . V (8 x tcgen05.mma; V is the
-//                      MN-major operand: its rows are keys), and commits to the mbarriers the
-//                      others wait on;
+// One CTA owns 128 query tokens of one head; two CTAs share an SM (about 100 KB of shared memory and
+// 256 columns of tensor memory each), so one's products run while the other's softmax does.  For each
+// tile of 128 keys:
+//   warp 0             loads the key tile and the value tile page by page with TMA (one box of
+//                      [page, 64] per page and half of the head, every lane issuing its own boxes; the
+//                      pool of a layer is one matrix of [pages * kv_heads * page, 128] rows),
+//                      128-byte swizzled, one buffer for keys and one for values: the next keys are
+//                      requested as soon as the scores are done, the next values after P . V;
+//   warp 1 (one lane)  issues S = Q . K^T (8 x tcgen05.mma of K = 16) into tensor memory, later
+//                      O += P . V (8 x tcgen05.mma; P is read from tensor memory, where the softmax
+//                      wrote it over the scores; V is the MN-major operand: its rows are keys), and
+//                      commits to the mbarriers the others wait on;
 //   warps 2-9          two threads per query row, 64 key columns each (warps w and w + 4 read the
 //                      same quarter of tensor memory): read their half of the row of S
 //                      (tcgen05.ld), mask on tiles that touch the diagonal or the sequence's end,
-//                      agree on the row's running maximum through shared memory, keep a partial
-//                      running sum each (float32), rescale their half of the row of O in tensor
-//                      memory when the maximum moved, write P as bf16 into shared memory in the
-//                      swizzled K-major layout the product reads.
+//                      agree on the row's maximum through shared memory, keep a partial running sum
+//                      each (float32), write P as bf16 pairs into tensor memory.  The reference
+//                      maximum of a row moves only when the new maximum exceeds it by more than 8
+//                      (in units of log2 e): P stays below 2^8 and the row of O in tensor memory is
+//                      rescaled on few tiles; the final division by the running sum makes the
+//                      result the same softmax.
 // The value rows of keys past the sequence's last token are zeroed in shared memory before the
 // last tile's P . V, so a probability of 0 never meets what an unwritten cache slot holds.
 // Every wait is bounded (see tc_common.cuh); a wait that runs out raises the device error word.
@@ -31,11 +35,12 @@
 #define AT_THREADS 320      // loader warp, MMA warp, 8 softmax warps
 #define AT_HALF_BYTES (128 * 64 * 2)      // one [128 x 64] bf16 swizzle atom column: 16 KB
 
+#define AT_RESCALE_STEP 8.0f     // a row's reference maximum moves in steps of more than this (log2 units)
+
 struct AtSmem {
-    // [alignment slack | 4 KB: barriers (256 B), row maxima exchange (2 KB at 1024) | Q 32 KB | P 32 KB |
-    //  K 2 x 32 KB | V 2 x 32 KB]
-    static constexpr int q_off = 4096, p_off = q_off + 2 * AT_HALF_BYTES, k_off = p_off + 2 * AT_HALF_BYTES,
-                         v_off = k_off + 4 * AT_HALF_BYTES, end = v_off + 4 * AT_HALF_BYTES;
+    // [alignment slack | 4 KB: barriers (256 B), row maxima exchange (2 KB at 1024) | Q 32 KB | K 32 KB | V 32 KB]
+    static constexpr int q_off = 4096, k_off = q_off + 2 * AT_HALF_BYTES, v_off = k_off + 2 * AT_HALF_BYTES,
+                         end = v_off + 2 * AT_HALF_BYTES;
     static constexpr int bytes = 1024 + end;
 };
 
@@ -68,7 +73,7 @@ __device__ __forceinline__ unsigned long long umma_desc_mn(const void* tile, uns
                    "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),   \
                    "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory")
 
-__global__ void __launch_bounds__(AT_THREADS)
+__global__ void __launch_bounds__(AT_THREADS, 2)
 paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                         const int* __restrict__ tiles, int n_tiles, const int* __restrict__ q_start,
@@ -78,19 +83,18 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     extern __shared__ unsigned char at_raw[];
     unsigned char* sm = reinterpret_cast<unsigned char*>(((size_t)at_raw + 1023) & ~(size_t)1023);
     unsigned long long* q_full = reinterpret_cast<unsigned long long*>(sm);
-    unsigned long long* k_full = q_full + 1;       // [2]
-    unsigned long long* k_empty = k_full + 2;      // [2]
-    unsigned long long* v_full = k_empty + 2;      // [2]
-    unsigned long long* v_empty = v_full + 2;      // [2]
-    unsigned long long* s_full = v_empty + 2;      // [2]
-    unsigned long long* p_ready = s_full + 2;
+    unsigned long long* k_full = q_full + 1;
+    unsigned long long* k_empty = k_full + 1;
+    unsigned long long* v_full = k_empty + 1;
+    unsigned long long* v_empty = v_full + 1;
+    unsigned long long* s_full = v_empty + 1;
+    unsigned long long* p_ready = s_full + 1;
     unsigned long long* o_done = p_ready + 1;
     unsigned long long* v_fixed = o_done + 1;
     unsigned long long* mx_bar = v_fixed + 1;      // the two halves of a row exchange their maxima
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(mx_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     unsigned char* q_s = sm + AtSmem::q_off;
-    unsigned char* p_s = sm + AtSmem::p_off;
     unsigned char* k_s = sm + AtSmem::k_off;
     unsigned char* v_s = sm + AtSmem::v_off;
 
@@ -107,13 +111,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
     if (tid == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&k_full[s], 1);
-            mbar_init(&k_empty[s], 1);
-            mbar_init(&v_full[s], 1);
-            mbar_init(&v_empty[s], 1);
-            mbar_init(&s_full[s], 1);
-        }
+        mbar_init(k_full, 1);
+        mbar_init(k_empty, 1);
+        mbar_init(v_full, 1);
+        mbar_init(v_empty, 1);
+        mbar_init(s_full, 1);
         mbar_init(p_ready, 8);          // one arrival per softmax warp
         mbar_init(o_done, 1);
         mbar_init(v_fixed, 1);
@@ -122,14 +124,14 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
-    if (warp == 1) {    // tensor memory: columns [0, 128) and [128, 256) scores, [256, 384) outputs
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(tmem_slot)), "r"(512));
+    if (warp == 1) {    // tensor memory: columns [0, 128) scores (P over the first 64), [128, 256) outputs
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(tmem_slot)), "r"(256));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + 256;
+    const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + 128;
 
     if (warp == 0) {
         // the loader warp: every lane issues its own TMA boxes (a box is one page x half a head, 2 KB at
@@ -143,7 +145,6 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const int* bt = block_table + (size_t)r * bt_width;
         bool ok = true;
         for (int j = 0; j < n_kt && ok; ++j) {
-            const int st = j & 1;
             const int kbase = j * AT_N;
             // the pages of this tile that exist (every lane counts: the loops below are uniform)
             int n_ok = 0;
@@ -154,10 +155,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 else if (key0 <= p_last && lane == 0) atomicOr(err, AIE_DEV_PAGE_OOB);
             }
             for (int kv = 0; kv < 2 && ok; ++kv) {      // keys first: the scores need them sooner
-                unsigned long long* full = kv ? &v_full[st] : &k_full[st];
-                unsigned long long* empty = kv ? &v_empty[st] : &k_empty[st];
+                unsigned long long* full = kv ? v_full : k_full;
+                unsigned long long* empty = kv ? v_empty : k_empty;
                 if (lane == 0) {
-                    ok = mbar_wait(empty, ((j >> 1) & 1) ^ 1, abort_flag, err);
+                    ok = mbar_wait(empty, (j & 1) ^ 1, abort_flag, err);
                     if (ok) {
                         if (n_ok > 0) mbar_expect_tx(full, (unsigned)n_ok * 2u * (unsigned)P * 128u);
                         else mbar_arrive_plain(full);
@@ -165,7 +166,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
-                unsigned char* dst = (kv ? v_s : k_s) + st * 2 * AT_HALF_BYTES;
+                unsigned char* dst = kv ? v_s : k_s;
                 const CUtensorMap* map = kv ? &map_v : &map_k;
                 for (int op = lane; op < 2 * ppt; op += 32) {      // op = (page of the tile, half of the head)
                     const int i = op >> 1, half = op & 1;
@@ -181,14 +182,14 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         __syncwarp();
         // the last tile: zero the value rows of keys past the sequence's end (whole warp)
         {
-            const int j = n_kt - 1, st = j & 1;
+            const int j = n_kt - 1;
             const int first_bad = p_last + 1 - j * AT_N;       // rows [first_bad, 128) are not keys
             bool ok = true;
             if (first_bad < AT_N) {
-                if (lane == 0) ok = mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, err);
+                if (lane == 0) ok = mbar_wait(v_full, j & 1, abort_flag, err);
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (ok) {
-                    unsigned char* vd = v_s + st * 2 * AT_HALF_BYTES;
+                    unsigned char* vd = v_s;
                     const int n_bad = AT_N - first_bad;
                     for (int i = lane; i < n_bad * 16; i += 32) {      // 16 chunks of 16 bytes per row (two halves)
                         const int row = first_bad + i / 16, c = i % 16;
@@ -203,47 +204,34 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     } else if (warp == 1) {
         if (lane == 0) {
             const unsigned idesc_s = umma_idesc(AT_N), idesc_o = umma_idesc(AT_D, true);
-            auto issue_scores = [&](int j) {       // S[j & 1] = Q . K(j)^T over d = 128: 8 steps of 16
-                unsigned char* kd = k_s + (j & 1) * 2 * AT_HALF_BYTES;
-                const unsigned d = tmem_s + (unsigned)((j & 1) * AT_N);
+            bool ok = mbar_wait(q_full, 0, abort_flag, err);
+            for (int j = 0; j < n_kt && ok; ++j) {
+                // S = Q . K(j)^T over d = 128: 8 steps of 16.  The tensor pipe runs what one thread issues
+                // in order, so these scores land after the previous P . V has read P from the same columns.
+                ok = mbar_wait(k_full, j & 1, abort_flag, err);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const unsigned long long da = umma_desc(q_s + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
-                    const unsigned long long db = umma_desc(kd + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
-                    umma(d, da, db, idesc_s, ks > 0 ? 1u : 0u);
+                    const unsigned long long db = umma_desc(k_s + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
+                    umma(tmem_s, da, db, idesc_s, ks > 0 ? 1u : 0u);
                 }
-                umma_commit(&k_empty[j & 1]);
-                umma_commit(&s_full[j & 1]);
-            };
-            bool ok = mbar_wait(q_full, 0, abort_flag, err);
-            if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag, err);
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                issue_scores(0);
-            }
-            for (int j = 0; j < n_kt && ok; ++j) {
-                const int st = j & 1;
-                if (j + 1 < n_kt) {         // the next tile's scores, while this tile's softmax runs
-                    ok = mbar_wait(&k_full[st ^ 1], ((j + 1) >> 1) & 1, abort_flag, err);
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    issue_scores(j + 1);
-                }
+                umma_commit(k_empty);
+                umma_commit(s_full);
                 ok = mbar_wait(p_ready, j & 1, abort_flag, err);
-                if (ok) ok = mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, err);
+                if (ok) ok = mbar_wait(v_full, j & 1, abort_flag, err);
                 if (ok && j == n_kt - 1) ok = mbar_wait(v_fixed, 0, abort_flag, err);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                // O += P . V over 128 keys: 8 steps of 16 keys; P is K-major (two halves of 64 keys),
+                // O += P . V over 128 keys: 8 steps of 16 keys; P is in tensor memory (two keys to a column),
                 // V is MN-major: 16 keys = two groups of 8 rows, the two d-halves AT_HALF_BYTES apart
-                unsigned char* vd = v_s + st * 2 * AT_HALF_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
-                    const unsigned long long da = umma_desc(p_s + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
-                    const unsigned long long db = umma_desc_mn(vd + ks * 2 * 1024, AT_HALF_BYTES);
-                    umma(tmem_o, da, db, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                    const unsigned long long db = umma_desc_mn(v_s + ks * 2 * 1024, AT_HALF_BYTES);
+                    umma_a_tmem(tmem_o, tmem_s + (unsigned)(ks * 8), db, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
                 }
-                umma_commit(&v_empty[st]);
+                umma_commit(v_empty);
                 umma_commit(o_done);
             }
         }
@@ -259,13 +247,13 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         float m_run = -INFINITY, l_run = 0.f;                // l_run: this thread's share of the row's sum
         bool ok = true;
         for (int j = 0; j < n_kt; ++j) {
-            if (lane == 0) ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, err);
+            if (lane == 0) ok = mbar_wait(s_full, j & 1, abort_flag, err);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int kbase = j * AT_N + ch * 64;
             const bool edge = j * AT_N + AT_N - 1 > p0;     // the tile touches the diagonal or the sequence's end
-            const unsigned s_addr = tmem_s + lane_addr + (unsigned)((j & 1) * AT_N + ch * 64);
+            const unsigned s_addr = tmem_s + lane_addr + (unsigned)(ch * 64);
             unsigned sv[64];
             AT_LD32((sv + 0), s_addr + 0);
             AT_LD32((sv + 32), s_addr + 32);
@@ -292,9 +280,13 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             if (!ok) break;
             __syncwarp();
             tmax = fmaxf(tmax, m_x[(j & 1) * 256 + (ch ^ 1) * 128 + row]) * sl2;
-            const float m_new = fmaxf(m_run, tmax);
+            // the row's reference maximum: the same decision in both threads of the row
+            float m_new = m_run, corr = 1.0f;
+            if (tmax > m_run + AT_RESCALE_STEP) {
+                m_new = tmax;
+                corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - tmax);
+            }
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            const float corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_use);
             // probabilities exp2(s * sl2 - m), this thread's share of their sum, packed to bf16 in place
             float psum = 0.f;
 #pragma unroll
@@ -327,15 +319,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                     asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
                 }
             }
-            // P into shared memory, K-major swizzled: this thread's 8 chunks of 8 keys (16 bytes)
-            {
-                unsigned char* half = p_s + ch * AT_HALF_BYTES + row * 128;
-#pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    *reinterpret_cast<uint4*>(half + ((c ^ (row & 7)) << 4)) =
-                        make_uint4(sv[c * 4], sv[c * 4 + 1], sv[c * 4 + 2], sv[c * 4 + 3]);
-            }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            // P into tensor memory, over the first 64 columns of this tile's scores (both threads of the row
+            // have read their scores: the exchange above came after the loads): two keys to a column
+            AT_ST32(sv, tmem_s + lane_addr + (unsigned)(ch * 32));
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_plain(p_ready);
@@ -385,16 +372,14 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     if (*abort_flag && tid == 0) {      // give copies in flight a bounded time to land
-        for (int s = 0; s < 2; ++s) {
-            for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(&k_full[s], 0) && !mbar_try_wait(&k_full[s], 1); ++i) {}
-            for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(&v_full[s], 0) && !mbar_try_wait(&v_full[s], 1); ++i) {}
-        }
+        for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(k_full, 0) && !mbar_try_wait(k_full, 1); ++i) {}
+        for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(v_full, 0) && !mbar_try_wait(v_full, 1); ++i) {}
     }
     __syncthreads();
     if (warp == 1) {
         __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(512));
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(256));
     }
 }
 

@@ -81,6 +81,77 @@ __global__ void rope_kv_write_kernel(const I* __restrict__ qkv, int parts, size_
     }
 }
 
+// Portions of prompts in bfloat16: one block per token.  The token's angles are computed once
+// (float32, the same expression as above) and kept in shared memory; every thread rotates 8 pairs
+// of one head with 16-byte loads and stores.  Needs rot_dim % 16 == 0 and d % 8 == 0.
+__global__ void __launch_bounds__(256)
+rope_kv_write_token_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf16* __restrict__ k_pages,
+                           bf16* __restrict__ v_pages, const int* __restrict__ positions,
+                           const int* __restrict__ token_req, const int* __restrict__ block_table, int bt_width,
+                           int num_pages, int P, int H, int K, int d, int rot_dim,
+                           const float* __restrict__ inv_freq, int write, unsigned* err) {
+    extern __shared__ float rope_cs[];       // [half] cosines, [half] sines
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const int pos = positions[t];
+    const int half = rot_dim / 2;
+    for (int i = tid; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
+        rope_cs[i] = cs;
+        rope_cs[half + i] = sn;
+    }
+    int page = -1;
+    if (write) {
+        const int pidx = pos / P;
+        page = (pidx < bt_width && pos >= 0) ? block_table[(size_t)token_req[t] * bt_width + pidx] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (tid == 0) atomicOr(err, AIE_DEV_PAGE_OOB);
+            page = -1;
+        }
+    }
+    __syncthreads();
+    const bf16* x = qkv + (size_t)t * (H + 2 * K) * d;
+    const size_t slot = page >= 0 ? ((size_t)page * K * P + (pos % P)) * d : 0;      // + kv head * P * d
+    const int cph = half / 8, heads = H + (page >= 0 ? K : 0);
+    for (int w = tid; w < heads * cph; w += blockDim.x) {
+        const int head = w / cph, c = (w % cph) * 8;
+        const bf16* src = x + (size_t)head * d + c;
+        bf16* dst = head < H ? q_out + ((size_t)t * H + head) * d + c : k_pages + slot + (size_t)(head - H) * P * d + c;
+        const uint4 a = *reinterpret_cast<const uint4*>(src), b = *reinterpret_cast<const uint4*>(src + half);
+        const bf16* x1 = reinterpret_cast<const bf16*>(&a);
+        const bf16* x2 = reinterpret_cast<const bf16*>(&b);
+        uint4 oa, ob;
+        bf16* o1 = reinterpret_cast<bf16*>(&oa);
+        bf16* o2 = reinterpret_cast<bf16*>(&ob);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float cs = rope_cs[c + e], sn = rope_cs[half + c + e];
+            const float u = to_f32<bf16>(x1[e]), v = to_f32<bf16>(x2[e]);
+            o1[e] = from_f32<bf16>(u * cs - v * sn);
+            o2[e] = from_f32<bf16>(u * sn + v * cs);
+        }
+        *reinterpret_cast<uint4*>(dst) = oa;
+        *reinterpret_cast<uint4*>(dst + half) = ob;
+    }
+    // what is not rotated: the tails of q and k heads, and the v heads (16-byte copies)
+    const int tail = (d - rot_dim) / 8;
+    for (int w = tid; w < heads * tail; w += blockDim.x) {
+        const int head = w / tail, c = rot_dim + (w % tail) * 8;
+        bf16* dst = head < H ? q_out + ((size_t)t * H + head) * d + c : k_pages + slot + (size_t)(head - H) * P * d + c;
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(x + (size_t)head * d + c);
+    }
+    if (page >= 0) {
+        const int dc = d / 8;
+        for (int w = tid; w < K * dc; w += blockDim.x) {
+            const int kh = w / dc, c = (w % dc) * 8;
+            *reinterpret_cast<uint4*>(v_pages + slot + (size_t)kh * P * d + c) =
+                *reinterpret_cast<const uint4*>(x + (size_t)(H + K + kh) * d + c);
+        }
+    }
+}
+
 extern "C" int aie_rope_kv_write(const void* qkv, int in_dtype, int parts, long long part_stride,
                                  void* q_out, void* k_pages, void* v_pages, int dtype, const int* positions, const int* token_req,
                                  const int* block_table, int bt_width, int num_pages, int P, int T,
@@ -88,6 +159,11 @@ extern "C" int aie_rope_kv_write(const void* qkv, int in_dtype, int parts, long 
                                  int write, unsigned* err, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (rot_dim % 2 || rot_dim > d || rot_dim < 0) return AIE_BAD_ARG;
+    if (T >= 64 && dtype == AIE_BF16 && in_dtype == AIE_BF16 && parts == 1 && rot_dim % 16 == 0 && d % 8 == 0 &&
+        !((size_t)qkv & 15) && !((size_t)q_out & 15) && !((size_t)k_pages & 15) && !((size_t)v_pages & 15))
+        return (int)launch_pdl(rope_kv_write_token_kernel, dim3(T), dim3(256), (size_t)rot_dim * sizeof(float), stream,
+                               (const bf16*)qkv, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, positions, token_req,
+                               block_table, bt_width, num_pages, P, H, K, d, rot_dim, inv_freq, write, err);
     // few tokens: one warp per block, so that the work spreads over the machine; many: 8 warps
     const int warps = T >= 256 ? 8 : 1;
     if ((H + 2 * K + warps - 1) / warps > 65535) return AIE_UNSUPPORTED;

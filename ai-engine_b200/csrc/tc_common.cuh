@@ -64,6 +64,15 @@ __device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsi
                  ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
                  : "memory");
 }
+// the same with the A operand in tensor memory: 128 lanes = rows, 16-bit elements packed two to a
+// 32-bit column along K (a step of K = 16 is 8 columns)
+__device__ __forceinline__ void umma_a_tmem(unsigned tmem_d, unsigned tmem_a, unsigned long long b, unsigned idesc,
+                                            unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}\n"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+                 : "memory");
+}
 __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc_smem(bar)) : "memory");
 }

@@ -235,6 +235,50 @@ def time_gemms(torch, tokens):
     return out
 
 
+def time_attention(torch, tokens, context):
+    """The attention kernels for a portion of `tokens` prompt tokens after `context` cached ones, alone, at the
+    flagship head layout (32 heads on 8 kv heads of 128, pages of 16): the tcgen05 kernel and the mma.sync
+    kernel, median of 10 with L2 flushed between runs; TFLOP/s counts the causal half only."""
+    from ai_engine_b200.kernels import ops
+
+    H, K, d, P = 32, 8, 128, 16
+    total = context + tokens
+    n_pages = (total + P - 1) // P
+    dev = "cuda"
+    torch.manual_seed(0)
+    kp = (torch.randn(n_pages, K, P, d, device=dev) * 0.5).bfloat16()
+    vp = torch.randn(n_pages, K, P, d, device=dev).bfloat16()
+    q = torch.randn(tokens, H, d, device=dev).bfloat16()
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=dev)
+    bt = torch.randperm(n_pages, device=dev).int().view(1, -1).contiguous()
+    tiles = i32([[0, o] for o in range(0, tokens, ops.PREFILL_TILE)])
+    qs, ql, cl = i32([0]), i32([tokens]), i32([context])
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    outs, row = {}, {}
+    impls = {"tcgen05": lambda o: ops.paged_attention_prefill_tc(q, kp, vp, tiles, qs, ql, cl, bt, d ** -0.5, 0, err, o),
+             "mma_sync": lambda o: ops.paged_attention_prefill(q, kp, vp, tiles, qs, ql, cl, bt, d ** -0.5, 0, err, o)}
+    flops = 4.0 * d * H * (tokens * context + tokens * (tokens + 1) / 2)
+    for name, fn in impls.items():
+        outs[name] = torch.zeros_like(q)
+        for _ in range(3):
+            fn(outs[name])
+        ts = []
+        for _ in range(10):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn(outs[name])
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3)
+        us = sorted(ts)[len(ts) // 2]
+        row[name] = dict(us=round(us, 1), tflops=round(flops / us / 1e6, 1))
+    assert int(err.item()) == 0
+    row["max_difference"] = float((outs["tcgen05"].float() - outs["mma_sync"].float()).abs().max())
+    return {f"attention[{tokens} tokens after {context}]": row}
+
+
 LLAMA32_1B = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermediate_size=8192,
                   num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
                   vocab_size=128256, max_position_embeddings=131072, rope_theta=500000.0, rms_norm_eps=1e-5,
@@ -288,7 +332,7 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--workload", choices=["serving1b", "long3b"], default=None,
                     help="run one of the serving workloads through Engine.generate() and print its numbers")
-    ap.add_argument("--only", choices=["decode", "prefill", "gemm"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "gemm", "attention"], default=None,
                     help="time one part only and print its numbers (for profiling)")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -312,6 +356,11 @@ def main():
     if a.only == "gemm":
         for k, v in time_gemms(torch, a.batch).items():
             print(k, json.dumps(v))
+        return 0
+    if a.only == "attention":
+        for tokens, context in ((PREFILL_TOKENS, 0), (PREFILL_TOKENS, 6144), (512, 0), (200, 1000)):
+            for k, v in time_attention(torch, tokens, context).items():
+                print(k, json.dumps(v))
         return 0
     cfg = dict(LLAMA3_8B)
     cfg["num_hidden_layers"] = a.layers

@@ -348,9 +348,11 @@ def test_bad_page_is_flagged_not_followed():
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,K,d,P,rot", [(4, 2, 16, 16, 16), (5, 1, 32, 8, 32), (6, 3, 48, 4, 32),
                                          (32, 8, 128, 16, 128), (2, 2, 64, 16, 0)])
-def test_rope_kv_write(dtype, H, K, d, P, rot):
+@pytest.mark.parametrize("many", [False, True])
+def test_rope_kv_write(dtype, H, K, d, P, rot, many):
+    """many: enough tokens for the block-per-token kernel that portions of prompts take in bfloat16."""
     torch.manual_seed(5)
-    lens, q_lens = [9, 41, 3], [9, 2, 1]
+    lens, q_lens = ([130, 100, 3], [90, 40, 1]) if many else ([9, 41, 3], [9, 2, 1])
     s = paged_setup(dtype, H, K, d, P, lens, q_lens, seed=6)
     T = sum(q_lens)
     qkv = torch.randn(T, (H + 2 * K) * d, device=DEV).to(dtype)

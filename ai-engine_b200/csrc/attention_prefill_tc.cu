@@ -14,11 +14,10 @@
 //                      O += P . V (8 x tcgen05.mma; P is read from tensor memory, where the softmax
 //                      wrote it over the scores; V is the MN-major operand: its rows are keys), and
 //                      commits to the mbarriers the others wait on;
-//   warps 2-9          two threads per query row, 64 key columns each (warps w and w + 4 read the
-//                      same quarter of tensor memory): read their half of the row of S
-//                      (tcgen05.ld), mask on tiles that touch the diagonal or the sequence's end,
-//                      agree on the row's maximum through shared memory, keep a partial running sum
-//                      each (float32), write P as bf16 pairs into tensor memory.  The reference
+//   warps 2-5          one thread per query row: read the row of S (tcgen05.ld, 128 registers), mask
+//                      on tiles that touch the diagonal or the sequence's end, take the row's
+//                      maximum and running sum (float32; the scale-and-subtract and the sum as packed
+//                      f32x2 instructions), write P as bf16 pairs into tensor memory.  The reference
 //                      maximum of a row moves only when the new maximum exceeds it by more than 8
 //                      (in units of log2 e): P stays below 2^8 and the row of O in tensor memory is
 //                      rescaled on few tiles; the final division by the running sum makes the
@@ -32,14 +31,14 @@
 #define AT_M 128          // query rows per CTA
 #define AT_N 128          // keys per tile
 #define AT_D 128          // head size
-#define AT_THREADS 320      // loader warp, MMA warp, 8 softmax warps
+#define AT_THREADS 192      // loader warp, MMA warp, 4 softmax warps
 #define AT_HALF_BYTES (128 * 64 * 2)      // one [128 x 64] bf16 swizzle atom column: 16 KB
 
 #define AT_RESCALE_STEP 8.0f     // a row's reference maximum moves in steps of more than this (log2 units)
 
 struct AtSmem {
-    // [alignment slack | 4 KB: barriers (256 B), row maxima exchange (2 KB at 1024) | Q 32 KB | K 32 KB | V 32 KB]
-    static constexpr int q_off = 4096, k_off = q_off + 2 * AT_HALF_BYTES, v_off = k_off + 2 * AT_HALF_BYTES,
+    // [alignment slack | 1 KB: barriers | Q 32 KB | K 32 KB | V 32 KB]
+    static constexpr int q_off = 1024, k_off = q_off + 2 * AT_HALF_BYTES, v_off = k_off + 2 * AT_HALF_BYTES,
                          end = v_off + 2 * AT_HALF_BYTES;
     static constexpr int bytes = 1024 + end;
 };
@@ -54,6 +53,27 @@ __device__ __forceinline__ unsigned long long umma_desc_mn(const void* tile, uns
     d |= (unsigned long long)1 << 46;
     d |= (unsigned long long)2 << 61;
     return d;
+}
+
+__device__ __forceinline__ float at_max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+__device__ __forceinline__ unsigned long long at_pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ float at_lo(unsigned long long v) {
+    float lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+    return lo;
+}
+__device__ __forceinline__ float at_hi(unsigned long long v) {
+    float lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+    return hi;
 }
 
 // 32 consecutive columns of this thread's lane of tensor memory
@@ -91,8 +111,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     unsigned long long* p_ready = s_full + 1;
     unsigned long long* o_done = p_ready + 1;
     unsigned long long* v_fixed = o_done + 1;
-    unsigned long long* mx_bar = v_fixed + 1;      // the two halves of a row exchange their maxima
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(mx_bar + 1);
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(v_fixed + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     unsigned char* q_s = sm + AtSmem::q_off;
     unsigned char* k_s = sm + AtSmem::k_off;
@@ -116,10 +135,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         mbar_init(v_full, 1);
         mbar_init(v_empty, 1);
         mbar_init(s_full, 1);
-        mbar_init(p_ready, 8);          // one arrival per softmax warp
+        mbar_init(p_ready, 4);          // one arrival per softmax warp
         mbar_init(o_done, 1);
         mbar_init(v_fixed, 1);
-        mbar_init(mx_bar, 8);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -236,109 +254,89 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             }
         }
     } else {
-        // softmax: two threads per query row; this one has key columns [64 * ch, 64 * ch + 64) of each
-        // tile and the same columns of the row of O
-        const int quarter = warp & 3, ch = (warp - 2) >> 2;
+        // softmax: one thread per query row (warp w reads lanes 32 * (w % 4) .. + 31 of tensor memory)
+        const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const int qpos = p0 + row;
         const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
         const float sl2 = scale * 1.4426950408889634f;      // scores in units of log2(e): exp2 below
-        float* m_x = reinterpret_cast<float*>(sm + 1024);    // [2 buffers][2 halves][128] floats
-        float m_run = -INFINITY, l_run = 0.f;                // l_run: this thread's share of the row's sum
+        float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int j = 0; j < n_kt; ++j) {
             if (lane == 0) ok = mbar_wait(s_full, j & 1, abort_flag, err);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const int kbase = j * AT_N + ch * 64;
-            const bool edge = j * AT_N + AT_N - 1 > p0;     // the tile touches the diagonal or the sequence's end
-            const unsigned s_addr = tmem_s + lane_addr + (unsigned)(ch * 64);
-            unsigned sv[64];
-            AT_LD32((sv + 0), s_addr + 0);
-            AT_LD32((sv + 32), s_addr + 32);
+            const int kbase = j * AT_N;
+            const bool edge = kbase + AT_N - 1 > p0;     // the tile touches the diagonal or the sequence's end
+            unsigned sv[128];
+            AT_LD32((sv + 0), tmem_s + lane_addr + 0);
+            AT_LD32((sv + 32), tmem_s + lane_addr + 32);
+            AT_LD32((sv + 64), tmem_s + lane_addr + 64);
+            AT_LD32((sv + 96), tmem_s + lane_addr + 96);
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-            float tmax = -INFINITY;
             if (edge) {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
+                for (int i = 0; i < 128; ++i)
                     if (kbase + i > qpos) sv[i] = 0xff800000u;      // -inf: not visible
-                    tmax = fmaxf(tmax, __uint_as_float(sv[i]));
-                }
-            } else {
+            }
+            float tmax = -INFINITY, tmax2 = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 64; ++i) tmax = fmaxf(tmax, __uint_as_float(sv[i]));
+            for (int i = 0; i < 128; i += 4) {
+                tmax = at_max3(tmax, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+                tmax2 = at_max3(tmax2, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
             }
-            // the row's maximum over both halves (a bounded exchange through shared memory)
-            m_x[(j & 1) * 256 + ch * 128 + row] = tmax;
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive_plain(mx_bar);
-                ok = mbar_wait(mx_bar, j & 1, abort_flag, err);
-            }
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-            if (!ok) break;
-            __syncwarp();
-            tmax = fmaxf(tmax, m_x[(j & 1) * 256 + (ch ^ 1) * 128 + row]) * sl2;
-            // the row's reference maximum: the same decision in both threads of the row
+            tmax = fmaxf(tmax, tmax2) * sl2;
+            // the row's reference maximum moves only by more than AT_RESCALE_STEP
             float m_new = m_run, corr = 1.0f;
             if (tmax > m_run + AT_RESCALE_STEP) {
                 m_new = tmax;
                 corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - tmax);
             }
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            // probabilities exp2(s * sl2 - m), this thread's share of their sum, packed to bf16 in place
-            float psum = 0.f;
+            // probabilities exp2(s * sl2 - m) (two to a packed multiply-add), their sum, packed to bf16 in place
+            const unsigned long long sl2_2 = at_pack2(sl2, sl2), negm_2 = at_pack2(-m_use, -m_use);
+            unsigned long long psum2 = 0ull;
 #pragma unroll
-            for (int i = 0; i < 64; i += 2) {
+            for (int i = 0; i < 128; i += 2) {
+                unsigned long long x2;
+                asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(x2) : "l"(at_pack2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1]))), "l"(sl2_2), "l"(negm_2));
                 float e0, e1;
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(fmaf(__uint_as_float(sv[i]), sl2, -m_use)));
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(fmaf(__uint_as_float(sv[i + 1]), sl2, -m_use)));
-                psum += e0 + e1;
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(at_lo(x2)));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(at_hi(x2)));
+                asm("add.rn.f32x2 %0, %1, %2;" : "=l"(psum2) : "l"(psum2), "l"(at_pack2(e0, e1)));
                 __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
                 sv[i >> 1] = *reinterpret_cast<unsigned*>(&b);
             }
-            l_run = l_run * corr + psum;
+            l_run = l_run * corr + (at_lo(psum2) + at_hi(psum2));
             m_run = m_new;
-            // the previous P . V must have landed before O is touched or P is overwritten
-            if (j > 0) {
+            // rows whose reference maximum moved rescale their row of O (the previous P . V has landed: the
+            // scores of this tile were issued after it)
+            if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
                 if (lane == 0) ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, err);
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll
-                    for (int c0 = 0; c0 < 64; c0 += 32) {
-                        unsigned ov[32];
-                        AT_LD32(ov, tmem_o + lane_addr + ch * 64 + c0);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                for (int c0 = 0; c0 < AT_D; c0 += 32) {
+                    unsigned ov[32];
+                    AT_LD32(ov, tmem_o + lane_addr + c0);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
-                        AT_ST32(ov, tmem_o + lane_addr + ch * 64 + c0);
-                    }
-                    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                    for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+                    AT_ST32(ov, tmem_o + lane_addr + c0);
                 }
+                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             }
-            // P into tensor memory, over the first 64 columns of this tile's scores (both threads of the row
-            // have read their scores: the exchange above came after the loads): two keys to a column
-            AT_ST32(sv, tmem_s + lane_addr + (unsigned)(ch * 32));
+            // P into tensor memory over the first 64 columns of this row's scores: two keys to a column
+            AT_ST32((sv + 0), tmem_s + lane_addr + 0);
+            AT_ST32((sv + 32), tmem_s + lane_addr + 32);
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_plain(p_ready);
         }
-        // the row's sum over both halves, the last P . V, then this thread's half of the row of O
-        if (ok) {
-            m_x[(n_kt & 1) * 256 + ch * 128 + row] = l_run;
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive_plain(mx_bar);
-                ok = mbar_wait(mx_bar, n_kt & 1, abort_flag, err);
-            }
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-            __syncwarp();
-            if (ok) l_run += m_x[(n_kt & 1) * 256 + (ch ^ 1) * 128 + row];
-        }
+        // the last P . V, then this row of O divided by the row's sum
         if (ok) {
             if (lane == 0) ok = mbar_wait(o_done, (n_kt - 1) & 1, abort_flag, err);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -346,11 +344,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-            bf16* dst = out + ((size_t)(t0 + row) * H + h) * AT_D + ch * 64;
+            bf16* dst = out + ((size_t)(t0 + row) * H + h) * AT_D;
 #pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 32) {
+            for (int c0 = 0; c0 < AT_D; c0 += 32) {
                 unsigned ov[32];
-                AT_LD32(ov, tmem_o + lane_addr + ch * 64 + c0);
+                AT_LD32(ov, tmem_o + lane_addr + c0);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
                 if (row < rows_valid) {
 #pragma unroll

@@ -2,22 +2,24 @@
 // (head size 128): scores and outputs live in tensor memory, operands come from shared memory
 // filled by TMA, softmax is float32 in registers.
 //
-// One CTA owns 128 query tokens of one head; two CTAs share an SM (about 100 KB of shared memory and
-// 256 columns of tensor memory each), so one's products run while the other's softmax does.  For each
-// tile of 128 keys:
-//   warp 0             loads the key tile and the value tile page by page with TMA (one box of
-//                      [page, 64] per page and half of the head, every lane issuing its own boxes; the
-//                      pool of a layer is one matrix of [pages * kv_heads * page, 128] rows),
-//                      128-byte swizzled, one buffer for keys and one for values: the next keys are
-//                      requested as soon as the scores are done, the next values after P . V;
-//   warp 1 (one lane)  issues S = Q . K^T (8 x tcgen05.mma of K = 16) into tensor memory, later
-//                      O += P . V (8 x tcgen05.mma; P is read from tensor memory, where the softmax
-//                      wrote it over the scores; V is the MN-major operand: its rows are keys), and
-//                      commits to the mbarriers the others wait on;
-//   warps 2-5          one thread per query row: read the row of S (tcgen05.ld, 128 registers), mask
-//                      on tiles that touch the diagonal or the sequence's end, take the row's
-//                      maximum and running sum (float32; the scale-and-subtract and the sum as packed
-//                      f32x2 instructions), write P as bf16 pairs into tensor memory.  The reference
+// One CTA owns 128 query tokens of TWO heads of one group (heads that read the same kv head: they share
+// every key and value tile); a group with an odd number of heads leaves the second place of its last CTA
+// empty.  While the softmax of one head runs, the tensor pipe works on the other.  For each tile of 128 keys:
+//   warp 0             loads the key tile and the value tile page by page with TMA: one box per page,
+//                      lane i issuing the box of the tile's page i (the pool of a layer is seen as
+//                      [groups of 8 rows][2 halves of the head][8 rows][64], so a box lands as 1 KB
+//                      128-byte-swizzled atoms, the two halves of a group side by side), a ring of
+//                      two buffers for keys and one of two for values; the loop has no division and
+//                      reads the next tile's page id while this tile's boxes are issued;
+//   warp 1 (one lane)  issues, head by head, O += P . V of this tile (8 x tcgen05.mma; P is read from
+//                      tensor memory, where the softmax wrote it over the scores; V is the MN-major
+//                      operand: its rows are keys) and then S = Q . K^T of the next tile (8 x
+//                      tcgen05.mma of K = 16), and commits to the mbarriers the others wait on;
+//   warps 2-5, 6-9     softmax of the first and of the second head, one thread per query row: read the
+//                      row of S (tcgen05.ld, 128 registers), mask on tiles that touch the diagonal or
+//                      the sequence's end, take the row's maximum and running sum (float32; the
+//                      scale-and-subtract and the sum as packed f32x2 instructions), write P as bf16
+//                      pairs into tensor memory.  The reference
 //                      maximum of a row moves only when the new maximum exceeds it by more than 8
 //                      (in units of log2 e): P stays below 2^8 and the row of O in tensor memory is
 //                      rescaled on few tiles; the final division by the running sum makes the
@@ -31,29 +33,34 @@
 #define AT_M 128          // query rows per CTA
 #define AT_N 128          // keys per tile
 #define AT_D 128          // head size
-#define AT_THREADS 192      // loader warp, MMA warp, 4 softmax warps
+#define AT_THREADS 320      // loader warp, MMA warp, 4 softmax warps for each of the two heads
 #define AT_HALF_BYTES (128 * 64 * 2)      // one [128 x 64] bf16 swizzle atom column: 16 KB
 
 #define AT_RESCALE_STEP 8.0f     // a row's reference maximum moves in steps of more than this (log2 units)
 
 struct AtSmem {
-    // [alignment slack | 1 KB: barriers | Q 32 KB | K 32 KB | V 32 KB]
-    static constexpr int q_off = 1024, k_off = q_off + 2 * AT_HALF_BYTES, v_off = k_off + 2 * AT_HALF_BYTES,
-                         end = v_off + 2 * AT_HALF_BYTES;
+    // [alignment slack | 1 KB: barriers | Q 2 heads x 32 KB | K 2 x 32 KB | V 2 x 32 KB]
+    static constexpr int q_off = 1024, k_off = q_off + 4 * AT_HALF_BYTES, v_off = k_off + 4 * AT_HALF_BYTES,
+                         end = v_off + 4 * AT_HALF_BYTES;
     static constexpr int bytes = 1024 + end;
 };
 
 // shared-memory descriptor of an MN-major operand: rows of 64 elements (128 bytes) along MN,
-// groups of 8 K-rows 1024 bytes apart, blocks of 64 MN elements `lbo` bytes apart
+// groups of 8 K-rows 2048 bytes apart, blocks of 64 MN elements `lbo` bytes apart
 __device__ __forceinline__ unsigned long long umma_desc_mn(const void* tile, unsigned lbo_bytes) {
     unsigned long long d = 0;
     d |= (unsigned long long)((tc_smem(tile) >> 4) & 0x3FFFu);
     d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)(2048 >> 4) << 32;
     d |= (unsigned long long)1 << 46;
     d |= (unsigned long long)2 << 61;
     return d;
 }
+
+#define AT_ST16(v, taddr)                                                                                             \
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" \
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), \
+                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory")
 
 __device__ __forceinline__ float at_max3(float a, float b, float c) {
     float r;
@@ -93,7 +100,7 @@ __device__ __forceinline__ float at_hi(unsigned long long v) {
                    "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),   \
                    "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory")
 
-__global__ void __launch_bounds__(AT_THREADS, 2)
+__global__ void __launch_bounds__(AT_THREADS, 1)
 paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                         const int* __restrict__ tiles, int n_tiles, const int* __restrict__ q_start,
@@ -103,24 +110,26 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     extern __shared__ unsigned char at_raw[];
     unsigned char* sm = reinterpret_cast<unsigned char*>(((size_t)at_raw + 1023) & ~(size_t)1023);
     unsigned long long* q_full = reinterpret_cast<unsigned long long*>(sm);
-    unsigned long long* k_full = q_full + 1;
-    unsigned long long* k_empty = k_full + 1;
-    unsigned long long* v_full = k_empty + 1;
-    unsigned long long* v_empty = v_full + 1;
-    unsigned long long* s_full = v_empty + 1;
-    unsigned long long* p_ready = s_full + 1;
-    unsigned long long* o_done = p_ready + 1;
-    unsigned long long* v_fixed = o_done + 1;
+    unsigned long long* k_full = q_full + 1;       // [2] stages
+    unsigned long long* k_empty = k_full + 2;      // [2]
+    unsigned long long* v_full = k_empty + 2;      // [2]
+    unsigned long long* v_empty = v_full + 2;      // [2]
+    unsigned long long* s_full = v_empty + 2;      // [2] heads
+    unsigned long long* p_ready = s_full + 2;      // [2] heads
+    unsigned long long* o_done = p_ready + 2;      // [2] heads
+    unsigned long long* v_fixed = o_done + 2;
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(v_fixed + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    unsigned char* q_s = sm + AtSmem::q_off;
-    unsigned char* k_s = sm + AtSmem::k_off;
+    unsigned char* q_s = sm + AtSmem::q_off;       // head g at + g * 2 * AT_HALF_BYTES
+    unsigned char* k_s = sm + AtSmem::k_off;       // stage st at + st * 2 * AT_HALF_BYTES
     unsigned char* v_s = sm + AtSmem::v_off;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile_i = n_tiles - 1 - (int)blockIdx.x;      // later tiles hold more keys: start them first
     const int r = tiles[2 * tile_i], q_off = tiles[2 * tile_i + 1];
-    const int h = blockIdx.y, kvh = h / (H / K);
+    const int G = H / K, pairs = (G + 1) / 2;
+    const int kvh = blockIdx.y / pairs, h0 = kvh * G + 2 * ((int)blockIdx.y % pairs);
+    const int n_heads = (h0 + 1 < (kvh + 1) * G) ? 2 : 1;      // heads of this CTA: h0 and, if the group has it, h0 + 1
     const int t0 = q_start[r] + q_off;
     const int rows_valid = min(AT_M, q_len[r] - q_off);
     const int p0 = ctx_len[r] + q_off;                 // position of the tile's first query
@@ -130,88 +139,90 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
     if (tid == 0) {
         mbar_init(q_full, 1);
-        mbar_init(k_full, 1);
-        mbar_init(k_empty, 1);
-        mbar_init(v_full, 1);
-        mbar_init(v_empty, 1);
-        mbar_init(s_full, 1);
-        mbar_init(p_ready, 4);          // one arrival per softmax warp
-        mbar_init(o_done, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1);
+            mbar_init(&v_empty[s], 1);
+            mbar_init(&s_full[s], 1);
+            mbar_init(&p_ready[s], 4);      // one arrival per softmax warp of the head
+            mbar_init(&o_done[s], 1);
+        }
         mbar_init(v_fixed, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
-    if (warp == 1) {    // tensor memory: columns [0, 128) scores (P over the first 64), [128, 256) outputs
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(tmem_slot)), "r"(256));
+    if (warp == 1) {    // tensor memory: scores of head g at columns [128 g, 128 g + 128) (P over the first 64),
+                        // outputs of head g at [256 + 128 g, 256 + 128 g + 128)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(tmem_slot)), "r"(512));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + 128;
+    const unsigned tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // the loader warp: every lane issues its own TMA boxes (a box is one page x half a head, 2 KB at
-        // page 16: issued by one thread alone they would dominate the kernel)
-        if (lane == 0) {
-            // queries of this tile: rows t0 .. t0 + 127 of q [T, H * 128], columns of head h
-            mbar_expect_tx(q_full, 2 * AT_HALF_BYTES);
-            tma_load_2d(q_s, &map_q, q_full, h * AT_D, t0);
-            tma_load_2d(q_s + AT_HALF_BYTES, &map_q, q_full, h * AT_D + 64, t0);
+            if (lane == 0) {
+            // queries of this tile: rows t0 .. t0 + 127 of q [T, H * 128], columns of heads h0 (and h0 + 1)
+            mbar_expect_tx(q_full, (unsigned)n_heads * 2u * AT_HALF_BYTES);
+            for (int g = 0; g < n_heads; ++g) {
+                tma_load_2d(q_s + (2 * g) * AT_HALF_BYTES, &map_q, q_full, (h0 + g) * AT_D, t0);
+                tma_load_2d(q_s + (2 * g + 1) * AT_HALF_BYTES, &map_q, q_full, (h0 + g) * AT_D + 64, t0);
+            }
         }
+        // lane i owns page i of every key tile: one box per page (all 128 columns of its P keys); the id of
+        // the next tile's page is read while this tile's boxes are issued
         const int* bt = block_table + (size_t)r * bt_width;
+        const int lp = 31 - __clz(P);                      // P is a power of two
+        auto page_of = [&](int jj) {
+            const int pidx = jj * ppt + lane;
+            return (lane < ppt && (pidx << lp) <= p_last && pidx < bt_width) ? bt[pidx] : -1;
+        };
+        int page = page_of(0);
         bool ok = true;
         for (int j = 0; j < n_kt && ok; ++j) {
-            const int kbase = j * AT_N;
-            // the pages of this tile that exist (every lane counts: the loops below are uniform)
-            int n_ok = 0;
-            for (int i = 0; i < ppt; ++i) {
-                const int key0 = kbase + i * P, pidx = key0 / P;
-                const int page = (key0 <= p_last && pidx < bt_width) ? bt[pidx] : -1;
-                if (page >= 0 && page < num_pages) ++n_ok;
-                else if (key0 <= p_last && lane == 0) atomicOr(err, AIE_DEV_PAGE_OOB);
-            }
+            const int st = j & 1;
+            const int page_next = j + 1 < n_kt ? page_of(j + 1) : -1;
+            const int n_pages = min(ppt, ((p_last - j * AT_N) >> lp) + 1);      // pages of this tile that hold keys
+            const bool have = lane < n_pages;
+            const bool valid = have && page >= 0 && page < num_pages;
+            if (have && !valid) atomicOr(err, AIE_DEV_PAGE_OOB);
+            // a missing page is flagged; page 0 stands in for it so that the byte count of the barrier holds
+            const int group0 = (((valid ? page : 0) * K + kvh) << lp) >> 3;     // first group of 8 rows of the page
             for (int kv = 0; kv < 2 && ok; ++kv) {      // keys first: the scores need them sooner
-                unsigned long long* full = kv ? v_full : k_full;
-                unsigned long long* empty = kv ? v_empty : k_empty;
+                unsigned long long* full = kv ? &v_full[st] : &k_full[st];
+                unsigned long long* empty = kv ? &v_empty[st] : &k_empty[st];
                 if (lane == 0) {
-                    ok = mbar_wait(empty, (j & 1) ^ 1, abort_flag, err);
-                    if (ok) {
-                        if (n_ok > 0) mbar_expect_tx(full, (unsigned)n_ok * 2u * (unsigned)P * 128u);
-                        else mbar_arrive_plain(full);
-                    }
+                    ok = mbar_wait(empty, ((j >> 1) & 1) ^ 1, abort_flag, err);
+                    if (ok) mbar_expect_tx(full, (unsigned)n_pages * (unsigned)P * 256u);
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
-                unsigned char* dst = kv ? v_s : k_s;
-                const CUtensorMap* map = kv ? &map_v : &map_k;
-                for (int op = lane; op < 2 * ppt; op += 32) {      // op = (page of the tile, half of the head)
-                    const int i = op >> 1, half = op & 1;
-                    const int key0 = kbase + i * P, pidx = key0 / P;
-                    const int page = (key0 <= p_last && pidx < bt_width) ? bt[pidx] : -1;
-                    if (page < 0 || page >= num_pages) continue;
-                    // rows of this page inside a [128 x 64] atom column
-                    tma_load_2d(dst + half * AT_HALF_BYTES + i * P * 128, map, full, half * 64, (page * K + kvh) * P);
-                }
+                if (have)
+                    tma_load_4d((kv ? v_s : k_s) + st * 2 * AT_HALF_BYTES + lane * P * 256, kv ? &map_v : &map_k, full,
+                                0, 0, 0, group0);
                 __syncwarp();
             }
+            page = page_next;
         }
         __syncwarp();
         // the last tile: zero the value rows of keys past the sequence's end (whole warp)
         {
-            const int j = n_kt - 1;
+            const int j = n_kt - 1, st = j & 1;
             const int first_bad = p_last + 1 - j * AT_N;       // rows [first_bad, 128) are not keys
-            bool ok = true;
+            bool ok2 = true;
             if (first_bad < AT_N) {
-                if (lane == 0) ok = mbar_wait(v_full, j & 1, abort_flag, err);
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (ok) {
-                    unsigned char* vd = v_s;
+                if (lane == 0) ok2 = mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, err);
+                ok2 = __shfl_sync(0xffffffffu, ok2 ? 1 : 0, 0) != 0;
+                if (ok2) {
+                    unsigned char* vd = v_s + st * 2 * AT_HALF_BYTES;
                     const int n_bad = AT_N - first_bad;
                     for (int i = lane; i < n_bad * 16; i += 32) {      // 16 chunks of 16 bytes per row (two halves)
                         const int row = first_bad + i / 16, c = i % 16;
-                        *reinterpret_cast<uint4*>(vd + (c / 8) * AT_HALF_BYTES + row * 128 + (c % 8) * 16) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(vd + ((row >> 3) * 2 + (c >> 3)) * 1024 + (row & 7) * 128 + (c & 7) * 16) =
+                            make_uint4(0, 0, 0, 0);
                     }
                     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 }
@@ -222,69 +233,95 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     } else if (warp == 1) {
         if (lane == 0) {
             const unsigned idesc_s = umma_idesc(AT_N), idesc_o = umma_idesc(AT_D, true);
+            // S of head g = Q_g . K^T over d = 128: 8 steps of 16, keys from stage st
+            auto issue_scores = [&](int g, int st) {
+                unsigned char* qd = q_s + g * 2 * AT_HALF_BYTES;
+                unsigned char* kd = k_s + st * 2 * AT_HALF_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const unsigned long long da = umma_desc(qd + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
+                    const unsigned long long db = umma_desc(kd + (ks >> 2) * 1024, 2048) + 2 * (ks & 3);
+                    umma(tmem_base + (unsigned)(g * AT_N), da, db, idesc_s, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(&s_full[g]);
+                if (g == n_heads - 1) umma_commit(&k_empty[st]);
+            };
             bool ok = mbar_wait(q_full, 0, abort_flag, err);
+            if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag, err);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                for (int g = 0; g < n_heads; ++g) issue_scores(g, 0);
+            }
             for (int j = 0; j < n_kt && ok; ++j) {
-                // S = Q . K(j)^T over d = 128: 8 steps of 16.  The tensor pipe runs what one thread issues
-                // in order, so these scores land after the previous P . V has read P from the same columns.
-                ok = mbar_wait(k_full, j & 1, abort_flag, err);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const int st = j & 1;
+                for (int g = 0; g < n_heads && ok; ++g) {
+                    ok = mbar_wait(&p_ready[g], j & 1, abort_flag, err);
+                    if (ok && g == 0) {
+                        ok = mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, err);
+                        if (ok && j == n_kt - 1) ok = mbar_wait(v_fixed, 0, abort_flag, err);
+                    }
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    // O_g += P_g . V over 128 keys: 8 steps of 16 keys; P is in tensor memory (two keys to a
+                    // column), V is MN-major: 16 keys = two groups of 8 rows, the two d-halves AT_HALF_BYTES apart
+                    unsigned char* vd = v_s + st * 2 * AT_HALF_BYTES;
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const unsigned long long da = umma_desc(q_s + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
-                    const unsigned long long db = umma_desc(k_s + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
-                    umma(tmem_s, da, db, idesc_s, ks > 0 ? 1u : 0u);
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const unsigned long long db = umma_desc_mn(vd + ks * 2 * 2048, 1024);
+                        umma_a_tmem(tmem_base + (unsigned)(256 + g * AT_D), tmem_base + (unsigned)(g * AT_N + ks * 8), db,
+                                    idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&o_done[g]);
+                    if (g == n_heads - 1) umma_commit(&v_empty[st]);
+                    // the head's scores of the next tile, over the P just read (the tensor pipe runs what one
+                    // thread issues in order); the other head's softmax runs meanwhile
+                    if (j + 1 < n_kt) {
+                        if (g == 0) {
+                            ok = mbar_wait(&k_full[st ^ 1], ((j + 1) >> 1) & 1, abort_flag, err);
+                            if (!ok) break;
+                            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                        }
+                        issue_scores(g, st ^ 1);
+                    }
                 }
-                umma_commit(k_empty);
-                umma_commit(s_full);
-                ok = mbar_wait(p_ready, j & 1, abort_flag, err);
-                if (ok) ok = mbar_wait(v_full, j & 1, abort_flag, err);
-                if (ok && j == n_kt - 1) ok = mbar_wait(v_fixed, 0, abort_flag, err);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                // O += P . V over 128 keys: 8 steps of 16 keys; P is in tensor memory (two keys to a column),
-                // V is MN-major: 16 keys = two groups of 8 rows, the two d-halves AT_HALF_BYTES apart
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const unsigned long long db = umma_desc_mn(v_s + ks * 2 * 1024, AT_HALF_BYTES);
-                    umma_a_tmem(tmem_o, tmem_s + (unsigned)(ks * 8), db, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-                }
-                umma_commit(v_empty);
-                umma_commit(o_done);
             }
         }
     } else {
-        // softmax: one thread per query row (warp w reads lanes 32 * (w % 4) .. + 31 of tensor memory)
+        // softmax of head g: one thread per query row (warp w reads lanes 32 * (w % 4) .. + 31 of tensor memory)
+        const int g = (warp - 2) >> 2;
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const int qpos = p0 + row;
         const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
+        const unsigned tmem_s = tmem_base + (unsigned)(g * AT_N), tmem_o = tmem_base + (unsigned)(256 + g * AT_D);
         const float sl2 = scale * 1.4426950408889634f;      // scores in units of log2(e): exp2 below
         float m_run = -INFINITY, l_run = 0.f;
-        bool ok = true;
-        for (int j = 0; j < n_kt; ++j) {
-            if (lane == 0) ok = mbar_wait(s_full, j & 1, abort_flag, err);
+        bool ok = g < n_heads;
+        for (int j = 0; j < n_kt && ok; ++j) {
+            if (lane == 0) ok = mbar_wait(&s_full[g], j & 1, abort_flag, err);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int kbase = j * AT_N;
             const bool edge = kbase + AT_N - 1 > p0;     // the tile touches the diagonal or the sequence's end
-            unsigned sv[128];
-            AT_LD32((sv + 0), tmem_s + lane_addr + 0);
-            AT_LD32((sv + 32), tmem_s + lane_addr + 32);
-            AT_LD32((sv + 64), tmem_s + lane_addr + 64);
-            AT_LD32((sv + 96), tmem_s + lane_addr + 96);
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-            if (edge) {
-#pragma unroll
-                for (int i = 0; i < 128; ++i)
-                    if (kbase + i > qpos) sv[i] = 0xff800000u;      // -inf: not visible
-            }
+            // pass 1: the row's maximum, 64 columns at a time
             float tmax = -INFINITY, tmax2 = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < 128; i += 4) {
-                tmax = at_max3(tmax, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
-                tmax2 = at_max3(tmax2, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+            for (int c0 = 0; c0 < AT_N; c0 += 64) {
+                unsigned a[64];
+                AT_LD32((a + 0), tmem_s + lane_addr + c0);
+                AT_LD32((a + 32), tmem_s + lane_addr + c0 + 32);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (edge) {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i)
+                        if (kbase + c0 + i > qpos) a[i] = 0xff800000u;      // -inf: not visible
+                }
+#pragma unroll
+                for (int i = 0; i < 64; i += 4) {
+                    tmax = at_max3(tmax, __uint_as_float(a[i]), __uint_as_float(a[i + 1]));
+                    tmax2 = at_max3(tmax2, __uint_as_float(a[i + 2]), __uint_as_float(a[i + 3]));
+                }
             }
             tmax = fmaxf(tmax, tmax2) * sl2;
             // the row's reference maximum moves only by more than AT_RESCALE_STEP
@@ -294,26 +331,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - tmax);
             }
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            // probabilities exp2(s * sl2 - m) (two to a packed multiply-add), their sum, packed to bf16 in place
-            const unsigned long long sl2_2 = at_pack2(sl2, sl2), negm_2 = at_pack2(-m_use, -m_use);
-            unsigned long long psum2 = 0ull;
-#pragma unroll
-            for (int i = 0; i < 128; i += 2) {
-                unsigned long long x2;
-                asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(x2) : "l"(at_pack2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1]))), "l"(sl2_2), "l"(negm_2));
-                float e0, e1;
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(at_lo(x2)));
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(at_hi(x2)));
-                asm("add.rn.f32x2 %0, %1, %2;" : "=l"(psum2) : "l"(psum2), "l"(at_pack2(e0, e1)));
-                __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
-                sv[i >> 1] = *reinterpret_cast<unsigned*>(&b);
-            }
-            l_run = l_run * corr + (at_lo(psum2) + at_hi(psum2));
             m_run = m_new;
             // rows whose reference maximum moved rescale their row of O (the previous P . V has landed: the
             // scores of this tile were issued after it)
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-                if (lane == 0) ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, err);
+                if (lane == 0) ok = mbar_wait(&o_done[g], (j - 1) & 1, abort_flag, err);
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -326,25 +348,54 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                     for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
                     AT_ST32(ov, tmem_o + lane_addr + c0);
                 }
-                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             }
-            // P into tensor memory over the first 64 columns of this row's scores: two keys to a column
-            AT_ST32((sv + 0), tmem_s + lane_addr + 0);
-            AT_ST32((sv + 32), tmem_s + lane_addr + 32);
+            // pass 2: probabilities exp2(s * sl2 - m), 32 columns at a time (the next 32 are on their way
+            // meanwhile), their sum, packed to bf16 and written over the scores already read: two keys to a
+            // column, so the P of columns [32 c, 32 c + 32) lands on columns [16 c, 16 c + 16)
+            const unsigned long long sl2_2 = at_pack2(sl2, sl2), negm_2 = at_pack2(-m_use, -m_use);
+            unsigned long long psum2 = 0ull;
+            unsigned a[32], b[32];
+            AT_LD32(a, tmem_s + lane_addr);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                unsigned* cur = (c & 1) ? b : a;
+                unsigned* nxt = (c & 1) ? a : b;
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (c < 3) AT_LD32(nxt, tmem_s + lane_addr + (unsigned)(32 * (c + 1)));
+                if (edge) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (kbase + 32 * c + i > qpos) cur[i] = 0xff800000u;
+                }
+                unsigned pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    unsigned long long x2;
+                    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(x2) : "l"(at_pack2(__uint_as_float(cur[i]), __uint_as_float(cur[i + 1]))), "l"(sl2_2), "l"(negm_2));
+                    float e0, e1;
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(at_lo(x2)));
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(at_hi(x2)));
+                    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(psum2) : "l"(psum2), "l"(at_pack2(e0, e1)));
+                    __nv_bfloat162 bb = __floats2bfloat162_rn(e0, e1);
+                    pk[i >> 1] = *reinterpret_cast<unsigned*>(&bb);
+                }
+                AT_ST16(pk, tmem_s + lane_addr + (unsigned)(16 * c));
+            }
+            l_run = l_run * corr + (at_lo(psum2) + at_hi(psum2));
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive_plain(p_ready);
+            if (lane == 0) mbar_arrive_plain(&p_ready[g]);
         }
         // the last P . V, then this row of O divided by the row's sum
-        if (ok) {
-            if (lane == 0) ok = mbar_wait(o_done, (n_kt - 1) & 1, abort_flag, err);
+        if (ok && g < n_heads) {
+            if (lane == 0) ok = mbar_wait(&o_done[g], (n_kt - 1) & 1, abort_flag, err);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         }
-        if (ok) {
+        if (ok && g < n_heads) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-            bf16* dst = out + ((size_t)(t0 + row) * H + h) * AT_D;
+            bf16* dst = out + ((size_t)(t0 + row) * H + h0 + g) * AT_D;
 #pragma unroll
             for (int c0 = 0; c0 < AT_D; c0 += 32) {
                 unsigned ov[32];
@@ -370,20 +421,22 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     if (*abort_flag && tid == 0) {      // give copies in flight a bounded time to land
-        for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(k_full, 0) && !mbar_try_wait(k_full, 1); ++i) {}
-        for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(v_full, 0) && !mbar_try_wait(v_full, 1); ++i) {}
+        for (int s = 0; s < 2; ++s) {
+            for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(&k_full[s], 0) && !mbar_try_wait(&k_full[s], 1); ++i) {}
+            for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(&v_full[s], 0) && !mbar_try_wait(&v_full[s], 1); ++i) {}
+        }
     }
     __syncthreads();
     if (warp == 1) {
         __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(256));
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512));
     }
 }
 
 // q, out: [T, H, 128] bf16; k_pages, v_pages: [num_pages, K, P, 128] bf16 of one layer;
 // tiles: [n_tiles][2] = (request row, offset of the 128-token tile within the request's tokens).
-// Takes head size 128, page sizes that divide 128 and layers without a window; refuses the rest
+// Takes head size 128, pages of 8 .. 128 keys that divide 128 and layers without a window; refuses the rest
 // (AIE_UNSUPPORTED): they take the mma.sync kernel.
 extern "C" int aie_paged_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out,
                                               const int* tiles, int n_tiles, const int* q_start, const int* q_len,
@@ -392,18 +445,18 @@ extern "C" int aie_paged_attention_prefill_tc(const void* q, const void* k_pages
                                               float scale, unsigned* err, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (K <= 0 || H % K) return AIE_BAD_ARG;
-    if (d != AT_D || P <= 0 || P > 128 || 128 % P || H > 65535 || window > 0) return AIE_UNSUPPORTED;
+    if (d != AT_D || P < 8 || P > 128 || 128 % P || H > 65535 || window > 0) return AIE_UNSUPPORTED;
     if (((size_t)q & 15) || ((size_t)k_pages & 15) || ((size_t)v_pages & 15)) return AIE_UNSUPPORTED;
     CUtensorMap mq, mk, mv;
     int rc = tc_make_map_2d(&mq, q, (unsigned long long)T, (unsigned long long)H * d, (unsigned long long)H * d * 2, AT_M, 64);
     if (rc) return rc;
     const unsigned long long rows = (unsigned long long)num_pages * K * P;
-    rc = tc_make_map_2d(&mk, k_pages, rows, d, (unsigned long long)d * 2, P, 64);
+    rc = tc_make_map_rows8(&mk, k_pages, rows, P / 8);
     if (rc) return rc;
-    rc = tc_make_map_2d(&mv, v_pages, rows, d, (unsigned long long)d * 2, P, 64);
+    rc = tc_make_map_rows8(&mv, v_pages, rows, P / 8);
     if (rc) return rc;
     cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AtSmem::bytes);
-    paged_prefill_tc_kernel<<<dim3(n_tiles, H), AT_THREADS, AtSmem::bytes, stream>>>(
+    paged_prefill_tc_kernel<<<dim3(n_tiles, K * ((H / K + 1) / 2)), AT_THREADS, AtSmem::bytes, stream>>>(
         mq, mk, mv, (bf16*)out, tiles, n_tiles, q_start, q_len, ctx_len, block_table, bt_width, num_pages, P, H, K,
         scale, err);
     AIE_LAUNCH_CHECK();

@@ -41,13 +41,19 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
                  ::"r"(tc_smem(dst)), "l"(map), "r"(tc_smem(bar)), "r"(x), "r"(y) : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, unsigned long long* bar, int c0, int c1,
+                                            int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n"
+                 ::"r"(tc_smem(dst)), "l"(map), "r"(tc_smem(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
 // K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle, groups of
 // 8 rows 1024 bytes apart (what the TMA load with SWIZZLE_128B writes).
-__device__ __forceinline__ unsigned long long umma_desc(const void* tile) {
+__device__ __forceinline__ unsigned long long umma_desc(const void* tile, unsigned group_stride_bytes = 1024) {
     unsigned long long d = 0;
     d |= (unsigned long long)((tc_smem(tile) >> 4) & 0x3FFFu);   // start address / 16
     d |= (unsigned long long)1 << 16;                             // leading byte offset / 16 (unused under swizzle)
-    d |= (unsigned long long)(1024 >> 4) << 32;                   // stride byte offset / 16: next group of 8 rows
+    d |= (unsigned long long)(group_stride_bytes >> 4) << 32;     // stride byte offset / 16: next group of 8 rows
     d |= (unsigned long long)1 << 46;                             // descriptor version of sm_100
     d |= (unsigned long long)2 << 61;                             // SWIZZLE_128B
     return d;
@@ -94,6 +100,22 @@ static inline TcEncodeTiledFn tc_encode_fn() {
             fn = (TcEncodeTiledFn)p;
     }
     return fn;
+}
+
+// bf16 matrix [rows, 128] (rows 256 bytes apart, rows a multiple of 8) seen as [groups of 8 rows][2 halves of
+// 64 columns][8 rows][64]: a box of `box_groups` groups lands in shared memory as, per group, the 8 rows of
+// the first 64 columns (1 KB, 128-byte swizzled) and then the 8 rows of the other 64 columns
+static inline int tc_make_map_rows8(CUtensorMap* map, const void* ptr, unsigned long long rows, int box_groups) {
+    TcEncodeTiledFn fn = tc_encode_fn();
+    if (!fn) return AIE_UNSUPPORTED;
+    cuuint64_t dims[4] = {64, 8, 2, (cuuint64_t)(rows / 8)};
+    cuuint64_t strides[3] = {256, 128, 2048};
+    cuuint32_t box[4] = {64, 8, 2, (cuuint32_t)box_groups};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : AIE_UNSUPPORTED;
 }
 
 // bf16 matrix [rows, cols] with rows `row_stride_bytes` apart, tiles of [box_rows, box_cols]

@@ -255,7 +255,7 @@ PREFILL_TC_SHAPES = [  # H, K, P, lens, q_lens  (head size 128, no window)
     (4, 2, 16, [5, 40], [5, 7]),
     (32, 8, 16, [300, 130, 64], [300, 2, 64]),
     (6, 2, 8, [257, 65], [129, 65]),           # a portion that starts mid-page and mid-tile
-    (5, 1, 4, [700], [63]),
+    (5, 1, 8, [700], [63]),
     (2, 2, 32, [1100], [1100]),
     (3, 3, 16, [200], [2]),
     (4, 1, 64, [191, 192, 193], [191, 128, 2]),
@@ -285,6 +285,32 @@ def test_paged_attention_prefill_tcgen05(shape):
     assert err.max() <= 2e-2, f"first wrong token {int((err > 2e-2).nonzero()[0])} of {sum(q_lens)}: {float(err.max())}"
 
 
+def test_prefill_tcgen05_scores_that_grow_along_the_sequence():
+    """Keys whose size grows from tile to tile (scores up to tens of units above everything before) and
+    then falls again: rows whose reference maximum has to move, and rows where it may stay."""
+    H, K, d, P = 6, 2, 128, 16
+    n = 900
+    s = paged_setup(torch.bfloat16, H, K, d, P, [n], [n], seed=21)
+    gain = torch.ones(n, device=DEV)
+    gain[130:260], gain[260:520], gain[520:700] = 2.0, 6.0, 0.3
+    for pos in range(n):
+        s["ks"][0][pos] = (s["ks"][0][pos].float() * gain[pos]).bfloat16()
+        pg, sl = int(s["bt"][0, pos // P]), pos % P
+        s["k_pages"][pg, :, sl] = s["ks"][0][pos]
+    scale = 1.0 / math.sqrt(d)
+    e = err_word()
+    out = torch.full_like(s["q"], float("nan"))
+    i32 = lambda a: torch.tensor(a, device=DEV, dtype=torch.int32)
+    tiles = [(0, o) for o in range(0, n, 128)]
+    assert ops().paged_attention_prefill_tc(s["q"], s["k_pages"], s["v_pages"], i32(tiles), i32([0]), i32([n]),
+                                            i32([0]), s["bt"], scale, 0, e, out)
+    torch.cuda.synchronize()
+    assert int(e.item()) == 0
+    want = attention_reference(s, H, K, d, scale, 0)
+    err = (out.double() - want).abs().amax(dim=(1, 2))
+    assert err.max() <= 2e-2, f"first wrong token {int((err > 2e-2).nonzero()[0])} of {n}: {float(err.max())}"
+
+
 def test_prefill_tcgen05_refuses_what_it_does_not_take():
     s = paged_setup(torch.bfloat16, 4, 2, 64, 16, [40], [40], seed=1)
     i32 = lambda a: torch.tensor(a, device=DEV, dtype=torch.int32)
@@ -294,6 +320,9 @@ def test_prefill_tcgen05_refuses_what_it_does_not_take():
     s = paged_setup(torch.bfloat16, 4, 2, 128, 16, [40], [40], seed=1)
     args = (s["q"], s["k_pages"], s["v_pages"], i32([[0, 0]]), i32([0]), i32([40]), i32([0]), s["bt"], 0.09)
     assert not ops().paged_attention_prefill_tc(*args, 7, err_word(), torch.zeros_like(s["q"]))   # a window
+    s = paged_setup(torch.bfloat16, 4, 2, 128, 4, [40], [40], seed=1)
+    args = (s["q"], s["k_pages"], s["v_pages"], i32([[0, 0]]), i32([0]), i32([40]), i32([0]), s["bt"], 0.09)
+    assert not ops().paged_attention_prefill_tc(*args, 0, err_word(), torch.zeros_like(s["q"]))   # pages of 4 keys
 
 
 def test_mixed_step_decode_and_prefill_kernels_side_by_side():

@@ -2,24 +2,24 @@
 // (head size 128): scores and outputs live in tensor memory, operands come from shared memory
 // filled by TMA, softmax is float32 in registers.
 //
-// One CTA owns 128 query tokens of TWO heads of one group (heads that read the same kv head: they share
-// every key and value tile); a group with an odd number of heads leaves the second place of its last CTA
-// empty.  While the softmax of one head runs, the tensor pipe works on the other.  For each tile of 128 keys:
+// One CTA owns 128 query tokens of one head.  For each tile of 128 keys:
 //   warp 0             loads the key tile and the value tile page by page with TMA: one box per page,
 //                      lane i issuing the box of the tile's page i (the pool of a layer is seen as
 //                      [groups of 8 rows][2 halves of the head][8 rows][64], so a box lands as 1 KB
 //                      128-byte-swizzled atoms, the two halves of a group side by side), a ring of
 //                      two buffers for keys and one of two for values; the loop has no division and
 //                      reads the next tile's page id while this tile's boxes are issued;
-//   warp 1 (one lane)  issues, head by head, O += P . V of this tile (8 x tcgen05.mma; P is read from
-//                      tensor memory, where the softmax wrote it over the scores; V is the MN-major
-//                      operand: its rows are keys) and then S = Q . K^T of the next tile (8 x
-//                      tcgen05.mma of K = 16), and commits to the mbarriers the others wait on;
-//   warps 2-5, 6-9     softmax of the first and of the second head, one thread per query row: read the
-//                      row of S (tcgen05.ld, 128 registers), mask on tiles that touch the diagonal or
-//                      the sequence's end, take the row's maximum and running sum (float32; the
-//                      scale-and-subtract and the sum as packed f32x2 instructions), write P as bf16
-//                      pairs into tensor memory.  The reference
+//   warp 1 (one lane)  issues S = Q . K^T (8 x tcgen05.mma of K = 16) into one of two score buffers in
+//                      tensor memory — the scores of the next tile are computed while the softmax of
+//                      this one runs, so the softmax warps never wait for a round trip — later
+//                      O += P . V (8 x tcgen05.mma; P is read from tensor memory, where the softmax
+//                      wrote it over the scores; V is the MN-major operand: its rows are keys), and
+//                      commits to the mbarriers the others wait on;
+//   warps 2-5          softmax, one thread per query row, in two passes over the row of S (tcgen05.ld):
+//                      the maximum, masked on tiles that touch the diagonal or the sequence's end; then
+//                      the probabilities and their running sum (float32; the scale-and-subtract and
+//                      the sum as packed f32x2 instructions), written as bf16 pairs into tensor
+//                      memory.  The reference
 //                      maximum of a row moves only when the new maximum exceeds it by more than 8
 //                      (in units of log2 e): P stays below 2^8 and the row of O in tensor memory is
 //                      rescaled on few tiles; the final division by the running sum makes the
@@ -33,14 +33,14 @@
 #define AT_M 128          // query rows per CTA
 #define AT_N 128          // keys per tile
 #define AT_D 128          // head size
-#define AT_THREADS 320      // loader warp, MMA warp, 4 softmax warps for each of the two heads
+#define AT_THREADS 192      // loader warp, MMA warp, 4 softmax warps
 #define AT_HALF_BYTES (128 * 64 * 2)      // one [128 x 64] bf16 swizzle atom column: 16 KB
 
 #define AT_RESCALE_STEP 8.0f     // a row's reference maximum moves in steps of more than this (log2 units)
 
 struct AtSmem {
-    // [alignment slack | 1 KB: barriers | Q 2 heads x 32 KB | K 2 x 32 KB | V 2 x 32 KB]
-    static constexpr int q_off = 1024, k_off = q_off + 4 * AT_HALF_BYTES, v_off = k_off + 4 * AT_HALF_BYTES,
+    // [alignment slack | 1 KB: barriers | Q 32 KB | K 2 x 32 KB | V 2 x 32 KB]
+    static constexpr int q_off = 1024, k_off = q_off + 2 * AT_HALF_BYTES, v_off = k_off + 4 * AT_HALF_BYTES,
                          end = v_off + 4 * AT_HALF_BYTES;
     static constexpr int bytes = 1024 + end;
 };
@@ -114,22 +114,20 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     unsigned long long* k_empty = k_full + 2;      // [2]
     unsigned long long* v_full = k_empty + 2;      // [2]
     unsigned long long* v_empty = v_full + 2;      // [2]
-    unsigned long long* s_full = v_empty + 2;      // [2] heads
-    unsigned long long* p_ready = s_full + 2;      // [2] heads
-    unsigned long long* o_done = p_ready + 2;      // [2] heads
-    unsigned long long* v_fixed = o_done + 2;
+    unsigned long long* s_full = v_empty + 2;      // [2] score buffers
+    unsigned long long* p_ready = s_full + 2;
+    unsigned long long* o_done = p_ready + 1;
+    unsigned long long* v_fixed = o_done + 1;
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(v_fixed + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    unsigned char* q_s = sm + AtSmem::q_off;       // head g at + g * 2 * AT_HALF_BYTES
+    unsigned char* q_s = sm + AtSmem::q_off;
     unsigned char* k_s = sm + AtSmem::k_off;       // stage st at + st * 2 * AT_HALF_BYTES
     unsigned char* v_s = sm + AtSmem::v_off;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile_i = n_tiles - 1 - (int)blockIdx.x;      // later tiles hold more keys: start them first
     const int r = tiles[2 * tile_i], q_off = tiles[2 * tile_i + 1];
-    const int G = H / K, pairs = (G + 1) / 2;
-    const int kvh = blockIdx.y / pairs, h0 = kvh * G + 2 * ((int)blockIdx.y % pairs);
-    const int n_heads = (h0 + 1 < (kvh + 1) * G) ? 2 : 1;      // heads of this CTA: h0 and, if the group has it, h0 + 1
+    const int h = blockIdx.y, kvh = h / (H / K);
     const int t0 = q_start[r] + q_off;
     const int rows_valid = min(AT_M, q_len[r] - q_off);
     const int p0 = ctx_len[r] + q_off;                 // position of the tile's first query
@@ -145,16 +143,16 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             mbar_init(&v_full[s], 1);
             mbar_init(&v_empty[s], 1);
             mbar_init(&s_full[s], 1);
-            mbar_init(&p_ready[s], 4);      // one arrival per softmax warp of the head
-            mbar_init(&o_done[s], 1);
         }
+        mbar_init(p_ready, 4);      // one arrival per softmax warp
+        mbar_init(o_done, 1);
         mbar_init(v_fixed, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
-    if (warp == 1) {    // tensor memory: scores of head g at columns [128 g, 128 g + 128) (P over the first 64),
-                        // outputs of head g at [256 + 128 g, 256 + 128 g + 128)
+    if (warp == 1) {    // tensor memory: score buffer b at columns [128 b, 128 b + 128) (P over its first 64),
+                        // outputs at [256, 384)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(tmem_slot)), "r"(512));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
@@ -165,12 +163,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
     if (warp == 0) {
             if (lane == 0) {
-            // queries of this tile: rows t0 .. t0 + 127 of q [T, H * 128], columns of heads h0 (and h0 + 1)
-            mbar_expect_tx(q_full, (unsigned)n_heads * 2u * AT_HALF_BYTES);
-            for (int g = 0; g < n_heads; ++g) {
-                tma_load_2d(q_s + (2 * g) * AT_HALF_BYTES, &map_q, q_full, (h0 + g) * AT_D, t0);
-                tma_load_2d(q_s + (2 * g + 1) * AT_HALF_BYTES, &map_q, q_full, (h0 + g) * AT_D + 64, t0);
-            }
+            // queries of this tile: rows t0 .. t0 + 127 of q [T, H * 128], columns of head h
+            mbar_expect_tx(q_full, 2 * AT_HALF_BYTES);
+            tma_load_2d(q_s, &map_q, q_full, h * AT_D, t0);
+            tma_load_2d(q_s + AT_HALF_BYTES, &map_q, q_full, h * AT_D + 64, t0);
         }
         // lane i owns page i of every key tile: one box per page (all 128 columns of its P keys); the id of
         // the next tile's page is read while this tile's boxes are issued
@@ -233,72 +229,66 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     } else if (warp == 1) {
         if (lane == 0) {
             const unsigned idesc_s = umma_idesc(AT_N), idesc_o = umma_idesc(AT_D, true);
-            // S of head g = Q_g . K^T over d = 128: 8 steps of 16, keys from stage st
-            auto issue_scores = [&](int g, int st) {
-                unsigned char* qd = q_s + g * 2 * AT_HALF_BYTES;
-                unsigned char* kd = k_s + st * 2 * AT_HALF_BYTES;
+            // S(j) = Q . K(j)^T over d = 128 into score buffer j & 1: 8 steps of 16
+            auto issue_scores = [&](int j) {
+                unsigned char* kd = k_s + (j & 1) * 2 * AT_HALF_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
-                    const unsigned long long da = umma_desc(qd + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
+                    const unsigned long long da = umma_desc(q_s + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
                     const unsigned long long db = umma_desc(kd + (ks >> 2) * 1024, 2048) + 2 * (ks & 3);
-                    umma(tmem_base + (unsigned)(g * AT_N), da, db, idesc_s, ks > 0 ? 1u : 0u);
+                    umma(tmem_base + (unsigned)((j & 1) * AT_N), da, db, idesc_s, ks > 0 ? 1u : 0u);
                 }
-                umma_commit(&s_full[g]);
-                if (g == n_heads - 1) umma_commit(&k_empty[st]);
+                umma_commit(&k_empty[j & 1]);
+                umma_commit(&s_full[j & 1]);
             };
             bool ok = mbar_wait(q_full, 0, abort_flag, err);
             if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag, err);
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                for (int g = 0; g < n_heads; ++g) issue_scores(g, 0);
+                issue_scores(0);
             }
             for (int j = 0; j < n_kt && ok; ++j) {
                 const int st = j & 1;
-                for (int g = 0; g < n_heads && ok; ++g) {
-                    ok = mbar_wait(&p_ready[g], j & 1, abort_flag, err);
-                    if (ok && g == 0) {
-                        ok = mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, err);
-                        if (ok && j == n_kt - 1) ok = mbar_wait(v_fixed, 0, abort_flag, err);
-                    }
+                if (j + 1 < n_kt) {
+                    // the next tile's scores, while this tile's softmax runs.  They go over the P of tile
+                    // j - 1, which the P . V issued before them has read: the tensor pipe runs what one thread
+                    // issues in order.
+                    ok = mbar_wait(&k_full[st ^ 1], ((j + 1) >> 1) & 1, abort_flag, err);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    // O_g += P_g . V over 128 keys: 8 steps of 16 keys; P is in tensor memory (two keys to a
-                    // column), V is MN-major: 16 keys = two groups of 8 rows, the two d-halves AT_HALF_BYTES apart
-                    unsigned char* vd = v_s + st * 2 * AT_HALF_BYTES;
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
-                        const unsigned long long db = umma_desc_mn(vd + ks * 2 * 2048, 1024);
-                        umma_a_tmem(tmem_base + (unsigned)(256 + g * AT_D), tmem_base + (unsigned)(g * AT_N + ks * 8), db,
-                                    idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-                    }
-                    umma_commit(&o_done[g]);
-                    if (g == n_heads - 1) umma_commit(&v_empty[st]);
-                    // the head's scores of the next tile, over the P just read (the tensor pipe runs what one
-                    // thread issues in order); the other head's softmax runs meanwhile
-                    if (j + 1 < n_kt) {
-                        if (g == 0) {
-                            ok = mbar_wait(&k_full[st ^ 1], ((j + 1) >> 1) & 1, abort_flag, err);
-                            if (!ok) break;
-                            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                        }
-                        issue_scores(g, st ^ 1);
-                    }
+                    issue_scores(j + 1);
                 }
+                ok = mbar_wait(p_ready, j & 1, abort_flag, err);
+                if (ok) ok = mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, err);
+                if (ok && j == n_kt - 1) ok = mbar_wait(v_fixed, 0, abort_flag, err);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                // O += P . V over 128 keys: 8 steps of 16 keys; P is in tensor memory (two keys to a column),
+                // V is MN-major: 16 keys = two groups of 8 rows, the two d-halves 1 KB apart
+                unsigned char* vd = v_s + st * 2 * AT_HALF_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const unsigned long long db = umma_desc_mn(vd + ks * 2 * 2048, 1024);
+                    umma_a_tmem(tmem_base + 256u, tmem_base + (unsigned)(st * AT_N + ks * 8), db, idesc_o,
+                                (j > 0 || ks > 0) ? 1u : 0u);
+                }
+                umma_commit(&v_empty[st]);
+                umma_commit(o_done);
             }
         }
     } else {
-        // softmax of head g: one thread per query row (warp w reads lanes 32 * (w % 4) .. + 31 of tensor memory)
-        const int g = (warp - 2) >> 2;
+        // softmax: one thread per query row (warp w reads lanes 32 * (w % 4) .. + 31 of tensor memory)
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const int qpos = p0 + row;
         const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
-        const unsigned tmem_s = tmem_base + (unsigned)(g * AT_N), tmem_o = tmem_base + (unsigned)(256 + g * AT_D);
+        const unsigned tmem_o = tmem_base + 256u;
         const float sl2 = scale * 1.4426950408889634f;      // scores in units of log2(e): exp2 below
         float m_run = -INFINITY, l_run = 0.f;
-        bool ok = g < n_heads;
+        bool ok = true;
         for (int j = 0; j < n_kt && ok; ++j) {
-            if (lane == 0) ok = mbar_wait(&s_full[g], j & 1, abort_flag, err);
+            const unsigned tmem_s = tmem_base + (unsigned)((j & 1) * AT_N);
+            if (lane == 0) ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, err);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -332,10 +322,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             }
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
             m_run = m_new;
-            // rows whose reference maximum moved rescale their row of O (the previous P . V has landed: the
-            // scores of this tile were issued after it)
+            // rows whose reference maximum moved rescale their row of O once the previous P . V has landed
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-                if (lane == 0) ok = mbar_wait(&o_done[g], (j - 1) & 1, abort_flag, err);
+                if (lane == 0) ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, err);
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -385,17 +374,17 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive_plain(&p_ready[g]);
+            if (lane == 0) mbar_arrive_plain(p_ready);
         }
         // the last P . V, then this row of O divided by the row's sum
-        if (ok && g < n_heads) {
-            if (lane == 0) ok = mbar_wait(&o_done[g], (n_kt - 1) & 1, abort_flag, err);
+        if (ok) {
+            if (lane == 0) ok = mbar_wait(o_done, (n_kt - 1) & 1, abort_flag, err);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         }
-        if (ok && g < n_heads) {
+        if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-            bf16* dst = out + ((size_t)(t0 + row) * H + h0 + g) * AT_D;
+            bf16* dst = out + ((size_t)(t0 + row) * H + h) * AT_D;
 #pragma unroll
             for (int c0 = 0; c0 < AT_D; c0 += 32) {
                 unsigned ov[32];
@@ -456,7 +445,7 @@ extern "C" int aie_paged_attention_prefill_tc(const void* q, const void* k_pages
     rc = tc_make_map_rows8(&mv, v_pages, rows, P / 8);
     if (rc) return rc;
     cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AtSmem::bytes);
-    paged_prefill_tc_kernel<<<dim3(n_tiles, K * ((H / K + 1) / 2)), AT_THREADS, AtSmem::bytes, stream>>>(
+    paged_prefill_tc_kernel<<<dim3(n_tiles, H), AT_THREADS, AtSmem::bytes, stream>>>(
         mq, mk, mv, (bf16*)out, tiles, n_tiles, q_start, q_len, ctx_len, block_table, bt_width, num_pages, P, H, K,
         scale, err);
     AIE_LAUNCH_CHECK();

@@ -15,8 +15,8 @@
 //                      O += P . V (8 x tcgen05.mma; P is read from tensor memory, where the softmax
 //                      wrote it over the scores; V is the MN-major operand: its rows are keys), and
 //                      commits to the mbarriers the others wait on;
-//   warps 2-5          softmax, one thread per query row, in two passes over the row of S (tcgen05.ld):
-//                      the maximum, masked on tiles that touch the diagonal or the sequence's end; then
+//   warps 2-5          softmax, one thread per query row: the row of S in registers (tcgen05.ld), masked
+//                      on tiles that touch the diagonal or the sequence's end, its maximum; then
 //                      the probabilities and their running sum (float32; the scale-and-subtract and
 //                      the sum as packed f32x2 instructions), written as bf16 pairs into tensor
 //                      memory.  The reference
@@ -294,24 +294,23 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int kbase = j * AT_N;
             const bool edge = kbase + AT_N - 1 > p0;     // the tile touches the diagonal or the sequence's end
-            // pass 1: the row's maximum, 64 columns at a time
+            // the row of scores in registers (all four loads in flight at once), masked; its maximum
+            unsigned sv[128];
+            AT_LD32((sv + 0), tmem_s + lane_addr + 0);
+            AT_LD32((sv + 32), tmem_s + lane_addr + 32);
+            AT_LD32((sv + 64), tmem_s + lane_addr + 64);
+            AT_LD32((sv + 96), tmem_s + lane_addr + 96);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            if (edge) {
+#pragma unroll
+                for (int i = 0; i < 128; ++i)
+                    if (kbase + i > qpos) sv[i] = 0xff800000u;      // -inf: not visible
+            }
             float tmax = -INFINITY, tmax2 = -INFINITY;
 #pragma unroll
-            for (int c0 = 0; c0 < AT_N; c0 += 64) {
-                unsigned a[64];
-                AT_LD32((a + 0), tmem_s + lane_addr + c0);
-                AT_LD32((a + 32), tmem_s + lane_addr + c0 + 32);
-                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-                if (edge) {
-#pragma unroll
-                    for (int i = 0; i < 64; ++i)
-                        if (kbase + c0 + i > qpos) a[i] = 0xff800000u;      // -inf: not visible
-                }
-#pragma unroll
-                for (int i = 0; i < 64; i += 4) {
-                    tmax = at_max3(tmax, __uint_as_float(a[i]), __uint_as_float(a[i + 1]));
-                    tmax2 = at_max3(tmax2, __uint_as_float(a[i + 2]), __uint_as_float(a[i + 3]));
-                }
+            for (int i = 0; i < 128; i += 4) {
+                tmax = at_max3(tmax, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+                tmax2 = at_max3(tmax2, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
             }
             tmax = fmaxf(tmax, tmax2) * sl2;
             // the row's reference maximum moves only by more than AT_RESCALE_STEP
@@ -338,38 +337,28 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                     AT_ST32(ov, tmem_o + lane_addr + c0);
                 }
             }
-            // pass 2: probabilities exp2(s * sl2 - m), 32 columns at a time (the next 32 are on their way
-            // meanwhile), their sum, packed to bf16 and written over the scores already read: two keys to a
-            // column, so the P of columns [32 c, 32 c + 32) lands on columns [16 c, 16 c + 16)
+            // probabilities exp2(s * sl2 - m), their sum, packed to bf16 and written over the scores, 32 columns
+            // at a time: two keys to a column, so the P of columns [32 c, 32 c + 32) lands on [16 c, 16 c + 16)
             const unsigned long long sl2_2 = at_pack2(sl2, sl2), negm_2 = at_pack2(-m_use, -m_use);
-            unsigned long long psum2 = 0ull;
-            unsigned a[32], b[32];
-            AT_LD32(a, tmem_s + lane_addr);
+            unsigned long long psum2 = 0ull, psum2b = 0ull;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                unsigned* cur = (c & 1) ? b : a;
-                unsigned* nxt = (c & 1) ? a : b;
-                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-                if (c < 3) AT_LD32(nxt, tmem_s + lane_addr + (unsigned)(32 * (c + 1)));
-                if (edge) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (kbase + 32 * c + i > qpos) cur[i] = 0xff800000u;
-                }
                 unsigned pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     unsigned long long x2;
-                    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(x2) : "l"(at_pack2(__uint_as_float(cur[i]), __uint_as_float(cur[i + 1]))), "l"(sl2_2), "l"(negm_2));
+                    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(x2) : "l"(at_pack2(__uint_as_float(sv[32 * c + i]), __uint_as_float(sv[32 * c + i + 1]))), "l"(sl2_2), "l"(negm_2));
                     float e0, e1;
                     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(at_lo(x2)));
                     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(at_hi(x2)));
-                    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(psum2) : "l"(psum2), "l"(at_pack2(e0, e1)));
+                    if (i & 2) asm("add.rn.f32x2 %0, %1, %2;" : "=l"(psum2b) : "l"(psum2b), "l"(at_pack2(e0, e1)));
+                    else asm("add.rn.f32x2 %0, %1, %2;" : "=l"(psum2) : "l"(psum2), "l"(at_pack2(e0, e1)));
                     __nv_bfloat162 bb = __floats2bfloat162_rn(e0, e1);
                     pk[i >> 1] = *reinterpret_cast<unsigned*>(&bb);
                 }
                 AT_ST16(pk, tmem_s + lane_addr + (unsigned)(16 * c));
             }
+            asm("add.rn.f32x2 %0, %1, %2;" : "=l"(psum2) : "l"(psum2), "l"(psum2b));
             l_run = l_run * corr + (at_lo(psum2) + at_hi(psum2));
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");

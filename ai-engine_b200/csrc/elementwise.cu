@@ -58,6 +58,29 @@ extern "C" int aie_embed_gather(const int* ids, const void* table, int table_dty
     AIE_LAUNCH_CHECK();
 }
 
+// ids[t] = last[src[t]] where src[t] >= 0: a token that the previous step sampled and that the host
+// has not read yet is taken from the device buffer the sampler left it in (no counterpart in the
+// reference, whose loop reads every token back before the next step: crates/ai-engine-candle/src/paged/engine.rs:150-170)
+__global__ void take_sampled_ids_kernel(int* __restrict__ ids, const int* __restrict__ src,
+                                        const int* __restrict__ last, int T, int n_last, unsigned* err) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    const int k = src[t];
+    if (k < 0) return;
+    if (k >= n_last) {
+        atomicOr(err, AIE_DEV_TOKEN_OOB);
+        return;
+    }
+    ids[t] = last[k];
+}
+
+extern "C" int aie_take_sampled_ids(int* ids, const int* src, const int* last, int T, int n_last, unsigned* err,
+                                    cudaStream_t stream) {
+    if (T <= 0) return 0;
+    take_sampled_ids_kernel<<<(T + 127) / 128, 128, 0, stream>>>(ids, src, last, T, n_last, err);
+    AIE_LAUNCH_CHECK();
+}
+
 // ---------------------------------------------------------------------------
 // Residual add + RMSNorm (crates/ai-engine-runtime/src/arch/rmsnorm.rs:29-42):
 //   s = x[row] (+ delta[row], or the sum of `parts` deltas `part_stride` elements apart);  ms = mean(s^2);  r = 1/sqrt(ms + eps);

@@ -4,15 +4,20 @@ Option names and defaults are the reference's provider keys where it has them
 (crates/ai-engine-config/src/lib.rs:97-140; defaults crates/ai-engine/src/app.rs:692-703):
 weights_path, device, max_num_seqs = 32, block_size = 16, kv_cache_blocks = 4096.
 The loop is the reference's run_loop (crates/ai-engine-candle/src/paged/engine.rs:62-180)
-with three changes: prompts are cut into portions under `max_num_batched_tokens`
+with four changes: prompts are cut into portions under `max_num_batched_tokens`
 and batched with decoded tokens; a request that cannot get pages is preempted and
 recomputed later instead of failed; the engine is stepped by its caller rather
-than by a thread of its own.
+than by a thread of its own; and the host runs one step ahead of the device
+(`async_scheduling`): step n + 1 is planned and launched while step n runs, its
+decoded tokens taken from the ids that step n's sampler left on the device, and
+step n's tokens are read (one pinned copy, one event) only then.  An EOS is
+therefore seen one step late: the token computed past it is dropped.
 """
 from __future__ import annotations
 
+from collections import deque
 from dataclasses import dataclass, field, fields
-from typing import Dict, List, Optional, Sequence, Tuple, Union
+from typing import Deque, Dict, List, Optional, Sequence, Tuple, Union
 
 import torch
 
@@ -38,6 +43,7 @@ class EngineOptions:
     random_weights: bool = False            # draw weights from `seed` instead of reading a folder
     seed: int = 0
     norm_weight_std: float = 0.0
+    async_scheduling: bool = True           # launch step n + 1 before reading step n's tokens
 
     @classmethod
     def from_dict(cls, d: dict) -> "EngineOptions":
@@ -69,6 +75,16 @@ class _Request:
     output: List[int] = field(default_factory=list)
     finished: bool = False
     reason: str = ""
+    pending: Optional[int] = None   # its last token is still on the device: row of the last step's sampled ids
+    pending_in: object = None       # ... and the record of the step that sampled it
+
+
+@dataclass
+class _InFlight:
+    """A launched step whose sampled ids have not been read yet."""
+    items: list                     # (request, place of the token in request.tokens, finished by length)
+    ids_host: Optional[torch.Tensor]        # pinned: n sampled ids, then the device error word
+    event: Optional[torch.cuda.Event]
 
 
 class Engine:
@@ -109,7 +125,9 @@ class Engine:
         self.eos_ids = set(spec.eos_token_ids)
         self.requests: Dict[int, _Request] = {}
         self._next_id = 0
-        self._since_check = 0
+        self._inflight: Deque[_InFlight] = deque()
+        self._pinned = [torch.zeros(opts.max_num_seqs + 1, dtype=torch.int32).pin_memory() for _ in range(3)]
+        self._turn = 0
         self.counters = dict(steps=0, h2d_bytes=0, d2h_bytes=0, batch_tokens=0, batch_requests=0)
 
     # -- requests ------------------------------------------------------------------
@@ -136,54 +154,101 @@ class Engine:
     # -- one scheduler iteration ------------------------------------------------------
     def step(self) -> List[Tuple[int, Optional[int], bool]]:
         """Schedule, run one batch, sample.  Returns (request id, token or None, finished)
-        for every request that got a token (or ended) in this step.  An EOS token ends
-        its request and is not returned (crates/ai-engine-candle/src/paged/engine.rs:165-170)."""
+        for every request whose token was read (or that ended) during this call: with
+        `async_scheduling` these are the tokens of the step before the one launched here.  An EOS
+        token ends its request and is not returned (crates/ai-engine-candle/src/paged/engine.rs:165-170)."""
+        events: List[Tuple[int, Optional[int], bool]] = []
         plan = self.scheduler.schedule()
         for rid in plan.admitted:
             self.cache.reset_state(self.scheduler.slot(rid))
         if not plan.entries:
-            return []
-        entries, sampled = [], []
+            self._drain(events)
+            return events
+        # A token that is still on the device can be handed to a lone decoded token of the next step;
+        # anything else that needs it (a request preempted and recomputed) waits for the host to read it.
         for e in plan.entries:
             req = self.requests[e.id]
+            if req.pending is not None and e.start + e.n_tokens == len(req.tokens) and e.n_tokens != 1:
+                self._drain(events)
+                break
+        entries, sampled = [], []
+        for e in plan.entries:
+            req = self.requests.get(e.id)
+            if req is None or req.finished:       # ended by an EOS that was read just now: its entry is dropped
+                continue
             toks = req.tokens[e.start:e.start + e.n_tokens]
-            entries.append(StepEntry(e.slot, e.start, toks, [e.n_tokens - 1] if e.sample else []))
+            src = req.pending if (req.pending is not None and e.start + e.n_tokens == len(req.tokens)) else None
+            entries.append(StepEntry(e.slot, e.start, toks, [e.n_tokens - 1] if e.sample else [], src))
             if e.sample:
                 sampled.append(req)
+        if not entries:
+            self.scheduler.commit(plan)
+            return events
         logits = self.runner.step(entries)
         ctx = self.runner.last_ctx
-        events: List[Tuple[int, Optional[int], bool]] = []
-        tokens: List[int] = []
+        rec = _InFlight([], None, None)
         if sampled:
+            n = len(sampled)
             ids = self.sampler.sample(logits, [r.params for r in sampled],
                                       [len(r.tokens) - r.prompt_len for r in sampled])
-            tokens = ids.cpu().tolist()                 # the step's result: one read
-            self.counters["d2h_bytes"] += len(tokens) * 4
-        # the device error word is read when nothing else is (no tokens), every 16th step, and
-        # whenever a request is about to end
-        self._since_check += 1
-        ending = any(len(r.tokens) - r.prompt_len + 1 >= r.params.max_tokens for r in sampled)
-        if not sampled or ending or self._since_check >= 16:
-            self.runner.check_errors()
-            self._since_check = 0
-            self.counters["d2h_bytes"] += 4
+            self.runner.publish_sampled(ids)
+            host = self._pinned[self._turn]
+            self._turn = (self._turn + 1) % len(self._pinned)
+            host[:n].copy_(ids, non_blocking=True)                 # the step's result: one read,
+            host[n:n + 1].copy_(self.runner.err, non_blocking=True)   # and the device error word beside it
+            rec.ids_host = host
+            rec.event = torch.cuda.Event()
+            rec.event.record()
+            self.counters["d2h_bytes"] += (n + 1) * 4
         self.scheduler.commit(plan)
-        for req, tok in zip(sampled, tokens):
-            is_eos = tok in self.eos_ids and not req.params.ignore_eos
-            req.tokens.append(tok)
-            done = self.scheduler.on_token(req.rid, is_eos)
-            if not is_eos:
-                req.output.append(tok)
-            if done:
-                req.finished = True
-                req.reason = "eos" if is_eos else "length"
-            events.append((req.rid, None if is_eos else tok, done))
+        for k, req in enumerate(sampled):
+            req.tokens.append(0)                  # its place; the id is written when the step's result is read
+            req.pending, req.pending_in = k, rec
+            done = self.scheduler.on_token(req.rid, False)
+            rec.items.append((req, len(req.tokens) - 1, done))
+        self._inflight.append(rec)
         c = self.counters
         c["steps"] += 1
         c["h2d_bytes"] += ctx.h2d_bytes + (16 * len(sampled) if sampled else 0)
         c["batch_tokens"] += ctx.T
         c["batch_requests"] += ctx.R
+        ahead = 1 if (self.options.async_scheduling and self.scheduler.has_work()) else 0
+        while len(self._inflight) > ahead:
+            self._resolve(self._inflight.popleft(), events)
         return events
+
+    def _drain(self, events) -> None:
+        while self._inflight:
+            self._resolve(self._inflight.popleft(), events)
+
+    def _resolve(self, rec: _InFlight, events) -> None:
+        """Read a launched step's sampled ids and finish what they finish."""
+        if rec.ids_host is None:
+            return
+        rec.event.synchronize()
+        n = len(rec.items)
+        got = rec.ids_host[:n + 1].tolist()
+        if got[n]:
+            self.runner.check_errors()            # raises with the meaning of the bits
+        for (req, place, done), tok in zip(rec.items, got):
+            if req.pending_in is rec:
+                req.pending, req.pending_in = None, None
+            if req.finished:                      # a token computed past an EOS: dropped
+                continue
+            req.tokens[place] = tok
+            is_eos = tok in self.eos_ids and not req.params.ignore_eos
+            if is_eos:
+                del req.tokens[place + 1:]
+                req.pending, req.pending_in = None, None
+                if not done:
+                    self.scheduler.finish(req.rid)
+                done = True
+            else:
+                req.output.append(tok)
+            if done:
+                req.finished = True
+                req.reason = "eos" if is_eos else "length"
+            events.append((req.rid, None if is_eos else tok, done))
 
     # -- the call a user makes -----------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]],
@@ -194,7 +259,7 @@ class Engine:
         if len(sampling) != len(prompts):
             raise ValueError("one SamplingParams per prompt (or one for all)")
         rids = [self.add_request(p, s) for p, s in zip(prompts, sampling)]
-        while self.scheduler.has_work():
+        while self.scheduler.has_work() or self._inflight:
             self.step()
         self.runner.check_errors()
         return [self.requests.pop(r).output for r in rids]

@@ -28,6 +28,7 @@ class StepEntry:
     start: int                   # tokens of the request already in the cache
     tokens: Sequence[int]        # its next tokens
     want: Sequence[int] = ()     # places among `tokens` whose logits are wanted
+    src: Optional[int] = None    # its one token is still on the device: row of the previous step's sampled ids
 
 
 class StepError(RuntimeError):
@@ -81,7 +82,7 @@ class StepContext:
     in one buffer that is filled on the host and copied once."""
 
     SEGMENTS = ("token_ids", "positions", "token_req", "decode_tokens", "other_tokens",
-                "prefill_tiles", "q_start", "q_len", "ctx_len", "slots", "logit_rows")
+                "prefill_tiles", "q_start", "q_len", "ctx_len", "slots", "logit_rows", "token_src")
 
     def __init__(self, entries: Sequence[StepEntry], cache, device, err: torch.Tensor,
                  buffers: Optional[dict] = None, bucket_width: bool = False):
@@ -105,6 +106,14 @@ class StepContext:
                          + np.repeat(ctx_len, q_len)).astype(np.int32)
         if token_ids.min() < 0 or token_ids.max() > 2**31 - 1:
             raise StepError("token ids must be non-negative 32-bit integers")
+        token_src = np.full(T, -1, dtype=np.int32)
+        self.has_src = False
+        for r, e in enumerate(entries):
+            if e.src is not None:
+                if len(e.tokens) != 1:
+                    raise StepError("only an entry of one token can take it from the device")
+                token_src[q_start[r]] = e.src
+                self.has_src = True
         rows: List[int] = []
         for r, e in enumerate(entries):
             for w in e.want:
@@ -139,7 +148,7 @@ class StepContext:
                                    for o in range(0, int(q_len[r]), PREFILL_TILE)]
         arrays = [token_ids.astype(np.int32), positions, token_req, dec.astype(np.int32), other,
                   np.asarray(tiles, dtype=np.int32).reshape(-1), q_start, q_len, ctx_len, slots,
-                  np.asarray(rows, dtype=np.int32)] + [tb.reshape(-1) for tb in tables]
+                  np.asarray(rows, dtype=np.int32), token_src] + [tb.reshape(-1) for tb in tables]
         key = tuple(len(a) for a in arrays) + (width,)
         self.layout_key = key
         buf = buffers.get(key) if buffers is not None else None
@@ -156,9 +165,9 @@ class StepContext:
         dev = buf.dev
         views = [dev[o:o + n] for o, n in buf.offsets]
         (self.token_ids, self.positions, self.token_req, self.decode_tokens, self.other_tokens,
-         pt, self.q_start, self.q_len, self.ctx_len, self.slots, self.logit_rows) = views[:11]
+         pt, self.q_start, self.q_len, self.ctx_len, self.slots, self.logit_rows, self.token_src) = views[:12]
         self.prefill_tiles = pt.view(-1, 2)
-        self.block_tables = [v.view(R, width) for v in views[11:]]
+        self.block_tables = [v.view(R, width) for v in views[12:]]
         self.err = err
         self.device = device
 
@@ -180,6 +189,13 @@ class StepRunner:
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
         self.graph_launches = 0        # kernels replayed through graphs (for launch counts)
         self.graphs_captured = 0
+        # the ids the last step sampled, left on the device for a next step that starts before the
+        # host has read them (StepEntry.src)
+        self.sampled = torch.zeros(max(1, cache.max_seqs), dtype=torch.int32, device=self.device)
+
+    def publish_sampled(self, ids: torch.Tensor) -> None:
+        """Keep this step's sampled ids (int32 [n], on the device) for the next step's entries with `src`."""
+        self.sampled[:ids.shape[0]].copy_(ids)
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the entries as one batch; float32 logits [wanted rows, vocab] on the
@@ -195,6 +211,9 @@ class StepRunner:
         graphed = self.use_graphs and decode_only
         ctx = StepContext(entries, self.cache, self.device, self.err, self.buffers, bucket_width=graphed)
         self.last_ctx = ctx
+        if ctx.has_src:
+            from ..kernels import ops
+            ops.take_sampled_ids(ctx.token_ids, ctx.token_src, self.sampled, self.err)
         if not graphed:
             return self.model.forward(ctx, self.cache)
         buf = ctx.buffers

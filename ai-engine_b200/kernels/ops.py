@@ -56,6 +56,15 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, err: torch.Tensor,
     return out
 
 
+def take_sampled_ids(ids: torch.Tensor, src: torch.Tensor, last: torch.Tensor, err: torch.Tensor) -> None:
+    """ids[t] = last[src[t]] where src[t] >= 0 (int32, in place): tokens that the previous step
+    sampled and the host has not read yet."""
+    _dev(ids, src, last, err)
+    lib = library("elementwise.cu")
+    check(lib.aie_take_sampled_ids(_p(ids), _p(src), _p(last), c_int(ids.shape[0]), c_int(last.shape[0]),
+                                   _p(err), _stream()), "take_sampled_ids")
+
+
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
                 write_back: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -214,6 +214,9 @@ def time_gemms(torch, tokens):
         for s_ in (2, 3, 4, 6, 9, 13):       # K cut into parts that are left for the consumer to add
             if T <= 64 and N < 148 * 128:
                 impls[f"tcgen05_p{s_}"] = (lambda s_=s_: ops.gemm_tc(x, w, torch.float32, err, splits=s_, raw_parts=True))
+        if name == "gate_up" and T <= 64:       # the activation in the epilogue, K cut into parts joined in a cluster
+            for s_ in (1, 2, 3, 4):
+                impls[f"tcgen05_swiglu_s{s_}"] = (lambda s_=s_: ops.gemm_tc(x, w, torch.bfloat16, err, splits=s_, swiglu=True))
         row = {}
         for iname, fn in impls.items():
             for _ in range(3):

@@ -191,7 +191,7 @@ class StepRunner:
         self.graphs_captured = 0
         # the ids the last step sampled, left on the device for a next step that starts before the
         # host has read them (StepEntry.src)
-        self.sampled = torch.zeros(max(1, cache.max_seqs), dtype=torch.int32, device=self.device)
+        self.sampled = torch.zeros(max(1, getattr(cache, 'max_seqs', 1)), dtype=torch.int32, device=self.device)
 
     def publish_sampled(self, ids: torch.Tensor) -> None:
         """Keep this step's sampled ids (int32 [n], on the device) for the next step's entries with `src`."""

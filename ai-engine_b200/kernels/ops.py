@@ -5,7 +5,6 @@ stream.  Shapes and dtypes a kernel does not take are refused with an error.
 from __future__ import annotations
 
 import ctypes
-import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -153,13 +152,14 @@ def tc_tile(T: int) -> int:
 def tc_splits(T: int, N: int, K: int, bn: int) -> int:
     """Parts to cut K into.  A weight with fewer 128-row tiles than the machine has SMs is
     cut so that the grid comes close to three CTAs per SM (what fits beside each other with
-    4-stage rings), each part at least 4 K blocks of 64; measured with `bench.py --only gemm`:
-    more, shorter CTAs beat fewer with deep rings.  A weight with more tiles is not cut."""
+    4-stage rings), each part at least 12 K blocks of 64: measured inside whole decode steps
+    of 1 to 64 tokens, K = 4096 is best cut into 5 parts (fewer leave SMs idle, more pay for
+    their unjoined float32 parts, which the consumer reads).  A weight with more tiles is not cut."""
     tiles = ((N + 127) // 128) * ((T + bn - 1) // bn)
     kb = (K + 63) // 64
     if tiles >= 148:
         return 1
-    return max(1, min((3 * 148) // tiles, kb // 4 if kb >= 4 else 1))
+    return max(1, min((3 * 148) // tiles, kb // 12))
 
 
 TC_SWIGLU_BLOCK = 64     # gate/up rows per half of a 128-row weight tile

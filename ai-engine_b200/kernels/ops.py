@@ -28,7 +28,14 @@ def _p(t: Optional[torch.Tensor]):
     return c_void_p(0 if t is None else t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """The current stream of device 0 as a handle for the launchers (the raw query costs a fraction
+    of a microsecond; `torch.cuda.current_stream()` several, once per kernel launch)."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(0))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 

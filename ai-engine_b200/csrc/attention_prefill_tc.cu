@@ -1,5 +1,5 @@
 // bfloat16 paged attention for portions of prompts on the fifth-generation tensor cores
-// (head size 128): scores and outputs live in tensor memory, operands come from shared memory
+// (head sizes 64 and 128): scores and outputs live in tensor memory, operands come from shared memory
 // filled by TMA, softmax is float32 in registers.
 //
 // One CTA owns 128 query tokens of one head.  For each tile of 128 keys:
@@ -32,26 +32,27 @@
 
 #define AT_M 128          // query rows per CTA
 #define AT_N 128          // keys per tile
-#define AT_D 128          // head size
 #define AT_THREADS 192      // loader warp, MMA warp, 4 softmax warps
 #define AT_HALF_BYTES (128 * 64 * 2)      // one [128 x 64] bf16 swizzle atom column: 16 KB
 
 #define AT_RESCALE_STEP 8.0f     // a row's reference maximum moves in steps of more than this (log2 units)
 
-struct AtSmem {
-    // [alignment slack | 1 KB: barriers | Q 32 KB | K 2 x 32 KB | V 2 x 32 KB]
-    static constexpr int q_off = 1024, k_off = q_off + 2 * AT_HALF_BYTES, v_off = k_off + 4 * AT_HALF_BYTES,
-                         end = v_off + 4 * AT_HALF_BYTES;
+// HD: head size, HD / 64 halves of 64 columns.  A tile of 128 keys (or queries) holds 16 KB per half.
+template <int HD> struct AtSmem {
+    static constexpr int HV = HD / 64;
+    static constexpr int tile = HV * AT_HALF_BYTES;
+    // [alignment slack | 1 KB: barriers | Q | K x 2 | V x 2]
+    static constexpr int q_off = 1024, k_off = q_off + tile, v_off = k_off + 2 * tile, end = v_off + 2 * tile;
     static constexpr int bytes = 1024 + end;
 };
 
 // shared-memory descriptor of an MN-major operand: rows of 64 elements (128 bytes) along MN,
-// groups of 8 K-rows 2048 bytes apart, blocks of 64 MN elements `lbo` bytes apart
-__device__ __forceinline__ unsigned long long umma_desc_mn(const void* tile, unsigned lbo_bytes) {
+// groups of 8 K-rows `sbo` bytes apart, blocks of 64 MN elements `lbo` bytes apart
+__device__ __forceinline__ unsigned long long umma_desc_mn(const void* tile, unsigned lbo_bytes, unsigned sbo_bytes) {
     unsigned long long d = 0;
     d |= (unsigned long long)((tc_smem(tile) >> 4) & 0x3FFFu);
     d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    d |= (unsigned long long)(2048 >> 4) << 32;
+    d |= (unsigned long long)((sbo_bytes >> 4) & 0x3FFFu) << 32;
     d |= (unsigned long long)1 << 46;
     d |= (unsigned long long)2 << 61;
     return d;
@@ -100,6 +101,7 @@ __device__ __forceinline__ float at_hi(unsigned long long v) {
                    "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),   \
                    "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory")
 
+template <int HD>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
@@ -120,9 +122,12 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     unsigned long long* v_fixed = o_done + 1;
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(v_fixed + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    unsigned char* q_s = sm + AtSmem::q_off;
-    unsigned char* k_s = sm + AtSmem::k_off;       // stage st at + st * 2 * AT_HALF_BYTES
-    unsigned char* v_s = sm + AtSmem::v_off;
+    constexpr int HV = HD / 64;                    // halves of 64 columns
+    constexpr int TILE = AtSmem<HD>::tile;         // bytes of a 128-row tile
+    constexpr int GROUP = HV * 1024;               // bytes of 8 rows (all halves) of a key or value tile
+    unsigned char* q_s = sm + AtSmem<HD>::q_off;
+    unsigned char* k_s = sm + AtSmem<HD>::k_off;   // stage st at + st * TILE
+    unsigned char* v_s = sm + AtSmem<HD>::v_off;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile_i = n_tiles - 1 - (int)blockIdx.x;      // later tiles hold more keys: start them first
@@ -152,7 +157,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
     if (warp == 1) {    // tensor memory: score buffer b at columns [128 b, 128 b + 128) (P over its first 64),
-                        // outputs at [256, 384)
+                        // outputs at [256, 256 + head size)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(tmem_slot)), "r"(512));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
@@ -164,9 +169,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     if (warp == 0) {
             if (lane == 0) {
             // queries of this tile: rows t0 .. t0 + 127 of q [T, H * 128], columns of head h
-            mbar_expect_tx(q_full, 2 * AT_HALF_BYTES);
-            tma_load_2d(q_s, &map_q, q_full, h * AT_D, t0);
-            tma_load_2d(q_s + AT_HALF_BYTES, &map_q, q_full, h * AT_D + 64, t0);
+            mbar_expect_tx(q_full, TILE);
+            for (int hv = 0; hv < HV; ++hv) tma_load_2d(q_s + hv * AT_HALF_BYTES, &map_q, q_full, h * HD + hv * 64, t0);
         }
         // lane i owns page i of every key tile: one box per page (all 128 columns of its P keys); the id of
         // the next tile's page is read while this tile's boxes are issued
@@ -192,12 +196,12 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 unsigned long long* empty = kv ? &v_empty[st] : &k_empty[st];
                 if (lane == 0) {
                     ok = mbar_wait(empty, ((j >> 1) & 1) ^ 1, abort_flag, err);
-                    if (ok) mbar_expect_tx(full, (unsigned)n_pages * (unsigned)P * 256u);
+                    if (ok) mbar_expect_tx(full, (unsigned)n_pages * (unsigned)P * (unsigned)(HD * 2));
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
                 if (have)
-                    tma_load_4d((kv ? v_s : k_s) + st * 2 * AT_HALF_BYTES + lane * P * 256, kv ? &map_v : &map_k, full,
+                    tma_load_4d((kv ? v_s : k_s) + st * TILE + lane * P * (HD * 2), kv ? &map_v : &map_k, full,
                                 0, 0, 0, group0);
                 __syncwarp();
             }
@@ -213,11 +217,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 if (lane == 0) ok2 = mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, err);
                 ok2 = __shfl_sync(0xffffffffu, ok2 ? 1 : 0, 0) != 0;
                 if (ok2) {
-                    unsigned char* vd = v_s + st * 2 * AT_HALF_BYTES;
+                    unsigned char* vd = v_s + st * TILE;
                     const int n_bad = AT_N - first_bad;
-                    for (int i = lane; i < n_bad * 16; i += 32) {      // 16 chunks of 16 bytes per row (two halves)
-                        const int row = first_bad + i / 16, c = i % 16;
-                        *reinterpret_cast<uint4*>(vd + ((row >> 3) * 2 + (c >> 3)) * 1024 + (row & 7) * 128 + (c & 7) * 16) =
+                    for (int i = lane; i < n_bad * HV * 8; i += 32) {      // 8 chunks of 16 bytes per row and half
+                        const int row = first_bad + i / (HV * 8), c = i % (HV * 8);
+                        *reinterpret_cast<uint4*>(vd + (row >> 3) * GROUP + (c >> 3) * 1024 + (row & 7) * 128 + (c & 7) * 16) =
                             make_uint4(0, 0, 0, 0);
                     }
                     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -228,14 +232,14 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const unsigned idesc_s = umma_idesc(AT_N), idesc_o = umma_idesc(AT_D, true);
-            // S(j) = Q . K(j)^T over d = 128 into score buffer j & 1: 8 steps of 16
+            const unsigned idesc_s = umma_idesc(AT_N), idesc_o = umma_idesc(HD, true);
+            // S(j) = Q . K(j)^T over the head size into score buffer j & 1: steps of 16
             auto issue_scores = [&](int j) {
-                unsigned char* kd = k_s + (j & 1) * 2 * AT_HALF_BYTES;
+                unsigned char* kd = k_s + (j & 1) * TILE;
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
+                for (int ks = 0; ks < HD / 16; ++ks) {
                     const unsigned long long da = umma_desc(q_s + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
-                    const unsigned long long db = umma_desc(kd + (ks >> 2) * 1024, 2048) + 2 * (ks & 3);
+                    const unsigned long long db = umma_desc(kd + (ks >> 2) * 1024, GROUP) + 2 * (ks & 3);
                     umma(tmem_base + (unsigned)((j & 1) * AT_N), da, db, idesc_s, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(&k_empty[j & 1]);
@@ -264,11 +268,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 // O += P . V over 128 keys: 8 steps of 16 keys; P is in tensor memory (two keys to a column),
-                // V is MN-major: 16 keys = two groups of 8 rows, the two d-halves 1 KB apart
-                unsigned char* vd = v_s + st * 2 * AT_HALF_BYTES;
+                // V is MN-major: 16 keys = two groups of 8 rows, the halves of the head 1 KB apart
+                unsigned char* vd = v_s + st * TILE;
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
-                    const unsigned long long db = umma_desc_mn(vd + ks * 2 * 2048, 1024);
+                    const unsigned long long db = umma_desc_mn(vd + ks * 2 * GROUP, 1024, GROUP);
                     umma_a_tmem(tmem_base + 256u, tmem_base + (unsigned)(st * AT_N + ks * 8), db, idesc_o,
                                 (j > 0 || ks > 0) ? 1u : 0u);
                 }
@@ -328,7 +332,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
-                for (int c0 = 0; c0 < AT_D; c0 += 32) {
+                for (int c0 = 0; c0 < HD; c0 += 32) {
                     unsigned ov[32];
                     AT_LD32(ov, tmem_o + lane_addr + c0);
                     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
@@ -373,9 +377,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-            bf16* dst = out + ((size_t)(t0 + row) * H + h) * AT_D;
+            bf16* dst = out + ((size_t)(t0 + row) * H + h) * HD;
 #pragma unroll
-            for (int c0 = 0; c0 < AT_D; c0 += 32) {
+            for (int c0 = 0; c0 < HD; c0 += 32) {
                 unsigned ov[32];
                 AT_LD32(ov, tmem_o + lane_addr + c0);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
@@ -412,10 +416,30 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     }
 }
 
-// q, out: [T, H, 128] bf16; k_pages, v_pages: [num_pages, K, P, 128] bf16 of one layer;
+template <int HD>
+static int launch_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out, const int* tiles,
+                             int n_tiles, const int* q_start, const int* q_len, const int* ctx_len,
+                             const int* block_table, int bt_width, int num_pages, int P, int T, int H, int K,
+                             float scale, unsigned* err, cudaStream_t stream) {
+    CUtensorMap mq, mk, mv;
+    int rc = tc_make_map_2d(&mq, q, (unsigned long long)T, (unsigned long long)H * HD, (unsigned long long)H * HD * 2, AT_M, 64);
+    if (rc) return rc;
+    const unsigned long long rows = (unsigned long long)num_pages * K * P;
+    rc = tc_make_map_rows8(&mk, k_pages, rows, HD / 64, P / 8);
+    if (rc) return rc;
+    rc = tc_make_map_rows8(&mv, v_pages, rows, HD / 64, P / 8);
+    if (rc) return rc;
+    cudaFuncSetAttribute(paged_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, AtSmem<HD>::bytes);
+    paged_prefill_tc_kernel<HD><<<dim3(n_tiles, H), AT_THREADS, AtSmem<HD>::bytes, stream>>>(
+        mq, mk, mv, (bf16*)out, tiles, n_tiles, q_start, q_len, ctx_len, block_table, bt_width, num_pages, P, H, K,
+        scale, err);
+    AIE_LAUNCH_CHECK();
+}
+
+// q, out: [T, H, d] bf16; k_pages, v_pages: [num_pages, K, P, d] bf16 of one layer;
 // tiles: [n_tiles][2] = (request row, offset of the 128-token tile within the request's tokens).
-// Takes head size 128, pages of 8 .. 128 keys that divide 128 and layers without a window; refuses the rest
-// (AIE_UNSUPPORTED): they take the mma.sync kernel.
+// Takes head sizes 64 and 128, pages of 8 .. 128 keys that divide 128 and layers without a window; refuses the
+// rest (AIE_UNSUPPORTED): they take the mma.sync kernel.
 extern "C" int aie_paged_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out,
                                               const int* tiles, int n_tiles, const int* q_start, const int* q_len,
                                               const int* ctx_len, const int* block_table, int bt_width,
@@ -423,19 +447,10 @@ extern "C" int aie_paged_attention_prefill_tc(const void* q, const void* k_pages
                                               float scale, unsigned* err, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (K <= 0 || H % K) return AIE_BAD_ARG;
-    if (d != AT_D || P < 8 || P > 128 || 128 % P || H > 65535 || window > 0) return AIE_UNSUPPORTED;
+    if ((d != 64 && d != 128) || P < 8 || P > 128 || 128 % P || H > 65535 || window > 0) return AIE_UNSUPPORTED;
     if (((size_t)q & 15) || ((size_t)k_pages & 15) || ((size_t)v_pages & 15)) return AIE_UNSUPPORTED;
-    CUtensorMap mq, mk, mv;
-    int rc = tc_make_map_2d(&mq, q, (unsigned long long)T, (unsigned long long)H * d, (unsigned long long)H * d * 2, AT_M, 64);
-    if (rc) return rc;
-    const unsigned long long rows = (unsigned long long)num_pages * K * P;
-    rc = tc_make_map_rows8(&mk, k_pages, rows, P / 8);
-    if (rc) return rc;
-    rc = tc_make_map_rows8(&mv, v_pages, rows, P / 8);
-    if (rc) return rc;
-    cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AtSmem::bytes);
-    paged_prefill_tc_kernel<<<dim3(n_tiles, H), AT_THREADS, AtSmem::bytes, stream>>>(
-        mq, mk, mv, (bf16*)out, tiles, n_tiles, q_start, q_len, ctx_len, block_table, bt_width, num_pages, P, H, K,
-        scale, err);
-    AIE_LAUNCH_CHECK();
+#define ARGS q, k_pages, v_pages, out, tiles, n_tiles, q_start, q_len, ctx_len, block_table, bt_width, num_pages, P, T, H, K, \
+             scale, err, stream
+    return d == 128 ? launch_prefill_tc<128>(ARGS) : launch_prefill_tc<64>(ARGS);
+#undef ARGS
 }

@@ -102,15 +102,16 @@ static inline TcEncodeTiledFn tc_encode_fn() {
     return fn;
 }
 
-// bf16 matrix [rows, 128] (rows 256 bytes apart, rows a multiple of 8) seen as [groups of 8 rows][2 halves of
+// bf16 matrix [rows, 64 * halves] (contiguous rows, rows a multiple of 8) seen as [groups of 8 rows][halves of
 // 64 columns][8 rows][64]: a box of `box_groups` groups lands in shared memory as, per group, the 8 rows of
-// the first 64 columns (1 KB, 128-byte swizzled) and then the 8 rows of the other 64 columns
-static inline int tc_make_map_rows8(CUtensorMap* map, const void* ptr, unsigned long long rows, int box_groups) {
+// the first 64 columns (1 KB, 128-byte swizzled), then the 8 rows of the next 64 columns, and so on
+static inline int tc_make_map_rows8(CUtensorMap* map, const void* ptr, unsigned long long rows, int halves,
+                                    int box_groups) {
     TcEncodeTiledFn fn = tc_encode_fn();
     if (!fn) return AIE_UNSUPPORTED;
-    cuuint64_t dims[4] = {64, 8, 2, (cuuint64_t)(rows / 8)};
-    cuuint64_t strides[3] = {256, 128, 2048};
-    cuuint32_t box[4] = {64, 8, 2, (cuuint32_t)box_groups};
+    cuuint64_t dims[4] = {64, 8, (cuuint64_t)halves, (cuuint64_t)(rows / 8)};
+    cuuint64_t strides[3] = {(cuuint64_t)halves * 128, 128, (cuuint64_t)halves * 1024};
+    cuuint32_t box[4] = {64, 8, (cuuint32_t)halves, (cuuint32_t)box_groups};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

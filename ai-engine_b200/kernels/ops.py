@@ -387,12 +387,12 @@ def paged_attention_prefill(q, k_pages, v_pages, tiles, q_start, q_len, ctx_len,
 def paged_attention_prefill_tc(q, k_pages, v_pages, tiles, q_start, q_len, ctx_len, block_table,
                                scale: float, window: int, err, out) -> bool:
     """The tcgen05 version of paged_attention_prefill (scores and outputs in tensor memory,
-    operands by TMA).  Takes head size 128, pages of 8 .. 128 keys that divide 128, no window; returns
+    operands by TMA).  Takes head sizes 64 and 128, pages of 8 .. 128 keys that divide 128, no window; returns
     False when it does not take the sizes (nothing was launched)."""
     _dev(q, k_pages, v_pages, tiles, q_start, q_len, ctx_len, block_table, err, out)
     T, H, d = q.shape
     num_pages, K, P, _ = k_pages.shape
-    if d != 128 or window > 0 or P < 8 or P > 128 or 128 % P:
+    if d not in (64, 128) or window > 0 or P < 8 or P > 128 or 128 % P:
         return False
     lib = library("attention_prefill_tc.cu")
     rc = lib.aie_paged_attention_prefill_tc(_p(q), _p(k_pages), _p(v_pages), _p(out), _p(tiles),

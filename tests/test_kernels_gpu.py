@@ -251,7 +251,7 @@ def test_paged_attention_prefill_tensor_cores(shape):
     assert err.max() <= 2e-2, f"first wrong token {int((err > 2e-2).nonzero()[0])} of {sum(q_lens)}: {float(err.max())}"
 
 
-PREFILL_TC_SHAPES = [  # H, K, P, lens, q_lens  (head size 128, no window)
+PREFILL_TC_SHAPES = [  # H, K, P, lens, q_lens  (head sizes 64 and 128, no window)
     (4, 2, 16, [5, 40], [5, 7]),
     (32, 8, 16, [300, 130, 64], [300, 2, 64]),
     (6, 2, 8, [257, 65], [129, 65]),           # a portion that starts mid-page and mid-tile
@@ -263,10 +263,10 @@ PREFILL_TC_SHAPES = [  # H, K, P, lens, q_lens  (head size 128, no window)
 ]
 
 
+@pytest.mark.parametrize("d", [128, 64])
 @pytest.mark.parametrize("shape", PREFILL_TC_SHAPES)
-def test_paged_attention_prefill_tcgen05(shape):
+def test_paged_attention_prefill_tcgen05(shape, d):
     H, K, P, lens, q_lens = shape
-    d = 128
     s = paged_setup(torch.bfloat16, H, K, d, P, lens, q_lens, seed=H + P + len(lens))
     scale = 1.0 / math.sqrt(d)
     e = err_word()
@@ -312,11 +312,11 @@ def test_prefill_tcgen05_scores_that_grow_along_the_sequence():
 
 
 def test_prefill_tcgen05_refuses_what_it_does_not_take():
-    s = paged_setup(torch.bfloat16, 4, 2, 64, 16, [40], [40], seed=1)
+    s = paged_setup(torch.bfloat16, 4, 2, 32, 16, [40], [40], seed=1)
     i32 = lambda a: torch.tensor(a, device=DEV, dtype=torch.int32)
     out = torch.zeros_like(s["q"])
     args = (s["q"], s["k_pages"], s["v_pages"], i32([[0, 0]]), i32([0]), i32([40]), i32([0]), s["bt"], 0.125)
-    assert not ops().paged_attention_prefill_tc(*args, 0, err_word(), out)          # head size 64
+    assert not ops().paged_attention_prefill_tc(*args, 0, err_word(), out)          # head size 32
     s = paged_setup(torch.bfloat16, 4, 2, 128, 16, [40], [40], seed=1)
     args = (s["q"], s["k_pages"], s["v_pages"], i32([[0, 0]]), i32([0]), i32([40]), i32([0]), s["bt"], 0.09)
     assert not ops().paged_attention_prefill_tc(*args, 7, err_word(), torch.zeros_like(s["q"]))   # a window

@@ -47,8 +47,8 @@ template <int BN> struct TcSmem {
     static constexpr int stage_bytes = TC_BM * TC_BK * 2 + BN * TC_BK * 2;
     static constexpr int max_stages = BN <= 64 ? 8 : (BN <= 128 ? 6 : 4);     // what 227 KB hold
     // the ring depth is chosen per launch: a grid of at most one CTA per SM takes the deepest ring
-    // (one CTA must keep its SM's share of the memory system busy); a larger grid takes a short ring
-    // so that several CTAs share an SM and cover each other's start and end
+    // (one CTA must keep its SM's share of the memory system busy); a larger grid takes the deepest
+    // ring with which its CTAs still share an SM and cover each other's start and end
     static constexpr int tile_bytes = BN * TC_BM * 4;      // the float32 tile staged for joining parts
     // [alignment slack | 1024 bytes of barriers | ring of stages, reused for the staged tile]
     static constexpr int bytes_for(int stages) {
@@ -273,7 +273,13 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((N + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, splits);
     const long long ctas = (long long)cfg.gridDim.x * cfg.gridDim.y * cfg.gridDim.z;
-    int stages = ctas <= 148 ? TcSmem<BN>::max_stages : (TcSmem<BN>::max_stages >= 8 ? 4 : TcSmem<BN>::max_stages);
+    // the deepest ring that still lets the grid's CTAs sit beside each other: one, two or three to an SM
+    // (228 KB of shared memory an SM, 1 KB of it reserved per CTA); a grid of more than three waves
+    // takes the ring for three
+    const int per_sm = ctas <= 148 ? 1 : (ctas <= 2 * 148 ? 2 : 3);
+    int stages = ((228 * 1024) / per_sm - 1024 - 2048) / TcSmem<BN>::stage_bytes;
+    if (stages > TcSmem<BN>::max_stages) stages = TcSmem<BN>::max_stages;
+    if (stages < 2) stages = 2;
     if (stages > kbps) stages = kbps < 2 ? 2 : kbps;
     const int smem = TcSmem<BN>::bytes_for(stages);
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN>::bytes_for(TcSmem<BN>::max_stages));

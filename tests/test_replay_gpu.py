@@ -207,15 +207,15 @@ FULL_SIZE_LAYERS = {
 
 @pytest.mark.parametrize("name", sorted(FULL_SIZE_LAYERS))
 def test_full_size_layers(tmp_path, name):
-    """One layer with the layer sizes of Llama-3-8B, Llama-3.2-3B and Llama-3.2-1B (a reduced vocabulary keeps
-    the folder small): the kernel configurations that full-size models take — products cut along K, tcgen05
+    """Layers with the sizes of Llama-3-8B (three of them), Llama-3.2-3B and Llama-3.2-1B (one each; a reduced
+    vocabulary keeps the folder small): the kernel configurations that full-size models take — products cut along K, tcgen05
     attention, grouped decode — against the plain implementation: a request whole, in portions and token by
     token, with a second request's tokens in the same steps."""
     import ai_engine_b200 as aie
     from ai_engine_b200.engine.replay import Replayer
 
-    raw = dict(architectures=["LlamaForCausalLM"], num_hidden_layers=1, vocab_size=4096, rope_theta=500000.0,
-               rms_norm_eps=1e-5, max_position_embeddings=8192, **FULL_SIZE_LAYERS[name])
+    raw = dict(architectures=["LlamaForCausalLM"], num_hidden_layers=3 if name == "llama3_8b" else 1, vocab_size=4096,
+               rope_theta=500000.0, rms_norm_eps=1e-5, max_position_embeddings=8192, **FULL_SIZE_LAYERS[name])
     d = os.path.join(str(tmp_path), name)
     aie.write_random_model(aie.LlamaConfig.from_dict(raw), d, seed=5, dtype="bfloat16")
     ids, other = random_ids(200, 4096, 31), random_ids(70, 4096, 32)

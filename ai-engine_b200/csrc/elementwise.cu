@@ -134,8 +134,23 @@ add_rmsnorm_row_kernel(float* __restrict__ x, const A* __restrict__ delta, const
     if (on) {
         s = reinterpret_cast<const float4*>(x + r * D)[i];
         if (delta) {
-            for (int p = 0; p < parts; ++p) {       // parts of a split product, added in order
-                const float4 dl = load4<A>(delta + p * part_stride + r * D + 4 * i);
+            // parts of a split product, added in order; four loads are in flight at a time
+            const A* dp = delta + r * D + 4 * i;
+            int p = 0;
+            for (; p + 4 <= parts; p += 4) {
+                float4 dl[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) dl[u] = load4<A>(dp + (size_t)(p + u) * part_stride);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    s.x += dl[u].x;
+                    s.y += dl[u].y;
+                    s.z += dl[u].z;
+                    s.w += dl[u].w;
+                }
+            }
+            for (; p < parts; ++p) {
+                const float4 dl = load4<A>(dp + (size_t)p * part_stride);
                 s.x += dl.x;
                 s.y += dl.y;
                 s.z += dl.z;

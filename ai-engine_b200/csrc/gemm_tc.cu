@@ -58,6 +58,22 @@ template <int BN> struct TcSmem {
 
 #define TC_EPI_STORE 0
 #define TC_EPI_SWIGLU 1
+#define TC_EPI_ROPE 2       // the fused q/k/v projection: rotate q and k by position, write k and v into their pages
+
+// What the rotary epilogue needs beside the product: the step's positions and block table, the pages of
+// the layer and the rotation's frequencies (rotation: crates/ai-engine-runtime/src/arch/rope.rs:38-44,66-106;
+// cache write: crates/ai-engine-candle/src/paged/attention.rs:59-83).  The output columns are
+// [H q heads | K k heads | K v heads] x d with d dividing 128, so a 128-row weight tile holds whole heads.
+struct TcRope {
+    bf16* q_out;              // [T, H, d]
+    bf16* k_pages;            // [num_pages, K, P, d]
+    bf16* v_pages;
+    const int* positions;     // [T]
+    const int* token_req;     // [T] row of the block table
+    const int* block_table;   // [R, bt_width]
+    const float* inv_freq;    // [d / 2]
+    int bt_width, num_pages, P, H, K, d, write;
+};
 
 __device__ __forceinline__ unsigned cluster_rank() {
     unsigned r;
@@ -81,7 +97,7 @@ template <int BN, int EPI, typename OT>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                OT* __restrict__ C, int T, int N, int K, int ldc, int kb_per_split, int STAGES, int raw_parts,
-               unsigned* err) {
+               unsigned* err, const TcRope rope) {
     constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
     extern __shared__ unsigned char tc_raw[];
     unsigned char* bars = reinterpret_cast<unsigned char*>(((size_t)tc_raw + 1023) & ~(size_t)1023);
@@ -223,6 +239,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const int f0 = blockIdx.x * COLS, width = EPI == TC_EPI_STORE ? N : N / 2;
             for (int idx = rank * share + e; idx < min((rank + 1) * share, total); idx += 128) {
                 const int tt = idx / COLS, j = idx % COLS;
+                if (EPI == TC_EPI_ROPE) {
+                    // pair (i, i + d/2) of head slot `slot`: columns c1, c2 of the tile
+                    const int hd = rope.d, half = hd / 2;
+                    const int hh = j / half, i = j % half;
+                    const int c1 = hh * hd + i, c2 = c1 + half;
+                    const int slot = blockIdx.x * (TC_BM / hd) + hh;
+                    float x1 = 0.f, x2 = 0.f;
+                    for (int p = 0; p < parts; ++p) {
+                        x1 += ld_peer(tile_addr + (tt * TC_BM + c1) * 4, p);
+                        x2 += ld_peer(tile_addr + (tt * TC_BM + c2) * 4, p);
+                    }
+                    const int t = t0 + tt;
+                    const int pos = rope.positions[t];
+                    if (slot >= rope.H + 2 * rope.K) continue;
+                    if (slot < rope.H + rope.K) {        // q and k heads are rotated; the angle in float32
+                        float sn, cs;
+                        sincosf((float)pos * rope.inv_freq[i], &sn, &cs);
+                        const float o1 = x1 * cs - x2 * sn, o2 = x1 * sn + x2 * cs;
+                        x1 = o1;
+                        x2 = o2;
+                    }
+                    bf16* dst;
+                    if (slot < rope.H) {
+                        dst = rope.q_out + ((size_t)t * rope.H + slot) * hd;
+                    } else {
+                        if (!rope.write) continue;           // the pages are another run's
+                        const int pidx = pos / rope.P;
+                        const int page = (pidx < rope.bt_width && pos >= 0)
+                                             ? rope.block_table[(size_t)rope.token_req[t] * rope.bt_width + pidx] : -1;
+                        if (page < 0 || page >= rope.num_pages) {
+                            atomicOr(err, AIE_DEV_PAGE_OOB);
+                            continue;
+                        }
+                        const bool is_v = slot >= rope.H + rope.K;
+                        const int kh = slot - rope.H - (is_v ? rope.K : 0);
+                        dst = (is_v ? rope.v_pages : rope.k_pages) +
+                              (((size_t)page * rope.K + kh) * rope.P + (pos - pidx * rope.P)) * hd;
+                    }
+                    dst[i] = __float2bfloat16_rn(x1);
+                    dst[i + half] = __float2bfloat16_rn(x2);
+                    continue;
+                }
                 float out;
                 if (EPI == TC_EPI_STORE) {
                     float acc = 0.f;
@@ -266,7 +324,7 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_
 
 template <int BN, int EPI, typename OT>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, int ldc,
-                     int splits, int raw_parts, unsigned* err, cudaStream_t st) {
+                     int splits, int raw_parts, unsigned* err, cudaStream_t st, const TcRope& rope = TcRope()) {
     const int kb_total = (K + TC_BK - 1) / TC_BK;
     const int kbps = (kb_total + splits - 1) / splits;
     auto kern = gemm_tc_kernel<BN, EPI, OT>;
@@ -300,7 +358,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int 
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, mx, (OT*)C, T, N, K, ldc, kbps, stages, raw_parts, err);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, mx, (OT*)C, T, N, K, ldc, kbps, stages, raw_parts, err, rope);
     return (int)e;
 }
 
@@ -339,6 +397,36 @@ extern "C" int aie_gemm_tc(const void* X, const void* W, void* C, int out_dtype,
     }
 #undef GO
     return rc;
+}
+
+// The fused q/k/v projection of a small step: qkv = X . W^T with K cut into `splits` parts (1 .. 8) joined in a
+// cluster, then, in the same kernel, q and k rotated by position (full rotation: inv_freq has d / 2 entries),
+// q written to q_out [T, H, d] and k, v into their cache pages.  d must divide 128 and N = (H + 2 K) d be a
+// multiple of 128; float32 sums, float32 angles.
+extern "C" int aie_gemm_tc_rope(const void* X, const void* W, int T, int N, int K, int bn, int splits, void* q_out,
+                                void* k_pages, void* v_pages, const int* positions, const int* token_req,
+                                const int* block_table, int bt_width, int num_pages, int P, int H, int Kh, int d,
+                                const float* inv_freq, int write, unsigned* err, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (K <= 0 || K % 8 || ((size_t)X & 15) || ((size_t)W & 15)) return AIE_UNSUPPORTED;
+    if (d < 2 || d % 2 || TC_BM % d || N != (H + 2 * Kh) * d || N % TC_BM) return AIE_UNSUPPORTED;
+    if (splits < 1 || splits > 8) return AIE_BAD_ARG;
+    if ((T + bn - 1) / bn > 65535) return AIE_UNSUPPORTED;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, W, N, K, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mx, X, T, K, bn);
+    if (rc) return rc;
+    TcRope r;
+    r.q_out = (bf16*)q_out; r.k_pages = (bf16*)k_pages; r.v_pages = (bf16*)v_pages;
+    r.positions = positions; r.token_req = token_req; r.block_table = block_table; r.inv_freq = inv_freq;
+    r.bt_width = bt_width; r.num_pages = num_pages; r.P = P; r.H = H; r.K = Kh; r.d = d; r.write = write;
+    switch (bn) {
+        case 16: return launch_tc<16, TC_EPI_ROPE, float>(mw, mx, nullptr, T, N, K, N, splits, 0, err, stream, r);
+        case 32: return launch_tc<32, TC_EPI_ROPE, float>(mw, mx, nullptr, T, N, K, N, splits, 0, err, stream, r);
+        case 64: return launch_tc<64, TC_EPI_ROPE, float>(mw, mx, nullptr, T, N, K, N, splits, 0, err, stream, r);
+        default: return AIE_BAD_ARG;
+    }
 }
 
 // A wait that nothing will ever satisfy, with a short limit: shows that a bounded wait gives up,

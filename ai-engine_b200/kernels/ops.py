@@ -206,6 +206,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, err: torch
 
 
 TC_MAX_TOKENS = 64       # up to here the tcgen05 kernel of this package; above, the library product
+TC_ROPE_MAX_TOKENS = 16  # up to here the q/k/v product rotates and writes the cache in its epilogue
 
 
 def linear_parts(x: torch.Tensor, w: torch.Tensor, err: Optional[torch.Tensor] = None,
@@ -254,6 +255,38 @@ def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor, block: int = 0,
         if y is not None:
             return y
     return silu_mul(linear(x, w_gu, x.dtype, err), block=block)
+
+
+def linear_rope_kv(x: torch.Tensor, w_qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                   positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor,
+                   inv_freq: torch.Tensor, H: int, K: int, d: int, err: torch.Tensor,
+                   write: bool = True) -> Optional[torch.Tensor]:
+    """The q/k/v projection of a small bfloat16 step with the rotation and the cache write in
+    its epilogue (one kernel instead of product + rotary kernel); returns q [T, H, d], or None
+    when the sizes are not taken: more than 16 tokens, a head size that does not divide 128,
+    a partial rotation, K not a multiple of 8."""
+    T, Kin = x.shape
+    N = w_qkv.shape[0]
+    if (T > TC_ROPE_MAX_TOKENS or x.dtype != torch.bfloat16 or w_qkv.dtype != torch.bfloat16
+            or k_pages.dtype != torch.bfloat16 or Kin % 8 or d % 2 or 128 % d or N % 128
+            or N != (H + 2 * K) * d or inv_freq.shape[0] * 2 != d):
+        return None
+    _dev(x, w_qkv, k_pages, v_pages, positions, token_req, block_table, inv_freq, err)
+    num_pages, Kp, P, dp = k_pages.shape
+    if (Kp, dp) != (K, d) or v_pages.shape != k_pages.shape:
+        raise KernelError("linear_rope_kv: page shape does not fit (K, d)")
+    bn = tc_tile(T)
+    kb = (Kin + 63) // 64
+    splits = max(1, min(8, kb // 8, (3 * 148) // max(1, N // 128)))
+    splits = -(-kb // -(-kb // splits))
+    q_out = torch.empty((T, H, d), dtype=torch.bfloat16, device=x.device)
+    lib = library("gemm_tc.cu")
+    check(lib.aie_gemm_tc_rope(_p(x), _p(w_qkv), c_int(T), c_int(N), c_int(Kin), c_int(bn), c_int(splits),
+                               _p(q_out), _p(k_pages), _p(v_pages), _p(positions), _p(token_req),
+                               _p(block_table), c_int(block_table.shape[1]), c_int(num_pages), c_int(P),
+                               c_int(H), c_int(K), c_int(d), _p(inv_freq), c_int(1 if write else 0), _p(err),
+                               _stream()), "gemm_tc_rope")
+    return q_out
 
 
 # ---------------------------------------------------------------------------

@@ -64,11 +64,16 @@ class GQAAttention(Mixer):
         return KVRequest(self.K, self.d, self.window)
 
     def forward(self, h, ctx, cache):
-        qkv = ops.linear_parts(h, self.w_qkv, ctx.err, self.env.dtype)
         inv_freq = self.rope.inv_freq if self.rope is not None else self._no_rope
-        q = ops.rope_kv_write(qkv, cache.k_pages, cache.v_pages, ctx.positions, ctx.token_req,
-                              cache.block_table, inv_freq, self.H, self.K, self.d, ctx.err,
-                              write=cache.writes)
+        # a small bfloat16 step: product, rotation and cache write in one kernel
+        q = ops.linear_rope_kv(h, self.w_qkv, cache.k_pages, cache.v_pages, ctx.positions, ctx.token_req,
+                               cache.block_table, inv_freq, self.H, self.K, self.d, ctx.err,
+                               write=cache.writes)
+        if q is None:
+            qkv = ops.linear_parts(h, self.w_qkv, ctx.err, self.env.dtype)
+            q = ops.rope_kv_write(qkv, cache.k_pages, cache.v_pages, ctx.positions, ctx.token_req,
+                                  cache.block_table, inv_freq, self.H, self.K, self.d, ctx.err,
+                                  write=cache.writes)
         a = ops.paged_attention(q, cache.k_pages, cache.v_pages, ctx, cache.block_table,
                                 self.scale, self.window)
         return ops.linear_parts(a.view(a.shape[0], self.H * self.d), self.w_o, ctx.err)

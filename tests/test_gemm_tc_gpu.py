@@ -151,6 +151,71 @@ def test_unjoined_parts_cover_k_exactly(T, N, K, splits):
     assert int(err.item()) == 0
 
 
+@pytest.mark.parametrize("H,K,d,P,Kin,T", [(32, 8, 128, 16, 4096, 8), (32, 8, 64, 16, 2048, 3), (6, 1, 32, 8, 320, 16),
+                                           (24, 8, 128, 32, 3072, 1), (4, 2, 16, 16, 64, 5)])
+def test_qkv_product_with_rotation_and_cache_write_in_its_epilogue(H, K, d, P, Kin, T):
+    """q/k/v product, rotation and page write in one kernel against the plain formulas: q rows, the rotated
+    key and the value in the right slot of the right page, nothing else in the pool touched."""
+    import plain_llama as pl
+    from ai_engine_b200.kernels import ops
+
+    torch.manual_seed(H + d + T)
+    N = (H + 2 * K) * d
+    x = torch.randn(T, Kin, device=DEV).bfloat16()
+    w = (torch.randn(N, Kin, device=DEV) * (1.0 / Kin ** 0.5)).bfloat16()
+    R, pages_per = 3, 6
+    num_pages = R * pages_per + 2
+    bt = torch.randperm(num_pages, device=DEV)[:R * pages_per].int().view(R, pages_per).contiguous()
+    token_req = torch.tensor([t % R for t in range(T)], dtype=torch.int32, device=DEV)
+    positions = torch.tensor([(7 * t + 3) % (pages_per * P) for t in range(T)], dtype=torch.int32, device=DEV)
+    # two tokens of one request must not share a position
+    seen = set()
+    for t in range(T):
+        while (int(token_req[t]), int(positions[t])) in seen:
+            positions[t] = (int(positions[t]) + 1) % (pages_per * P)
+        seen.add((int(token_req[t]), int(positions[t])))
+    inv_freq = torch.from_numpy(pl.inv_freq_default(d, 500000.0)).to(DEV)
+    kp = torch.full((num_pages, K, P, d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    vp = torch.full_like(kp, float("nan"))
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    q = ops.linear_rope_kv(x, w, kp, vp, positions, token_req, bt, inv_freq, H, K, d, err)
+    assert q is not None and q.shape == (T, H, d)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    y = (x.double() @ w.double().T).view(T, H + 2 * K, d).cpu()
+    pos = positions.cpu()
+    rot = lambda t: pl.rope(t.transpose(0, 1), pos, pl.inv_freq_default(d, 500000.0)).transpose(0, 1)
+    tol = 2e-2 * max(1.0, float(y.abs().max()))
+    assert (q.double().cpu() - rot(y[:, :H])).abs().max() <= tol
+    kr, vr = rot(y[:, H:H + K]), y[:, H + K:]
+    touched = torch.zeros(kp.shape, dtype=torch.bool, device=DEV)
+    for t in range(T):
+        pg, sl = int(bt[int(token_req[t]), int(pos[t]) // P]), int(pos[t]) % P
+        assert (kp[pg, :, sl].double().cpu() - kr[t]).abs().max() <= tol
+        assert (vp[pg, :, sl].double().cpu() - vr[t]).abs().max() <= tol
+        touched[pg, :, sl] = True
+    assert bool(torch.isnan(kp[~touched]).all()) and bool(torch.isnan(vp[~touched]).all())
+    # against the two-kernel path (same sums, same rotation): equal up to the order of the float32 adds
+    kp2, vp2 = torch.zeros_like(kp), torch.zeros_like(vp)
+    q2 = ops.rope_kv_write(ops.linear_parts(x, w, err), kp2, vp2, positions, token_req, bt, inv_freq, H, K, d, err)
+    assert (q.float() - q2.float()).abs().max() <= tol / 4
+    # write=False leaves the pool alone and still returns q
+    kp3 = torch.full_like(kp, float("nan"))
+    q3 = ops.linear_rope_kv(x, w, kp3, torch.full_like(kp, float("nan")), positions, token_req, bt, inv_freq, H, K, d,
+                            err, write=False)
+    assert torch.equal(q3, q) and bool(torch.isnan(kp3).all())
+    # a block-table entry outside the pool is flagged, not followed
+    bad = bt.clone()
+    bad[int(token_req[0]), int(pos[0]) // P] = num_pages + 5
+    ops.linear_rope_kv(x, w, torch.zeros_like(kp), torch.zeros_like(kp), positions, token_req, bad, inv_freq, H, K, d, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) & 2
+    err.zero_()
+    # sizes it does not take
+    assert ops.linear_rope_kv(torch.randn(17, Kin, device=DEV).bfloat16(), w, kp, vp, positions, token_req, bt, inv_freq,
+                              H, K, d, err) is None
+
+
 def test_a_bounded_wait_gives_up_and_the_step_runner_reports_it():
     """A barrier that nothing arrives at: the wait runs out after its limit, the kernel sets the
     device error word and returns; the context stays usable and check_errors raises."""

@@ -22,11 +22,15 @@
 //                      C[token][row] (32 lanes write 32 consecutive rows of a token).
 // Split K: the CTAs that share an output tile form a thread-block cluster along z.
 // Each stores its float32 partial tile in its own shared memory; after a cluster
-// barrier the CTA of rank 0 adds the tiles through distributed shared memory in rank
-// order (so the sum does not depend on timing), applies the epilogue and stores.
-// Epilogues: plain store (bf16 or float32), or SwiGLU on a weight whose 128-row tiles
+// barrier every CTA adds, for its share of the tile, the tiles of all through distributed
+// shared memory in rank order (so the sum does not depend on timing), applies the
+// epilogue and stores.  Or the parts are left unjoined (`raw_parts`: float32
+// [parts, T, N]) for a consumer that adds them (the norm and rotary kernels).
+// Epilogues: plain store (bf16 or float32); SwiGLU on a weight whose 128-row tiles
 // hold 64 gate rows followed by their 64 up rows: a[t, f] = silu(g) * u in float32
-// (crates/ai-engine-runtime/src/arch/ffn.rs:50-54).
+// (crates/ai-engine-runtime/src/arch/ffn.rs:50-54); or, for the fused q/k/v projection
+// of a small step, the rotation of q and k by position and the write of k and v into
+// their cache pages (a 128-row tile holds whole heads).
 // The kernel is launched as a programmatic dependent: barriers, tensor memory and the
 // first weight tiles of the ring are set up and requested before griddepcontrol.wait,
 // while the previous kernel is still finishing; only the token tiles wait for it.

@@ -22,7 +22,6 @@ from typing import Deque, Dict, List, Optional, Sequence, Tuple, Union
 import torch
 
 from ..cache.manager import PagedCache, host
-from ..config.registry import load_config
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .loading import load_model, parse_dtype, random_model

@@ -13,7 +13,7 @@ Logits come back only for the rows that are wanted.
 from __future__ import annotations
 
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
 import numpy as np

@@ -4,7 +4,6 @@ stream.  Shapes and dtypes a kernel does not take are refused with an error.
 """
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 

@@ -11,7 +11,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..weights.loader import TensorSpec, WeightSource
-from .base import BuildEnv, KVRequest, LayerCache, Part, StateRequest
+from .base import BuildEnv, KVRequest, Part, StateRequest
 from .registry import lookup
 from .spec import LayerSpec, ModelSpec, PartSpec
 

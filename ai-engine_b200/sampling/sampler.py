@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 from ctypes import c_int
-from typing import List, Sequence
+from typing import Sequence
 
 import numpy as np
 import torch

@@ -12,7 +12,7 @@ from __future__ import annotations
 import hashlib
 import json
 import os
-from typing import Dict, Iterator, Sequence, Tuple
+from typing import Iterator, Sequence, Tuple
 
 import torch
 

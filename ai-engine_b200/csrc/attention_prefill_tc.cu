@@ -7,7 +7,9 @@
 //                      lane i issuing the box of the tile's page i (the pool of a layer is seen as
 //                      [groups of 8 rows][2 halves of the head][8 rows][64], so a box lands as 1 KB
 //                      128-byte-swizzled atoms, the two halves of a group side by side), a ring of
-//                      two buffers for keys and one of two for values; the loop has no division and
+//                      three buffers for keys and one of three for values (four at head size 64: a
+//                      tile is requested when its buffer is freed, and a ring of two left the
+//                      products waiting for loads); the loop has no division and
 //                      reads the next tile's page id while this tile's boxes are issued;
 //   warp 1 (one lane)  issues S = Q . K^T (8 x tcgen05.mma of K = 16) into one of two score buffers in
 //                      tensor memory — the scores of the next tile are computed while the softmax of
@@ -41,8 +43,11 @@
 template <int HD> struct AtSmem {
     static constexpr int HV = HD / 64;
     static constexpr int tile = HV * AT_HALF_BYTES;
-    // [alignment slack | 1 KB: barriers | Q | K x 2 | V x 2]
-    static constexpr int q_off = 1024, k_off = q_off + tile, v_off = k_off + 2 * tile, end = v_off + 2 * tile;
+    // [alignment slack | 1 KB: barriers | Q | K x NST | V x NST]
+    // rings of NST key tiles and NST value tiles: as deep as 227 KB allow (3 at head size 128), because a
+    // tile is requested when its buffer is freed and a ring of two leaves the products waiting for loads
+    static constexpr int NST = HD >= 128 ? 3 : 4;
+    static constexpr int q_off = 1024, k_off = q_off + tile, v_off = k_off + NST * tile, end = v_off + NST * tile;
     static constexpr int bytes = 1024 + end;
 };
 
@@ -112,11 +117,12 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     extern __shared__ unsigned char at_raw[];
     unsigned char* sm = reinterpret_cast<unsigned char*>(((size_t)at_raw + 1023) & ~(size_t)1023);
     unsigned long long* q_full = reinterpret_cast<unsigned long long*>(sm);
-    unsigned long long* k_full = q_full + 1;       // [2] stages
-    unsigned long long* k_empty = k_full + 2;      // [2]
-    unsigned long long* v_full = k_empty + 2;      // [2]
-    unsigned long long* v_empty = v_full + 2;      // [2]
-    unsigned long long* s_full = v_empty + 2;      // [2] score buffers
+    constexpr int NST = AtSmem<HD>::NST;           // stages of the key ring and of the value ring
+    unsigned long long* k_full = q_full + 1;       // [NST]
+    unsigned long long* k_empty = k_full + NST;
+    unsigned long long* v_full = k_empty + NST;
+    unsigned long long* v_empty = v_full + NST;
+    unsigned long long* s_full = v_empty + NST;    // [2] score buffers
     unsigned long long* p_ready = s_full + 2;
     unsigned long long* o_done = p_ready + 1;
     unsigned long long* v_fixed = o_done + 1;
@@ -142,13 +148,14 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
     if (tid == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < NST; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&k_empty[s], 1);
             mbar_init(&v_full[s], 1);
             mbar_init(&v_empty[s], 1);
-            mbar_init(&s_full[s], 1);
         }
+        mbar_init(&s_full[0], 1);
+        mbar_init(&s_full[1], 1);
         mbar_init(p_ready, 4);      // one arrival per softmax warp
         mbar_init(o_done, 1);
         mbar_init(v_fixed, 1);
@@ -183,7 +190,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         int page = page_of(0);
         bool ok = true;
         for (int j = 0; j < n_kt && ok; ++j) {
-            const int st = j & 1;
+            const int st = j % NST;
             const int page_next = j + 1 < n_kt ? page_of(j + 1) : -1;
             const int n_pages = min(ppt, ((p_last - j * AT_N) >> lp) + 1);      // pages of this tile that hold keys
             const bool have = lane < n_pages;
@@ -195,7 +202,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 unsigned long long* full = kv ? &v_full[st] : &k_full[st];
                 unsigned long long* empty = kv ? &v_empty[st] : &k_empty[st];
                 if (lane == 0) {
-                    ok = mbar_wait(empty, ((j >> 1) & 1) ^ 1, abort_flag, err);
+                    ok = mbar_wait(empty, ((j / NST) & 1) ^ 1, abort_flag, err);
                     if (ok) mbar_expect_tx(full, (unsigned)n_pages * (unsigned)P * (unsigned)(HD * 2));
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -210,11 +217,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         __syncwarp();
         // the last tile: zero the value rows of keys past the sequence's end (whole warp)
         {
-            const int j = n_kt - 1, st = j & 1;
+            const int j = n_kt - 1, st = j % NST;
             const int first_bad = p_last + 1 - j * AT_N;       // rows [first_bad, 128) are not keys
             bool ok2 = true;
             if (first_bad < AT_N) {
-                if (lane == 0) ok2 = mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, err);
+                if (lane == 0) ok2 = mbar_wait(&v_full[st], (j / NST) & 1, abort_flag, err);
                 ok2 = __shfl_sync(0xffffffffu, ok2 ? 1 : 0, 0) != 0;
                 if (ok2) {
                     unsigned char* vd = v_s + st * TILE;
@@ -235,14 +242,14 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             const unsigned idesc_s = umma_idesc(AT_N), idesc_o = umma_idesc(HD, true);
             // S(j) = Q . K(j)^T over the head size into score buffer j & 1: steps of 16
             auto issue_scores = [&](int j) {
-                unsigned char* kd = k_s + (j & 1) * TILE;
+                unsigned char* kd = k_s + (j % NST) * TILE;
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks) {
                     const unsigned long long da = umma_desc(q_s + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
                     const unsigned long long db = umma_desc(kd + (ks >> 2) * 1024, GROUP) + 2 * (ks & 3);
                     umma(tmem_base + (unsigned)((j & 1) * AT_N), da, db, idesc_s, ks > 0 ? 1u : 0u);
                 }
-                umma_commit(&k_empty[j & 1]);
+                umma_commit(&k_empty[j % NST]);
                 umma_commit(&s_full[j & 1]);
             };
             bool ok = mbar_wait(q_full, 0, abort_flag, err);
@@ -252,18 +259,18 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 issue_scores(0);
             }
             for (int j = 0; j < n_kt && ok; ++j) {
-                const int st = j & 1;
+                const int st = j % NST;
                 if (j + 1 < n_kt) {
                     // the next tile's scores, while this tile's softmax runs.  They go over the P of tile
                     // j - 1, which the P . V issued before them has read: the tensor pipe runs what one thread
                     // issues in order.
-                    ok = mbar_wait(&k_full[st ^ 1], ((j + 1) >> 1) & 1, abort_flag, err);
+                    ok = mbar_wait(&k_full[(j + 1) % NST], ((j + 1) / NST) & 1, abort_flag, err);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                     issue_scores(j + 1);
                 }
                 ok = mbar_wait(p_ready, j & 1, abort_flag, err);
-                if (ok) ok = mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, err);
+                if (ok) ok = mbar_wait(&v_full[st], (j / NST) & 1, abort_flag, err);
                 if (ok && j == n_kt - 1) ok = mbar_wait(v_fixed, 0, abort_flag, err);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -273,7 +280,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const unsigned long long db = umma_desc_mn(vd + ks * 2 * GROUP, 1024, GROUP);
-                    umma_a_tmem(tmem_base + 256u, tmem_base + (unsigned)(st * AT_N + ks * 8), db, idesc_o,
+                    umma_a_tmem(tmem_base + 256u, tmem_base + (unsigned)((j & 1) * AT_N + ks * 8), db, idesc_o,
                                 (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 umma_commit(&v_empty[st]);
@@ -403,7 +410,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     if (*abort_flag && tid == 0) {      // give copies in flight a bounded time to land
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < NST; ++s) {
             for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(&k_full[s], 0) && !mbar_try_wait(&k_full[s], 1); ++i) {}
             for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(&v_full[s], 0) && !mbar_try_wait(&v_full[s], 1); ++i) {}
         }

@@ -24,9 +24,16 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
                  : "=r"(ok) : "r"(tc_smem(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                 : "=r"(ok) : "r"(tc_smem(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Bounded wait.  Returns false when it gave up or when another role has aborted.
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag,
                                           unsigned* err) {
+    if (mbar_test_wait(bar, parity)) return true;       // the phase is often over already: no blocking wait then
     for (unsigned i = 0; i < TC_WAIT_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 1023u) == 1023u && *abort_flag) return false;

@@ -9,7 +9,8 @@
 //                      128-byte-swizzled atoms, the two halves of a group side by side), a ring of
 //                      three buffers for keys and one of three for values (four at head size 64: a
 //                      tile is requested when its buffer is freed, and a ring of two left the
-//                      products waiting for loads); the loop has no division and
+//                      products waiting for loads), one mbarrier per stage counting the bytes of both;
+//                      the loop has no division and
 //                      reads the next tile's page id while this tile's boxes are issued;
 //   warp 1 (one lane)  issues S = Q . K^T (8 x tcgen05.mma of K = 16) into one of two score buffers in
 //                      tensor memory — the scores of the next tile are computed while the softmax of
@@ -118,10 +119,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     unsigned char* sm = reinterpret_cast<unsigned char*>(((size_t)at_raw + 1023) & ~(size_t)1023);
     unsigned long long* q_full = reinterpret_cast<unsigned long long*>(sm);
     constexpr int NST = AtSmem<HD>::NST;           // stages of the key ring and of the value ring
-    unsigned long long* k_full = q_full + 1;       // [NST]
-    unsigned long long* k_empty = k_full + NST;
-    unsigned long long* v_full = k_empty + NST;
-    unsigned long long* v_empty = v_full + NST;
+    unsigned long long* kv_full = q_full + 1;      // [NST] keys and values of a tile have landed
+    unsigned long long* k_empty = kv_full + NST;   // [NST] the scores have read the keys
+    unsigned long long* v_empty = k_empty + NST;   // [NST] P . V has read the values
     unsigned long long* s_full = v_empty + NST;    // [2] score buffers
     unsigned long long* p_ready = s_full + 2;
     unsigned long long* o_done = p_ready + 1;
@@ -149,9 +149,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     if (tid == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < NST; ++s) {
-            mbar_init(&k_full[s], 1);
+            mbar_init(&kv_full[s], 1);
             mbar_init(&k_empty[s], 1);
-            mbar_init(&v_full[s], 1);
             mbar_init(&v_empty[s], 1);
         }
         mbar_init(&s_full[0], 1);
@@ -198,20 +197,19 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             if (have && !valid) atomicOr(err, AIE_DEV_PAGE_OOB);
             // a missing page is flagged; page 0 stands in for it so that the byte count of the barrier holds
             const int group0 = (((valid ? page : 0) * K + kvh) << lp) >> 3;     // first group of 8 rows of the page
-            for (int kv = 0; kv < 2 && ok; ++kv) {      // keys first: the scores need them sooner
-                unsigned long long* full = kv ? &v_full[st] : &k_full[st];
-                unsigned long long* empty = kv ? &v_empty[st] : &k_empty[st];
-                if (lane == 0) {
-                    ok = mbar_wait(empty, ((j / NST) & 1) ^ 1, abort_flag, err);
-                    if (ok) mbar_expect_tx(full, (unsigned)n_pages * (unsigned)P * (unsigned)(HD * 2));
-                }
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (!ok) break;
-                if (have)
-                    tma_load_4d((kv ? v_s : k_s) + st * TILE + lane * P * (HD * 2), kv ? &map_v : &map_k, full,
-                                0, 0, 0, group0);
-                __syncwarp();
+            // one barrier counts the bytes of the tile's keys and values: the products wait once per tile
+            if (lane == 0) {
+                const unsigned ph = ((j / NST) & 1) ^ 1;
+                ok = mbar_wait(&k_empty[st], ph, abort_flag, err) && mbar_wait(&v_empty[st], ph, abort_flag, err);
+                if (ok) mbar_expect_tx(&kv_full[st], 2u * (unsigned)n_pages * (unsigned)P * (unsigned)(HD * 2));
             }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            if (have) {
+                tma_load_4d(k_s + st * TILE + lane * P * (HD * 2), &map_k, &kv_full[st], 0, 0, 0, group0);
+                tma_load_4d(v_s + st * TILE + lane * P * (HD * 2), &map_v, &kv_full[st], 0, 0, 0, group0);
+            }
+            __syncwarp();
             page = page_next;
         }
         __syncwarp();
@@ -221,7 +219,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             const int first_bad = p_last + 1 - j * AT_N;       // rows [first_bad, 128) are not keys
             bool ok2 = true;
             if (first_bad < AT_N) {
-                if (lane == 0) ok2 = mbar_wait(&v_full[st], (j / NST) & 1, abort_flag, err);
+                if (lane == 0) ok2 = mbar_wait(&kv_full[st], (j / NST) & 1, abort_flag, err);
                 ok2 = __shfl_sync(0xffffffffu, ok2 ? 1 : 0, 0) != 0;
                 if (ok2) {
                     unsigned char* vd = v_s + st * TILE;
@@ -240,51 +238,54 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     } else if (warp == 1) {
         if (lane == 0) {
             const unsigned idesc_s = umma_idesc(AT_N), idesc_o = umma_idesc(HD, true);
-            // S(j) = Q . K(j)^T over the head size into score buffer j & 1: steps of 16
-            auto issue_scores = [&](int j) {
-                unsigned char* kd = k_s + (j % NST) * TILE;
+            // descriptors of the first step of each operand, built once; a step or a stage further along is an
+            // addition to the descriptor's address field (bytes / 16)
+            const unsigned long long dq0 = umma_desc(q_s), dk0 = umma_desc(k_s, GROUP), dv0 = umma_desc_mn(v_s, 1024, GROUP);
+            // S(j) = Q . K(j)^T over the head size into score buffer j & 1: steps of 16; keys from stage `st`
+            auto issue_scores = [&](int j, int st) {
+                const unsigned long long dk = dk0 + (unsigned long long)((st * TILE) >> 4);
+                const unsigned ts = tmem_base + (unsigned)((j & 1) * AT_N);
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {
-                    const unsigned long long da = umma_desc(q_s + (ks >> 2) * AT_HALF_BYTES) + 2 * (ks & 3);
-                    const unsigned long long db = umma_desc(kd + (ks >> 2) * 1024, GROUP) + 2 * (ks & 3);
-                    umma(tmem_base + (unsigned)((j & 1) * AT_N), da, db, idesc_s, ks > 0 ? 1u : 0u);
-                }
-                umma_commit(&k_empty[j % NST]);
+                for (int ks = 0; ks < HD / 16; ++ks)
+                    umma(ts, dq0 + (unsigned long long)((((ks >> 2) * AT_HALF_BYTES) >> 4) + 2 * (ks & 3)),
+                         dk + (unsigned long long)((((ks >> 2) * 1024) >> 4) + 2 * (ks & 3)), idesc_s, ks > 0 ? 1u : 0u);
+                umma_commit(&k_empty[st]);
                 umma_commit(&s_full[j & 1]);
             };
             bool ok = mbar_wait(q_full, 0, abort_flag, err);
-            if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag, err);
+            if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag, err);
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                issue_scores(0);
+                issue_scores(0, 0);
             }
+            int st = 0, ph = 0;             // stage and phase of tile j in the rings
             for (int j = 0; j < n_kt && ok; ++j) {
-                const int st = j % NST;
+                const int st1 = st + 1 == NST ? 0 : st + 1, ph1 = st + 1 == NST ? ph ^ 1 : ph;      // of tile j + 1
                 if (j + 1 < n_kt) {
                     // the next tile's scores, while this tile's softmax runs.  They go over the P of tile
                     // j - 1, which the P . V issued before them has read: the tensor pipe runs what one thread
                     // issues in order.
-                    ok = mbar_wait(&k_full[(j + 1) % NST], ((j + 1) / NST) & 1, abort_flag, err);
+                    ok = mbar_wait(&kv_full[st1], ph1, abort_flag, err);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    issue_scores(j + 1);
+                    issue_scores(j + 1, st1);
                 }
-                ok = mbar_wait(p_ready, j & 1, abort_flag, err);
-                if (ok) ok = mbar_wait(&v_full[st], (j / NST) & 1, abort_flag, err);
+                ok = mbar_wait(p_ready, j & 1, abort_flag, err);      // (the tile's values landed with its keys)
                 if (ok && j == n_kt - 1) ok = mbar_wait(v_fixed, 0, abort_flag, err);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 // O += P . V over 128 keys: 8 steps of 16 keys; P is in tensor memory (two keys to a column),
                 // V is MN-major: 16 keys = two groups of 8 rows, the halves of the head 1 KB apart
-                unsigned char* vd = v_s + st * TILE;
+                const unsigned long long dv = dv0 + (unsigned long long)((st * TILE) >> 4);
+                const unsigned tp = tmem_base + (unsigned)((j & 1) * AT_N);
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const unsigned long long db = umma_desc_mn(vd + ks * 2 * GROUP, 1024, GROUP);
-                    umma_a_tmem(tmem_base + 256u, tmem_base + (unsigned)((j & 1) * AT_N + ks * 8), db, idesc_o,
-                                (j > 0 || ks > 0) ? 1u : 0u);
-                }
+                for (int ks = 0; ks < 8; ++ks)
+                    umma_a_tmem(tmem_base + 256u, tp + (unsigned)(ks * 8), dv + (unsigned long long)((ks * 2 * GROUP) >> 4),
+                                idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
                 umma_commit(&v_empty[st]);
                 umma_commit(o_done);
+                st = st1;
+                ph = ph1;
             }
         }
     } else {
@@ -411,8 +412,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     __syncthreads();
     if (*abort_flag && tid == 0) {      // give copies in flight a bounded time to land
         for (int s = 0; s < NST; ++s) {
-            for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(&k_full[s], 0) && !mbar_try_wait(&k_full[s], 1); ++i) {}
-            for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(&v_full[s], 0) && !mbar_try_wait(&v_full[s], 1); ++i) {}
+            for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(&kv_full[s], 0) && !mbar_try_wait(&kv_full[s], 1); ++i) {}
         }
     }
     __syncthreads();

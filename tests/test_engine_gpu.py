@@ -171,6 +171,44 @@ def test_running_a_step_ahead_changes_no_token(tmp_path, dtype):
         assert outs[True, 64] == outs[False, 64] and outs[True, 8] == outs[False, 8]
 
 
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_random_workloads_step_ahead_against_step_by_step(tmp_path, seed):
+    """Random prompts, lengths, sampling options, EOS sets, token budgets and pool sizes (float32, where the
+    two loops must agree token for token): the engine a step ahead of the device against the engine that reads
+    every token first; all pages come back."""
+    import ai_engine_b200 as aie
+
+    rng = np.random.RandomState(seed)
+    d = make_model_dir(tmp_path, "B")
+    n = int(rng.randint(3, 9))
+    prompts = [random_ids(int(rng.randint(1, 90)), 384, 1000 * seed + i) for i in range(n)]
+    cfgp = os.path.join(d, "config.json")
+    raw = json.load(open(cfgp))
+    raw["eos_token_id"] = [int(t) for t in rng.randint(0, 384, size=40)]      # a tenth of the vocabulary ends a request
+    json.dump(raw, open(cfgp, "w"))
+    params = []
+    for i in range(n):
+        kind = rng.randint(0, 3)
+        params.append(aie.SamplingParams(max_tokens=int(rng.randint(1, 40)), ignore_eos=bool(rng.randint(0, 4) == 0),
+                                         temperature=[0.0, 0.7, 1.3][kind], seed=int(rng.randint(0, 1000)),
+                                         top_k=[None, None, 20][int(rng.randint(0, 3))], top_p=[None, 0.9][int(rng.randint(0, 2))]))
+    page = TINY["B"][1]["block_size"]
+    need = max((len(p) + sp.max_tokens + page - 1) // page for p, sp in zip(prompts, params))
+    opts = dict(kv_cache_blocks=int(need + rng.randint(0, 6)), max_num_batched_tokens=int(rng.choice([16, 32, 64])),
+                max_num_seqs=int(rng.randint(2, 5)))
+    outs = []
+    for ahead in (False, True):
+        eng = engine(d, "B", "fp32", async_scheduling=ahead, **opts)
+        outs.append(eng.generate(prompts, params))
+        st = eng.stats()
+        assert st["running"] == 0 and st["waiting"] == 0 and not eng._inflight
+        assert all(g["in_use"] == 0 for g in st["cache"].values())
+    assert outs[0] == outs[1]
+    eos = set(raw["eos_token_id"])
+    for o, sp in zip(outs[0], params):
+        assert len(o) <= sp.max_tokens and (sp.ignore_eos or not (set(o) & eos))
+
+
 def test_long_decoding_and_first_tokens(tmp_path):
     """300 tokens decoded one by one after a 3-token prompt: logits of the first tokens and
     of every decoded position against the plain implementation run on the final sequence."""

@@ -12,6 +12,11 @@ tokens in and out, `prefill` = one 2,048-token prompt in one step, `roofline` = 
 bytes a decode step has to read (every weight once + the live requests' cache)
 over its time against the measured copy bandwidth, `points` = decode at batch 1
 and 64.
+
+Parts alone (one line each, for profiles): `--only decode|prefill` (with `--layers`,
+`--batch`), `--only gemm` (each projection at `--batch` tokens: library product and
+the tcgen05 kernel), `--only attention` (the prompt-attention kernels).  The other
+configurations of the baseline through Engine.generate(): `--workload serving1b|long3b`.
 """
 import argparse
 import json

@@ -15,7 +15,8 @@ and 64.
 
 Parts alone (one line each, for profiles): `--only decode|prefill` (with `--layers`,
 `--batch`), `--only gemm` (each projection at `--batch` tokens: library product and
-the tcgen05 kernel), `--only attention` (the prompt-attention kernels).  The other
+the tcgen05 kernel), `--only attention` (the prompt-attention kernels), `--only peaks`
+(a device copy and a library bf16 product on this box).  The other
 configurations of the baseline through Engine.generate(): `--workload serving1b|long3b`.
 """
 import argparse
@@ -243,6 +244,48 @@ def time_gemms(torch, tokens):
     return out
 
 
+def time_peaks(torch):
+    """What this box does on a plain device copy (read + write bytes over time) and on a library bf16 product:
+    the two figures the roofline fractions are taken against, measured here for context (the fractions in
+    the JSON line use MEASURED_PEAKS.json when the driver wrote it, else the stated fallback)."""
+    out = {}
+    n = 1 << 30
+    a = torch.empty(n, dtype=torch.uint8, device="cuda")
+    b = torch.empty_like(a)
+    ts = []
+    for i in range(8):
+        s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s_.record()
+        b.copy_(a)
+        e_.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            ts.append(s_.elapsed_time(e_))
+    out["copy_gb_s"] = round(2 * n / (sorted(ts)[len(ts) // 2] * 1e-3) / 1e9, 1)
+    del a, b
+    m = 8192
+    x = torch.randn(m, m, device="cuda").bfloat16()
+    w = torch.randn(m, m, device="cuda").bfloat16()
+    ts = []
+    for i in range(8):
+        s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s_.record()
+        torch.mm(x, w.t())
+        e_.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            ts.append(s_.elapsed_time(e_))
+    out["bf16_tflops_burst"] = round(2.0 * m ** 3 / (sorted(ts)[len(ts) // 2] * 1e-3) / 1e12, 1)
+    s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s_.record()
+    for _ in range(1500):
+        torch.mm(x, w.t())
+    e_.record()
+    torch.cuda.synchronize()
+    out["bf16_tflops_sustained"] = round(1500 * 2.0 * m ** 3 / (s_.elapsed_time(e_) * 1e-3) / 1e12, 1)
+    return out
+
+
 def time_attention(torch, tokens, context):
     """The attention kernels for a portion of `tokens` prompt tokens after `context` cached ones, alone, at the
     flagship head layout (32 heads on 8 kv heads of 128, pages of 16): the tcgen05 kernel and the mma.sync
@@ -340,7 +383,7 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--workload", choices=["serving1b", "long3b"], default=None,
                     help="run one of the serving workloads through Engine.generate() and print its numbers")
-    ap.add_argument("--only", choices=["decode", "prefill", "gemm", "attention"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "gemm", "attention", "peaks"], default=None,
                     help="time one part only and print its numbers (for profiling)")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -364,6 +407,12 @@ def main():
     if a.only == "gemm":
         for k, v in time_gemms(torch, a.batch).items():
             print(k, json.dumps(v))
+        return 0
+    if a.only == "peaks":
+        with ClockSampler() as clocks:
+            r = time_peaks(torch)
+        r["clocks"] = clocks.summary()
+        print(json.dumps({"only": "peaks", **r}))
         return 0
     if a.only == "attention":
         for tokens, context in ((PREFILL_TOKENS, 0), (PREFILL_TOKENS, 6144), (512, 0), (200, 1000)):

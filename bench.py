@@ -371,6 +371,17 @@ def run_workload(torch, aie, name):
             "preemptions": st["preemptions"], "mean_batch_tokens": round(st["batch_tokens"] / max(st["steps"], 1), 1)}
 
 
+def config_record(layers, batch, peaks_source):
+    """Every size of the run, flat (what is deeper than one level is lost in the record)."""
+    c = LLAMA3_8B
+    return {"model": "Llama-3-8B shape", "layers": layers, "layers_of_config": c["num_hidden_layers"],
+            "hidden": c["hidden_size"], "heads": c["num_attention_heads"], "kv_heads": c["num_key_value_heads"],
+            "head_dim": c["head_dim"], "intermediate": c["intermediate_size"], "vocab": c["vocab_size"],
+            "global_batch": batch, "seq_len": PROMPT_LEN, "context": CONTEXT, "kv_page": PAGE,
+            "parallelism": "single GPU", "l2": "inputs larger than L2 (weights read every step)",
+            "peaks": peaks_source}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -447,12 +458,7 @@ def main():
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0, 0.02), uniform random token ids",
         "impl": "ours",
-        "config": {"model": "Llama-3-8B shape", "layers": a.layers, "layers_of_config": 32,
-                   "hidden": 4096, "heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 14336,
-                   "vocab": 128256, "global_batch": a.batch, "seq_len": PROMPT_LEN, "context": CONTEXT,
-                   "kv_page": PAGE, "parallelism": "single GPU",
-                   "l2": "inputs larger than L2 (weights read every step)",
-                   "peaks": pk["source"]},
+        "config": config_record(a.layers, a.batch, pk["source"]),
         "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": main_pt["launches"],
         "prefill": {"value": round(prefill["value"], 1), "tokens": prefill["tokens"],

@@ -420,6 +420,19 @@ def test_rope_kv_write(dtype, H, K, d, P, rot, many):
     assert torch.equal(q2, q) and bool(((s["k_pages"] == k2) | torch.isnan(k2)).all())
 
 
+def test_take_sampled_ids_hands_tokens_over_on_the_device():
+    """ids[t] = last[src[t]] where src[t] >= 0; the others stay; a source row outside `last` is flagged."""
+    last = torch.tensor([11, 22, 33, 44], device=DEV, dtype=torch.int32)
+    ids = torch.tensor([5, 0, 7, 0, 9, 0], device=DEV, dtype=torch.int32)
+    src = torch.tensor([-1, 2, -1, 0, -1, 3], device=DEV, dtype=torch.int32)
+    e = err_word()
+    ops().take_sampled_ids(ids, src, last, e)
+    assert ids.tolist() == [5, 33, 7, 11, 9, 44] and int(e.item()) == 0
+    ops().take_sampled_ids(ids, torch.tensor([4, -1, -1, -1, -1, -1], device=DEV, dtype=torch.int32), last, e)
+    torch.cuda.synchronize()
+    assert int(e.item()) & 1 and ids.tolist() == [5, 33, 7, 11, 9, 44]
+
+
 def test_sampling_kernel_against_the_plain_sampler():
     from ai_engine_b200.sampling.sampler import sample_rows
 

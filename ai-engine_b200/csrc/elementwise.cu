@@ -241,18 +241,19 @@ __global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ a, int
 }
 
 // Eight outputs per thread with 16-byte accesses (bfloat16) when F and the group size are
-// multiples of 8; the same arithmetic as the scalar kernel.
+// multiples of 8.
 __global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ a, int F, int block,
                                      size_t total8) {
     pdl_launch_dependents();
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    const int F8 = F / 8;
+    const unsigned F8 = (unsigned)(F / 8);
     for (; i < total8; i += stride) {
-        const size_t t = i / F8, f = (i % F8) * 8;
-        const size_t gc = block ? (f / block) * 2 * block + f % block : f;
-        const size_t uc = block ? gc + block : F + f;
+        const size_t t = i / F8;
+        const unsigned f = (unsigned)(i - t * F8) * 8u;
+        const unsigned gc = block ? (f / (unsigned)block) * 2u * (unsigned)block + f % (unsigned)block : f;
+        const unsigned uc = block ? gc + (unsigned)block : (unsigned)F + f;
         const uint4 gr = *reinterpret_cast<const uint4*>(gu + t * 2 * F + gc);
         const uint4 ur = *reinterpret_cast<const uint4*>(gu + t * 2 * F + uc);
         const bf16* ge = reinterpret_cast<const bf16*>(&gr);
@@ -261,9 +262,13 @@ __global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restri
         bf16* oe = reinterpret_cast<bf16*>(&o);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
+            // sigmoid by ex2.approx and rcp.approx (relative error about 1e-6, far below the bf16 rounding of
+            // the result): with expf and a division the kernel was bound by instruction issue, not by memory
             const float g = __bfloat162float(ge[j]), u = __bfloat162float(ue[j]);
-            const float sv = g * (1.0f / (1.0f + expf(-g)));
-            oe[j] = __float2bfloat16_rn(sv * u);
+            float e, r;
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+            oe[j] = __float2bfloat16_rn((g * r) * u);
         }
         *reinterpret_cast<uint4*>(a + t * F + f) = o;
     }

@@ -161,9 +161,15 @@ extern "C" int aie_rope_kv_write(const void* qkv, int in_dtype, int parts, long 
     if (rot_dim % 2 || rot_dim > d || rot_dim < 0) return AIE_BAD_ARG;
     if (T >= 64 && dtype == AIE_BF16 && in_dtype == AIE_BF16 && parts == 1 && rot_dim % 16 == 0 && d % 8 == 0 &&
         !((size_t)qkv & 15) && !((size_t)q_out & 15) && !((size_t)k_pages & 15) && !((size_t)v_pages & 15))
-        return (int)launch_pdl(rope_kv_write_token_kernel, dim3(T), dim3(256), (size_t)rot_dim * sizeof(float), stream,
+    {
+        // one pass over the token's rotated chunks when they fit a block: (H + K) heads x rot_dim / 16 chunks
+        int threads = ((H + K) * (rot_dim / 16) + 31) / 32 * 32;
+        threads = threads < 64 ? 64 : (threads > 256 ? ((threads + 1) / 2 + 31) / 32 * 32 : threads);
+        if (threads > 256) threads = 256;
+        return (int)launch_pdl(rope_kv_write_token_kernel, dim3(T), dim3(threads), (size_t)rot_dim * sizeof(float), stream,
                                (const bf16*)qkv, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, positions, token_req,
                                block_table, bt_width, num_pages, P, H, K, d, rot_dim, inv_freq, write, err);
+    }
     // few tokens: one warp per block, so that the work spreads over the machine; many: 8 warps
     const int warps = T >= 256 ? 8 : 1;
     if ((H + 2 * K + warps - 1) / warps > 65535) return AIE_UNSUPPORTED;

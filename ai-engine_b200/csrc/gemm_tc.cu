@@ -296,7 +296,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         g += ld_peer(tile_addr + (tt * TC_BM + j) * 4, p);
                         u += ld_peer(tile_addr + (tt * TC_BM + 64 + j) * 4, p);
                     }
-                    out = g * (1.0f / (1.0f + expf(-g))) * u;
+                    // sigmoid by ex2.approx and rcp.approx (relative error about 1e-6; the result is rounded to bf16)
+                    float e, r;
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
+                    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+                    out = (g * r) * u;
                 }
                 if (f0 + j < width) tc_store<OT>(C + (size_t)(t0 + tt) * ldc + f0 + j, out);
             }

@@ -225,6 +225,58 @@ sample_rows_kernel(const float* __restrict__ logits, int V, int ld,
     if (tid == 0) out[r] = idx < 0 || idx >= V ? 0 : idx;
 }
 
+// Greedy alone, a row spread over `gridDim.y` blocks: each block packs its best (value, first index) as
+// (order bits << 32 | ~index), so that an atomic maximum keeps the largest value and, among equals, the
+// lowest index; the block that finishes last for a row writes the id and leaves the scratch zeroed.
+// One block per row reads 513 KB of logits through one SM: 16 us at a vocabulary of 128K.
+__global__ void __launch_bounds__(256)
+argmax_rows_kernel(const float* __restrict__ logits, int V, int ld, u64* __restrict__ best,
+                   int* __restrict__ tickets, int* __restrict__ out) {
+    __shared__ u64 wbest[8];
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const float* row = logits + (size_t)r * ld;
+    const int per = (V + gridDim.y - 1) / gridDim.y;
+    const int lo = blockIdx.y * per, hi = min(V, lo + per);
+    u64 b = 0;
+    for (int i = lo + tid; i < hi; i += 256) {
+        const float v = row[i];
+        if (v == v) {       // a NaN is never the maximum
+            const u64 k = ((u64)order_key(v) << 32) | (u64)(0xFFFFFFFFu - (unsigned)i);
+            b = k > b ? k : b;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const u64 ob = __shfl_xor_sync(0xffffffffu, b, o);
+        b = ob > b ? ob : b;
+    }
+    if ((tid & 31) == 0) wbest[tid >> 5] = b;
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < 8; ++w) b = wbest[w] > b ? wbest[w] : b;
+        if (b) atomicMax(&best[r], b);
+        __threadfence();
+        if (atomicAdd(&tickets[r], 1) == (int)gridDim.y - 1) {
+            __threadfence();
+            const u64 w = atomicExch(&best[r], 0ull);
+            out[r] = w ? (int)(0xFFFFFFFFu - (unsigned)(w & 0xFFFFFFFFull)) : 0;
+            tickets[r] = 0;
+        }
+    }
+}
+
+// out[r] = index of the first maximum of row r.  best [N] (64-bit) and tickets [N] must be zero on entry and
+// are zero again on return.
+extern "C" int aie_argmax_rows(const float* logits, int N, int V, int ld, void* best, int* tickets, int* out,
+                               cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (V <= 0) return AIE_BAD_ARG;
+    int chunks = (V + 8191) / 8192;         // at least 8K logits a block
+    if (chunks > 32) chunks = 32;
+    argmax_rows_kernel<<<dim3(N, chunks), 256, 0, stream>>>(logits, V, ld, (u64*)best, tickets, out);
+    AIE_LAUNCH_CHECK();
+}
+
 extern "C" int aie_sample_rows(const float* logits, int N, int V, int ld, const float* temperature,
                                const int* top_k, const float* top_p, const float* uniform, int* out,
                                cudaStream_t stream) {

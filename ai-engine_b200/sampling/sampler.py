@@ -29,24 +29,36 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Te
     return out
 
 
+def argmax_rows(logits: torch.Tensor, scratch) -> torch.Tensor:
+    """Greedy for every row: int32 [N], the first maximum.  scratch: (int64 [>= N], int32 [>= N]) zeroed
+    device tensors that the kernel leaves zeroed (a row is spread over several blocks)."""
+    _dev(*scratch)
+    if logits.dtype != torch.float32 or not logits.is_cuda or logits.dim() != 2 or logits.stride(1) != 1:
+        raise ValueError("sampling reads float32 logits [N, V] on the device, rows contiguous")
+    N, V = logits.shape
+    out = torch.empty(N, dtype=torch.int32, device=logits.device)
+    lib = library("sampling.cu")
+    check(lib.aie_argmax_rows(_p(logits), c_int(N), c_int(V), c_int(logits.stride(0)), _p(scratch[0]), _p(scratch[1]),
+                              _p(out), _stream()), "argmax_rows")
+    return out
+
+
 class Sampler:
     """Packs per-request options for a step and launches the kernel."""
 
     def __init__(self, device):
         self.device = device
-        self._greedy = {}          # n -> device tensors of an all-greedy step (nothing to upload)
+        self._scratch = None       # zeroed scratch of the all-greedy kernel
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                draw_index: Sequence[int]) -> torch.Tensor:
         n = len(params)
         if all(p.temperature == 0 for p in params):
-            g = self._greedy.get(n)
-            if g is None:
-                z = torch.zeros(n, dtype=torch.float32, device=self.device)
-                g = (z, torch.zeros(n, dtype=torch.int32, device=self.device),
-                     torch.ones(n, dtype=torch.float32, device=self.device))
-                self._greedy[n] = g
-            return sample_rows(logits, g[0], g[1], g[2], g[0])
+            if self._scratch is None or self._scratch[0].shape[0] < n:
+                m = max(n, 64)
+                self._scratch = (torch.zeros(m, dtype=torch.int64, device=self.device),
+                                 torch.zeros(m, dtype=torch.int32, device=self.device))
+            return argmax_rows(logits, self._scratch)
         packed = np.zeros((4, n), dtype=np.float32)
         for i, (p, k) in enumerate(zip(params, draw_index)):
             packed[0, i] = p.temperature

@@ -96,7 +96,7 @@ def time_decode(torch, aie, model, batch, prompt_len, steps, warmup, ctx_cap):
     from ai_engine_b200.cache import PagedCache
     from ai_engine_b200.engine.step import StepEntry, StepRunner
     from ai_engine_b200.kernels.loader import LAUNCHES
-    from ai_engine_b200.sampling.sampler import sample_rows
+    from ai_engine_b200.sampling.sampler import Sampler
 
     total = prompt_len + warmup + steps + 1
     pages = batch * ((total + PAGE - 1) // PAGE) + 4
@@ -112,15 +112,14 @@ def time_decode(torch, aie, model, batch, prompt_len, steps, warmup, ctx_cap):
         for a in range(0, prompt_len, 2048):
             runner.step([StepEntry(s, a, ids[a:a + 2048], [])])
     runner.check_errors()
-    zeros = torch.zeros(batch, device=model.device)
-    zk = torch.zeros(batch, dtype=torch.int32, device=model.device)
-    ones = torch.ones(batch, device=model.device)
+    sampler = Sampler(model.device)
+    greedy = [aie.SamplingParams(max_tokens=1, temperature=0.0)] * batch
     tokens = torch.randint(0, vocab, (batch,), generator=g).tolist()
 
     def one(i):
         nonlocal tokens
         logits = runner.step([StepEntry(s, prompt_len + i, [tokens[j]], [0]) for j, s in enumerate(slots)])
-        return sample_rows(logits, zeros, zk, ones, zeros)
+        return sampler.sample(logits, greedy, [0] * batch)
 
     for i in range(warmup):
         out = one(i)

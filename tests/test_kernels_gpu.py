@@ -433,6 +433,32 @@ def test_take_sampled_ids_hands_tokens_over_on_the_device():
     assert int(e.item()) & 1 and ids.tolist() == [5, 33, 7, 11, 9, 44]
 
 
+@pytest.mark.parametrize("N,V", [(1, 7), (8, 128256), (64, 1000), (3, 8192 * 5 + 13)])
+def test_greedy_over_several_blocks_takes_the_first_maximum(N, V):
+    from ai_engine_b200.sampling.sampler import argmax_rows
+
+    torch.manual_seed(N + V)
+    base = torch.randn(N, V + 5, device=DEV)
+    logits = base[:, :V]                                   # rows V + 5 apart
+    for r in range(N):                                      # ties at the maximum: the first one wins
+        top = float(logits[r].max()) + 1.0
+        where = torch.randperm(V, device=DEV)[:min(3, V)]
+        logits[r, where] = top
+    if N > 2:
+        logits[1, :] = float("-inf")                        # no finite value: index 0
+        logits[2, 0] = float("nan")                         # a NaN is never chosen
+    scratch = (torch.zeros(64, dtype=torch.int64, device=DEV), torch.zeros(64, dtype=torch.int32, device=DEV))
+    for _ in range(2):                                      # the scratch comes back zeroed
+        got = argmax_rows(logits, scratch).cpu()
+        assert int(scratch[0].abs().sum()) == 0 and int(scratch[1].abs().sum()) == 0
+    want = []
+    for r in range(N):
+        row = logits[r].clone()
+        row[torch.isnan(row)] = float("-inf")
+        want.append(int((row == row.max()).nonzero()[0]))
+    assert got.tolist() == want
+
+
 def test_sampling_kernel_against_the_plain_sampler():
     from ai_engine_b200.sampling.sampler import sample_rows
 

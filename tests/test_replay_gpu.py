@@ -237,3 +237,52 @@ def test_full_size_layers(tmp_path, name):
             err = np.abs(np.concatenate(g) - r).max(axis=1)
             assert err.max() <= tol, (f"{dtype}, request {what}: first wrong token {int(np.argmax(err > tol))}: "
                                       f"{err.max()} (logits up to {scale})")
+
+
+ODD_SIZES = {
+    "width_100_head_16": dict(hidden_size=100, intermediate_size=116, num_attention_heads=5, num_key_value_heads=5,
+                              head_dim=16, vocab_size=257, tie_word_embeddings=False),
+    "head_80_vocab_1001": dict(hidden_size=328, intermediate_size=1000, num_attention_heads=2, num_key_value_heads=1,
+                               head_dim=80, vocab_size=1001, tie_word_embeddings=True),
+    "head_192": dict(hidden_size=576, intermediate_size=136, num_attention_heads=3, num_key_value_heads=3, head_dim=192,
+                     vocab_size=130, tie_word_embeddings=False),
+    "head_256_width_520": dict(hidden_size=520, intermediate_size=264, num_attention_heads=2, num_key_value_heads=2,
+                               head_dim=256, vocab_size=333, tie_word_embeddings=True),
+}
+
+
+@pytest.mark.parametrize("name", sorted(ODD_SIZES))
+def test_sizes_off_the_fast_paths(tmp_path, name):
+    """Widths that are no multiple of 8, head sizes that no tensor-core kernel takes, odd vocabularies, plain
+    multi-head attention: every size either takes a slower kernel or is refused — never a wrong result."""
+    import ai_engine_b200 as aie
+    from ai_engine_b200.engine.replay import Replayer
+
+    raw = dict(architectures=["LlamaForCausalLM"], num_hidden_layers=2, rope_theta=10000.0, rms_norm_eps=1e-5,
+               max_position_embeddings=512, **ODD_SIZES[name])
+    d = os.path.join(str(tmp_path), name)
+    aie.write_random_model(aie.LlamaConfig.from_dict(raw), d, seed=9, dtype="bfloat16", std=0.05)
+    ids = random_ids(90, raw["vocab_size"], 77)
+    ref = plain_logits(d, ids, torch.float32)
+    scale = max(1.0, float(np.abs(ref).max()))
+    for dtype, tol in (("float32", TOL_F32 * scale), ("bfloat16", TOL_BF16 * scale)):
+        rep = Replayer(d, dtype, max_tokens=128, block_size=16)
+        got = [rep.run_step([dict(id="x", tokens=ids[:50], want=list(range(50)))]).numpy()]
+        got.append(rep.run_step([dict(id="x", tokens=ids[50:83], want=list(range(33)))]).numpy())
+        for t in ids[83:]:
+            got.append(rep.run_step([dict(id="x", tokens=[t], want=[0])]).numpy())
+        err = np.abs(np.concatenate(got) - ref).max(axis=1)
+        assert err.max() <= tol, f"{dtype}: first wrong token {int(np.argmax(err > tol))}: {err.max()} (logits up to {scale})"
+
+
+def test_a_head_size_that_no_kernel_takes_is_refused_by_name(tmp_path):
+    import ai_engine_b200 as aie
+    from ai_engine_b200.engine.replay import Replayer
+
+    raw = dict(architectures=["LlamaForCausalLM"], num_hidden_layers=1, rope_theta=10000.0, rms_norm_eps=1e-5,
+               max_position_embeddings=64, hidden_size=100, intermediate_size=116, num_attention_heads=5,
+               num_key_value_heads=5, head_dim=20, vocab_size=257, tie_word_embeddings=False)
+    d = os.path.join(str(tmp_path), "head20")
+    with pytest.raises(ValueError, match="head_dim 20 must be a multiple of 16"):      # already when the parts are built
+        aie.write_random_model(aie.LlamaConfig.from_dict(raw), d, seed=9, dtype="bfloat16")
+        Replayer(d, "bfloat16", max_tokens=64, block_size=16)

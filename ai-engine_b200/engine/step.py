@@ -218,7 +218,7 @@ class StepRunner:
             return self.model.forward(ctx, self.cache)
         buf = ctx.buffers
         if buf.graph is None:
-            if buf.uses < 2:                       # a layout seen once is not worth a capture
+            if buf.uses < 3:                       # a layout seen once or twice is not worth a capture
                 return self.model.forward(ctx, self.cache)
             from ..kernels.loader import LAUNCHES
             self.model.forward(ctx, self.cache)    # warm-up outside the capture (library set-up)

@@ -39,23 +39,47 @@ _ERR_BITS = {1: "a token id outside the vocabulary", 2: "a block table entry out
              4: "a bounded wait in a kernel ran out", 8: "a request row outside its table"}
 
 
-class _Buffers:
-    """Pinned host and device int32 buffers of one layout (one tuple of segment
-    lengths), reused by every step of that layout; a CUDA graph captured on them
-    stays valid because their addresses never change."""
+class _Staging:
+    """A ring of pinned host buffers shared by all layouts: the host may run ahead of the device, so a
+    buffer is rewritten only after the copy that read it has finished.  They grow with the largest step
+    (pinning memory takes about half a millisecond: not once per layout)."""
 
-    def __init__(self, lengths, device):
+    def __init__(self, pinned: bool, depth: int = 4):
+        self.pinned = pinned
+        self.hosts = [None] * depth
+        self.copied = [None] * depth
+        self.turn = 0
+
+    def take(self, n: int):
+        """(index, int32 host view of n elements) of the next buffer, free to be written."""
+        i = self.turn
+        self.turn = (i + 1) % len(self.hosts)
+        if self.copied[i] is not None:
+            self.copied[i].synchronize()
+        h = self.hosts[i]
+        if h is None or h.shape[0] < n:
+            h = torch.zeros(max(1024, 1 << (n - 1).bit_length()), dtype=torch.int32, pin_memory=self.pinned)
+            self.hosts[i] = h
+        return i, h[:n]
+
+    def sent(self, i: int) -> None:
+        if self.pinned:
+            ev = self.copied[i] or torch.cuda.Event()
+            ev.record()
+            self.copied[i] = ev
+
+
+class _Buffers:
+    """The device int32 buffer of one layout (one tuple of segment lengths), reused by every step
+    of that layout; a CUDA graph captured on it stays valid because its address never changes."""
+
+    def __init__(self, lengths, device, staging: Optional[_Staging] = None):
         self.offsets, o = [], 0
         for n in lengths:
             self.offsets.append((o, n))
             o += (n + 3) // 4 * 4
         self.total = max(o, 4)
-        # a ring of pinned staging buffers: the host may run ahead of the device, so a
-        # staging buffer is rewritten only after the copy that read it has finished
-        self.hosts = [torch.zeros(self.total, dtype=torch.int32, pin_memory=device.type == "cuda")
-                      for _ in range(4)]
-        self.copied = [None] * 4
-        self.turn = 0
+        self.staging = staging or _Staging(device.type == "cuda")
         self.dev = torch.zeros(self.total, dtype=torch.int32, device=device)
         self.graph = None          # torch.cuda.CUDAGraph of a decode-only step on these buffers
         self.graph_logits = None
@@ -63,18 +87,12 @@ class _Buffers:
         self.uses = 0
 
     def upload(self, arrays) -> None:
-        i = self.turn
-        self.turn = (i + 1) % len(self.hosts)
-        if self.copied[i] is not None:
-            self.copied[i].synchronize()
-        hv = self.hosts[i].numpy()
+        i, host = self.staging.take(self.total)
+        hv = host.numpy()
         for (o, n), a in zip(self.offsets, arrays):
             hv[o:o + n] = a
-        self.dev.copy_(self.hosts[i], non_blocking=True)
-        if self.dev.is_cuda:
-            ev = self.copied[i] or torch.cuda.Event()
-            ev.record()
-            self.copied[i] = ev
+        self.dev.copy_(host, non_blocking=True)
+        self.staging.sent(i)
 
 
 class StepContext:
@@ -153,10 +171,10 @@ class StepContext:
         self.layout_key = key
         buf = buffers.get(key) if buffers is not None else None
         if buf is None:
-            buf = _Buffers(key[:-1], device)
+            buf = _Buffers(key[:-1], device, buffers.get("staging") if buffers is not None else None)
             if buffers is not None:
                 if len(buffers) >= 128:
-                    buffers.pop(next(iter(buffers)))
+                    buffers.pop(next(k for k in buffers if k != "staging"))
                 buffers[key] = buf
         buf.uses += 1
         self.buffers = buf
@@ -182,7 +200,7 @@ class StepRunner:
         self.device = model.device
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.last_ctx: Optional[StepContext] = None
-        self.buffers: dict = {}
+        self.buffers: dict = {"staging": _Staging(self.device.type == "cuda")}
         if use_graphs is None:
             use_graphs = (model.dtype == torch.bfloat16 and not model.has_host_parts()
                           and not os.environ.get("AI_ENGINE_B200_NO_GRAPHS"))

@@ -209,8 +209,8 @@ class Engine:
         c = self.counters
         c["steps"] += 1
         c["h2d_bytes"] += ctx.h2d_bytes + (16 * len(sampled) if sampled else 0)
-        c["batch_tokens"] += ctx.T
-        c["batch_requests"] += ctx.R
+        c["batch_tokens"] += ctx.real_T
+        c["batch_requests"] += ctx.real_R
         ahead = 1 if (self.options.async_scheduling and self.scheduler.has_work()) else 0
         while len(self._inflight) > ahead:
             self._resolve(self._inflight.popleft(), events)

@@ -205,6 +205,9 @@ class StepRunner:
             use_graphs = (model.dtype == torch.bfloat16 and not model.has_host_parts()
                           and not os.environ.get("AI_ENGINE_B200_NO_GRAPHS"))
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
+        # a mixer with state of its own would update it twice for a repeated entry: no rounding up then
+        requests = model.cache_requests() if hasattr(model, "cache_requests") else []
+        self.pad_decode = not any(st is not None for _, st, _ in requests)
         self.graph_launches = 0        # kernels replayed through graphs (for launch counts)
         self.graphs_captured = 0
         # the ids the last step sampled, left on the device for a next step that starts before the
@@ -227,11 +230,24 @@ class StepRunner:
                                 f"tokens, more than max_seq_len {max_len}")
             decode_only = decode_only and len(e.tokens) == 1
         graphed = self.use_graphs and decode_only
+        n_real, real_rows = len(entries), None
+        if graphed and self.pad_decode and n_real > 8 and n_real % 8:
+            # the number of requests of a decode step is rounded up to a multiple of 8 by repeating the first
+            # entry (the same token at the same place: it writes the same key and value again), so that
+            # batches that shrink and grow request by request share their layouts, and with them their graphs
+            real_rows = sum(len(e.want) for e in entries)
+            e0 = entries[0]
+            entries = list(entries) + [StepEntry(e0.slot, e0.start, e0.tokens, [0], e0.src)] * (8 - n_real % 8)
         ctx = StepContext(entries, self.cache, self.device, self.err, self.buffers, bucket_width=graphed)
+        ctx.real_R, ctx.real_T = n_real, ctx.T - (len(entries) - n_real)
         self.last_ctx = ctx
         if ctx.has_src:
             from ..kernels import ops
             ops.take_sampled_ids(ctx.token_ids, ctx.token_src, self.sampled, self.err)
+        logits = self._run(ctx, graphed)
+        return logits if real_rows is None else logits[:real_rows]
+
+    def _run(self, ctx: StepContext, graphed: bool) -> torch.Tensor:
         if not graphed:
             return self.model.forward(ctx, self.cache)
         buf = ctx.buffers

@@ -298,3 +298,36 @@ def test_decode_steps_replayed_from_a_graph_match_eager_steps(tmp_path):
     assert (outs[True] - outs[False]).abs().max() <= 1e-2
     ref = plain_logits(d, ids[1][:40], torch.float32)
     assert np.abs(outs[True][:, 1].numpy() - ref[20:40]).max() <= TOL_BF16
+
+
+def test_decode_batches_rounded_up_to_a_multiple_of_eight_share_a_graph(tmp_path):
+    """Decode steps of 9 to 16 requests run as 16 rows (the first entry repeated): one layout, one graph, and
+    the logits of the real rows are what the step of exactly those rows gives."""
+    from ai_engine_b200.cache import PagedCache
+    from ai_engine_b200.engine.loading import load_model
+    from ai_engine_b200.engine.step import StepEntry, StepRunner
+
+    d = make_model_dir(tmp_path, "D")
+    model, _ = load_model(d, "bf16")
+    page = TINY["D"][1]["block_size"]
+    outs = {}
+    for graphs in (False, True):
+        cache = PagedCache(model.cache_requests(), page, 64, 16, 256, model.dtype, model.device)
+        runner = StepRunner(model, cache, use_graphs=graphs)
+        slots = [cache.admit() for _ in range(13)]
+        prompts = [random_ids(10 + s, 300, 200 + s) for s in range(13)]
+        for s, p in zip(slots, prompts):
+            assert cache.ensure(s, 40)
+            runner.step([StepEntry(s, 0, p[:10 + s - 6], [])])
+        got = []
+        for k in range(6):            # 13, 12, 11, 13, 10, 9 requests: all within one bucket of 16
+            live = [13, 12, 11, 13, 10, 9][k]
+            es = [StepEntry(s, len(p) - 6 + k, [p[len(p) - 6 + k]], [0]) for s, p in list(zip(slots, prompts))[:live]]
+            lg = runner.step(es)
+            assert lg.shape[0] == live
+            got.append(lg[:9].float().cpu().clone())
+        runner.check_errors()
+        outs[graphs] = torch.stack(got)
+        if graphs:
+            assert runner.graphs_captured == 1 and runner.graph_launches > 0
+    assert (outs[True] - outs[False]).abs().max() <= 1e-2      # other split counts of the attention: rounding only

@@ -263,6 +263,14 @@ class Engine:
         self.runner.check_errors()
         return [self.requests.pop(r).output for r in rids]
 
+    def take(self, request_id: int) -> List[int]:
+        """The generated ids of a finished request, which the engine then forgets (callers that drive
+        `add_request` / `step` themselves call this once a request's `finished` event has come)."""
+        req = self.requests.get(request_id)
+        if req is None or not req.finished:
+            raise KeyError(f"request {request_id} is unknown or still running")
+        return self.requests.pop(request_id).output
+
     def forward_tokens(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """The raw step function (tests, replay): logits at the wanted rows."""
         return self.runner.step(entries)

@@ -209,6 +209,30 @@ def test_random_workloads_step_ahead_against_step_by_step(tmp_path, seed):
         assert len(o) <= sp.max_tokens and (sp.ignore_eos or not (set(o) & eos))
 
 
+def test_stepping_by_hand_and_taking_finished_requests(tmp_path):
+    import ai_engine_b200 as aie
+
+    d = make_model_dir(tmp_path, "A")
+    eng = engine(d, "A", "fp32")
+    want = engine(d, "A", "fp32").generate([random_ids(9, 256, 3), random_ids(30, 256, 4)],
+                                             aie.SamplingParams(max_tokens=7, ignore_eos=True))
+    a = eng.add_request(random_ids(9, 256, 3), aie.SamplingParams(max_tokens=7, ignore_eos=True))
+    b = eng.add_request(random_ids(30, 256, 4), aie.SamplingParams(max_tokens=7, ignore_eos=True))
+    with pytest.raises(KeyError):
+        eng.take(a)
+    streamed = {a: [], b: []}
+    done = set()
+    while eng.has_unfinished() or eng._inflight:
+        for rid, tok, fin in eng.step():
+            if tok is not None:
+                streamed[rid].append(tok)
+            if fin:
+                done.add(rid)
+    assert done == {a, b}
+    assert [eng.take(a), eng.take(b)] == want == [streamed[a], streamed[b]]
+    assert not eng.requests
+
+
 def test_long_decoding_and_first_tokens(tmp_path):
     """300 tokens decoded one by one after a 3-token prompt: logits of the first tokens and
     of every decoded position against the plain implementation run on the final sequence."""

@@ -116,15 +116,20 @@ def _build(target: str, cmd_prefix: List[str], sources: List[str], deps: List[st
 
 
 def cuda_library(source: str, extra_flags: Optional[List[str]] = None) -> str:
-    """Path of the shared library of csrc/<source>, compiled if need be."""
-    src = os.path.join(CSRC, source)
+    """Path of the shared library of csrc/<source>, compiled if need be.  An absolute path names a
+    `.cu` file outside the package (a part defined elsewhere brings its own kernel); it may include
+    the package's headers."""
+    outside = os.path.isabs(source)
+    src = source if outside else os.path.join(CSRC, source)
     flags = NVCC_FLAGS + (extra_flags or [])
-    deps = [src] + _headers(CSRC)
+    deps = [src] + _headers(CSRC) + (_headers(os.path.dirname(src)) if outside else [])
     key = _hash(deps, flags)
-    target = os.path.join(build_dir(), f"lib{os.path.splitext(source)[0]}-{key}.so")
+    stem = os.path.splitext(os.path.basename(source))[0]
+    target = os.path.join(build_dir(), f"lib{stem}-{key}.so")
     if os.path.exists(target):
         return target
-    return _build(target, [find_nvcc()], [src], deps, flags + ["-I", CSRC], f"csrc/{source}")
+    return _build(target, [find_nvcc()], [src], deps, flags + ["-I", CSRC],
+                  source if outside else f"csrc/{source}")
 
 
 def host_module_path() -> str:

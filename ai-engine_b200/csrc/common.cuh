@@ -122,6 +122,30 @@ static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 blo
     return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
+// What the launchers size their grids by, asked from the current device once: the number of SMs and
+// the shared memory of one SM (148 and 228 KB on a B200).
+static inline int aie_sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0, v = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 1;
+        n = v;
+    }
+    return n;
+}
+static inline int aie_smem_per_sm() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0, v = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) != cudaSuccess || v <= 0)
+            v = 48 * 1024;
+        n = v;
+    }
+    return n;
+}
+
 #define AIE_LAUNCH_CHECK()                                   \
     do {                                                     \
         cudaError_t e__ = cudaGetLastError();                \

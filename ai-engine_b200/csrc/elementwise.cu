@@ -279,11 +279,11 @@ extern "C" int aie_silu_mul(const void* gu, void* a, int dtype, int T, int F, in
     if (T <= 0) return 0;
     const size_t total = (size_t)T * F;
     int blocks = (int)((total + 255) / 256);
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > aie_sm_count() * 16) blocks = aie_sm_count() * 16;
     if (dtype == AIE_BF16 && F % 8 == 0 && block % 8 == 0 && !((size_t)gu & 15) && !((size_t)a & 15)) {
         const size_t total8 = total / 8;
         int b8 = (int)((total8 + 255) / 256);
-        if (b8 > 148 * 16) b8 = 148 * 16;
+        if (b8 > aie_sm_count() * 16) b8 = aie_sm_count() * 16;
         launch_pdl(silu_mul_vec8_kernel, dim3(b8), dim3(256), 0, stream, (const bf16*)gu, (bf16*)a, F, block, total8);
         AIE_LAUNCH_CHECK();
     }
@@ -310,7 +310,7 @@ extern "C" int aie_cast(const void* in, int in_dtype, void* out, int out_dtype, 
                         cudaStream_t stream) {
     if (n <= 0) return 0;
     int blocks = (int)((n + 255) / 256);
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > aie_sm_count() * 16) blocks = aie_sm_count() * 16;
     if (in_dtype == AIE_F32 && out_dtype == AIE_BF16)
         cast_kernel<float, bf16><<<blocks, 256, 0, stream>>>((const float*)in, (bf16*)out, (size_t)n);
     else if (in_dtype == AIE_BF16 && out_dtype == AIE_F32)

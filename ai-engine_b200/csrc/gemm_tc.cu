@@ -342,8 +342,9 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int 
     // the deepest ring that still lets the grid's CTAs sit beside each other: one, two or three to an SM
     // (228 KB of shared memory an SM, 1 KB of it reserved per CTA); a grid of more than three waves
     // takes the ring for three
-    const int per_sm = ctas <= 148 ? 1 : (ctas <= 2 * 148 ? 2 : 3);
-    int stages = ((228 * 1024) / per_sm - 1024 - 2048) / TcSmem<BN>::stage_bytes;
+    const int sms = aie_sm_count();
+    const int per_sm = ctas <= sms ? 1 : (ctas <= 2 * sms ? 2 : 3);
+    int stages = (aie_smem_per_sm() / per_sm - 1024 - 2048) / TcSmem<BN>::stage_bytes;
     if (stages > TcSmem<BN>::max_stages) stages = TcSmem<BN>::max_stages;
     if (stages < 2) stages = 2;
     if (stages > kbps) stages = kbps < 2 ? 2 : kbps;

@@ -31,7 +31,8 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda") -> Tuple[Model, 
     dt = parse_dtype(dtype)
     arch, cfg = load_config(model_dir)
     model = Model(arch.build_spec(cfg), dt, device)
-    source, folder = open_folder(model_dir, model.tensor_specs(), dt, model.device)
+    source, folder = open_folder(model_dir, model.tensor_specs(), dt, model.device,
+                                 ignored=model.spec.ignored_tensors)
     try:
         model.load(source)
     finally:

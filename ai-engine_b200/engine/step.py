@@ -14,12 +14,12 @@ from __future__ import annotations
 
 import os
 from dataclasses import dataclass
+from types import SimpleNamespace
 from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
 
-from ..kernels.ops import PREFILL_TILE
 
 
 @dataclass
@@ -96,14 +96,22 @@ class _Buffers:
 
 
 class StepContext:
-    """Device-side description of one step.  All index arrays are int32 and live
-    in one buffer that is filled on the host and copied once."""
+    """Device-side description of one step.  All index arrays are int32 and live in one buffer that
+    is filled on the host and copied once.
 
-    SEGMENTS = ("token_ids", "positions", "token_req", "decode_tokens", "other_tokens",
-                "prefill_tiles", "q_start", "q_len", "ctx_len", "slots", "logit_rows", "token_src")
+    Generic arrays (what any part may read): `token_ids`, `positions`, `token_req` [T] (row of the token's
+    request); `q_start`, `q_len`, `ctx_len`, `slots`, `live` [R] (first token, tokens brought, tokens already
+    cached, cache slot, 0 for a row that only rounds the batch up); `logit_rows` [N]; `token_src` [T];
+    one block table [R, bt_width] per cache group.  Their host copies are `h_q_start`, `h_q_len`,
+    `h_ctx_len`, `h_slots`.  Lists that only one kind of part wants are made by that part's
+    `StepPlanner` and read with `plan(planner)`."""
+
+    SEGMENTS = ("token_ids", "positions", "token_req", "q_start", "q_len", "ctx_len", "slots", "live",
+                "logit_rows", "token_src")
 
     def __init__(self, entries: Sequence[StepEntry], cache, device, err: torch.Tensor,
-                 buffers: Optional[dict] = None, bucket_width: bool = False):
+                 buffers: Optional[dict] = None, bucket_width: bool = False, planners=(),
+                 n_live: Optional[int] = None):
         R = len(entries)
         q_len = np.array([len(e.tokens) for e in entries], dtype=np.int32)
         if R == 0 or int(q_len.min()) < 1:
@@ -139,6 +147,9 @@ class StepContext:
                     raise StepError(f"wanted place {w} is outside the entry's {len(e.tokens)} tokens")
                 rows.append(int(q_start[r]) + int(w))
         N = len(rows)
+        live = np.ones(R, dtype=np.int32)
+        if n_live is not None:
+            live[n_live:] = 0
         self.T, self.R, self.num_logit_rows = T, R, N
         self.h_q_len, self.h_ctx_len, self.h_slots, self.h_q_start = q_len, ctx_len, slots, q_start
         self.max_q_len = int(q_len.max())
@@ -146,32 +157,24 @@ class StepContext:
         width = cache.block_table_width(self.max_total_len)
         if bucket_width:            # few distinct widths, so layouts (and graphs) are reused
             width = max(64, 1 << (width - 1).bit_length())
-        self.bt_width = width
+        self.bt_width, self.page_size, self.bucketed = width, cache.page_size, bool(bucket_width)
         tables = cache.fill_block_tables(slots.tolist(), width)
 
-        # requests that bring one token (decode) and the tokens of all others
-        if T == R:
-            dec, other = q_start, np.empty(0, dtype=np.int32)
-            self.n_decode = R
-            self.max_decode_len = self.max_total_len
-        else:
-            is_dec = q_len == 1
-            dec = q_start[is_dec]
-            other = np.nonzero(np.repeat(~is_dec, q_len))[0].astype(np.int32)
-            self.n_decode = int(dec.shape[0])
-            self.max_decode_len = int((ctx_len[is_dec] + 1).max()) if self.n_decode else 0
-        if bucket_width and self.n_decode:
-            self.max_decode_len = width * cache.page_size      # a property of the layout, not of the step
-        tiles = [] if T == R else [(r, o) for r in range(R) if q_len[r] != 1
-                                   for o in range(0, int(q_len[r]), PREFILL_TILE)]
-        arrays = [token_ids.astype(np.int32), positions, token_req, dec.astype(np.int32), other,
-                  np.asarray(tiles, dtype=np.int32).reshape(-1), q_start, q_len, ctx_len, slots,
-                  np.asarray(rows, dtype=np.int32), token_src] + [tb.reshape(-1) for tb in tables]
-        key = tuple(len(a) for a in arrays) + (width,)
+        arrays = [token_ids.astype(np.int32), positions, token_req, q_start, q_len, ctx_len, slots, live,
+                  np.asarray(rows, dtype=np.int32), token_src]
+        n_generic = len(arrays)
+        planned = []                # (planner, [(name, shape)], scalars)
+        for pl in planners:
+            arrs, scalars = pl.plan(self)
+            planned.append((pl, [(name, a.shape) for name, a in arrs.items()], scalars))
+            arrays += [np.ascontiguousarray(a, dtype=np.int32).reshape(-1) for a in arrs.values()]
+        n_planned = len(arrays)
+        arrays += [tb.reshape(-1) for tb in tables]
+        key = tuple(len(a) for a in arrays) + (width,) + tuple(pl.key for pl in planners)
         self.layout_key = key
         buf = buffers.get(key) if buffers is not None else None
         if buf is None:
-            buf = _Buffers(key[:-1], device, buffers.get("staging") if buffers is not None else None)
+            buf = _Buffers(key[:len(arrays)], device, buffers.get("staging") if buffers is not None else None)
             if buffers is not None:
                 if len(buffers) >= 128:
                     buffers.pop(next(k for k in buffers if k != "staging"))
@@ -182,12 +185,32 @@ class StepContext:
         self.h2d_bytes = buf.total * 4
         dev = buf.dev
         views = [dev[o:o + n] for o, n in buf.offsets]
-        (self.token_ids, self.positions, self.token_req, self.decode_tokens, self.other_tokens,
-         pt, self.q_start, self.q_len, self.ctx_len, self.slots, self.logit_rows, self.token_src) = views[:12]
-        self.prefill_tiles = pt.view(-1, 2)
-        self.block_tables = [v.view(R, width) for v in views[12:]]
+        (self.token_ids, self.positions, self.token_req, self.q_start, self.q_len, self.ctx_len, self.slots,
+         self.live, self.logit_rows, self.token_src) = views[:n_generic]
+        self._plans = {}
+        at = n_generic
+        for pl, shapes, scalars in planned:
+            ns = SimpleNamespace(**scalars)
+            for name, shape in shapes:
+                setattr(ns, name, views[at].view(shape))
+                at += 1
+            self._plans[id(pl)] = ns
+        self.block_tables = [v.view(R, width) for v in views[n_planned:]]
         self.err = err
         self.device = device
+
+    def plan(self, planner):
+        """The lists of `planner` for this step.  They are in the step's buffer when the planner was known
+        when the step was built (`StepRunner` passes its model's planners); else they are made and uploaded
+        now, each by a copy of its own."""
+        ns = self._plans.get(id(planner))
+        if ns is None:
+            arrs, scalars = planner.plan(self)
+            ns = SimpleNamespace(**scalars)
+            for name, a in arrs.items():
+                setattr(ns, name, torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(self.device))
+            self._plans[id(planner)] = ns
+        return ns
 
 
 class StepRunner:
@@ -205,9 +228,9 @@ class StepRunner:
             use_graphs = (model.dtype == torch.bfloat16 and not model.has_host_parts()
                           and not os.environ.get("AI_ENGINE_B200_NO_GRAPHS"))
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
-        # a mixer with state of its own would update it twice for a repeated entry: no rounding up then
-        requests = model.cache_requests() if hasattr(model, "cache_requests") else []
-        self.pad_decode = not any(st is not None for _, st, _ in requests)
+        # decode steps are rounded up by repeating a row only if every part that keeps state skips such rows
+        self.pad_decode = model.pads_decode_rows() if hasattr(model, "pads_decode_rows") else True
+        self.planners = tuple(model.step_planners()) if hasattr(model, "step_planners") else ()
         self.graph_launches = 0        # kernels replayed through graphs (for launch counts)
         self.graphs_captured = 0
         # the ids the last step sampled, left on the device for a next step that starts before the
@@ -238,7 +261,8 @@ class StepRunner:
             real_rows = sum(len(e.want) for e in entries)
             e0 = entries[0]
             entries = list(entries) + [StepEntry(e0.slot, e0.start, e0.tokens, [0], e0.src)] * (8 - n_real % 8)
-        ctx = StepContext(entries, self.cache, self.device, self.err, self.buffers, bucket_width=graphed)
+        ctx = StepContext(entries, self.cache, self.device, self.err, self.buffers, bucket_width=graphed,
+                          planners=self.planners, n_live=n_real)
         ctx.real_R, ctx.real_T = n_real, ctx.T - (len(entries) - n_real)
         self.last_ctx = ctx
         if ctx.has_src:
@@ -255,7 +279,10 @@ class StepRunner:
             if buf.uses < 3:                       # a layout seen once or twice is not worth a capture
                 return self.model.forward(ctx, self.cache)
             from ..kernels.loader import LAUNCHES
-            self.model.forward(ctx, self.cache)    # warm-up outside the capture (library set-up)
+            # This step runs eagerly (which is also the warm-up that a capture needs: library set-up) and
+            # its logits are the step's result; the capture that follows launches nothing, so a part that
+            # keeps state is updated once.  The graph is replayed from the layout's next use on.
+            logits = self.model.forward(ctx, self.cache)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             n0 = LAUNCHES[0]
@@ -264,6 +291,7 @@ class StepRunner:
             buf.graph_kernels = LAUNCHES[0] - n0
             buf.graph = g
             self.graphs_captured += 1
+            return logits
         buf.graph.replay()
         self.graph_launches += buf.graph_kernels
         return buf.graph_logits

@@ -47,6 +47,16 @@ def _dev(*ts):
             raise KernelError("kernel operands must be contiguous")
 
 
+_SMS = [0]
+
+
+def sm_count() -> int:
+    """SMs of the device (148 on a B200), asked once: grids and split counts are sized by it."""
+    if not _SMS[0]:
+        _SMS[0] = int(torch.cuda.get_device_properties(0).multi_processor_count)
+    return _SMS[0]
+
+
 # ---------------------------------------------------------------------------
 def embed_gather(ids: torch.Tensor, table: torch.Tensor, err: torch.Tensor,
                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -163,9 +173,9 @@ def tc_splits(T: int, N: int, K: int, bn: int) -> int:
     their unjoined float32 parts, which the consumer reads).  A weight with more tiles is not cut."""
     tiles = ((N + 127) // 128) * ((T + bn - 1) // bn)
     kb = (K + 63) // 64
-    if tiles >= 148:
+    if tiles >= sm_count():
         return 1
-    return max(1, min((3 * 148) // tiles, kb // 12))
+    return max(1, min((3 * sm_count()) // tiles, kb // 12))
 
 
 TC_SWIGLU_BLOCK = 64     # gate/up rows per half of a 128-row weight tile
@@ -276,7 +286,7 @@ def linear_rope_kv(x: torch.Tensor, w_qkv: torch.Tensor, k_pages: torch.Tensor, 
         raise KernelError("linear_rope_kv: page shape does not fit (K, d)")
     bn = tc_tile(T)
     kb = (Kin + 63) // 64
-    splits = max(1, min(8, kb // 8, (3 * 148) // max(1, N // 128)))
+    splits = max(1, min(8, kb // 8, (3 * sm_count()) // max(1, N // 128)))
     splits = -(-kb // -(-kb // splits))
     q_out = torch.empty((T, H, d), dtype=torch.bfloat16, device=x.device)
     lib = library("gemm_tc.cu")
@@ -351,10 +361,10 @@ def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
 
 def decode_splits(n_dec: int, kv_heads: int, group: int, max_keys: int, bt_width: int = 0) -> int:
     """How many parts to cut each decode request's keys into so that the grid fills
-    the machine (two CTAs fit on each of the 148 SMs), with parts of at least 128
+    the machine (two CTAs fit on each SM), with parts of at least 128
     keys, and no part spanning more block-table entries than a CTA keeps."""
     ctas = n_dec * kv_heads * ((group + 7) // 8)
-    want = max(1, (2 * 148) // ctas)          # rounded down: one full wave, no short second one
+    want = max(1, (2 * sm_count()) // ctas)   # rounded down: one full wave, no short second one
     s = max(1, min(want, (max_keys + 127) // 128, 64))
     return max(s, (bt_width + 1999) // 2000)
 
@@ -438,8 +448,10 @@ def paged_attention_prefill_tc(q, k_pages, v_pages, tiles, q_start, q_len, ctx_l
     return True
 
 
-def paged_attention(q, k_pages, v_pages, ctx, block_table, scale: float, window: int):
-    """Attention of a step's query tokens over the cache.  float32 takes the plain
+def paged_attention(q, k_pages, v_pages, ctx, work, block_table, scale: float, window: int):
+    """Attention of a step's query tokens over the cache.  `ctx` gives the step's generic arrays
+    (positions, token_req, q_start, q_len, ctx_len, R), `work` the attention work lists derived from
+    them (decode_tokens, prefill_tiles, n_decode, max_decode_len).  float32 takes the plain
     kernel.  bfloat16 with a head size of 64 or 128: requests that bring one token
     take the split-KV decode kernel, the others a tensor-core kernel for portions of
     prompts (tcgen05 for head size 128 without a window, else mma.sync); other head sizes
@@ -451,15 +463,15 @@ def paged_attention(q, k_pages, v_pages, ctx, block_table, scale: float, window:
         return paged_attention_plain(q, k_pages, v_pages, ctx.positions, ctx.token_req, block_table,
                                      scale, window, ctx.err)
     out = torch.empty_like(q)
-    if ctx.n_decode:
-        keys = ctx.max_decode_len if window <= 0 else min(window, ctx.max_decode_len)
-        paged_attention_decode(q, k_pages, v_pages, ctx.decode_tokens, ctx.positions, ctx.token_req,
+    if work.n_decode:
+        keys = work.max_decode_len if window <= 0 else min(window, work.max_decode_len)
+        paged_attention_decode(q, k_pages, v_pages, work.decode_tokens, ctx.positions, ctx.token_req,
                                block_table, scale, window,
-                               decode_splits(ctx.n_decode, K, H // K, keys, block_table.shape[1]),
+                               decode_splits(work.n_decode, K, H // K, keys, block_table.shape[1]),
                                ctx.err, out)
-    if ctx.n_decode < ctx.R:
-        if not paged_attention_prefill_tc(q, k_pages, v_pages, ctx.prefill_tiles, ctx.q_start, ctx.q_len,
+    if work.n_decode < ctx.R:
+        if not paged_attention_prefill_tc(q, k_pages, v_pages, work.prefill_tiles, ctx.q_start, ctx.q_len,
                                           ctx.ctx_len, block_table, scale, window, ctx.err, out):
-            paged_attention_prefill(q, k_pages, v_pages, ctx.prefill_tiles, ctx.q_start, ctx.q_len,
+            paged_attention_prefill(q, k_pages, v_pages, work.prefill_tiles, ctx.q_start, ctx.q_len,
                                     ctx.ctx_len, block_table, scale, window, ctx.err, out)
     return out

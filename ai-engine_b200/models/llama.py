@@ -50,7 +50,9 @@ def build_llama_spec(cfg: LlamaConfig) -> ModelSpec:
         order=[RunStep(i) for i in range(cfg.num_hidden_layers)],
         final_norm=PartSpec("rmsnorm", dict(size=D, eps=cfg.rms_norm_eps),
                             dict(weight="model.norm.weight")),
-        lm_head=head, position_encodings={"rope": rope}, eos_token_ids=cfg.eos_token_ids)
+        lm_head=head, position_encodings={"rope": rope}, eos_token_ids=cfg.eos_token_ids,
+        # older exports store the rotary table's frequencies as a buffer of every layer
+        ignored_tensors=("self_attn.rotary_emb.inv_freq",))
 
 
 register_architecture(LlamaConfig.ARCHITECTURE, LlamaConfig, build_llama_spec)

@@ -1,6 +1,6 @@
-from .attention import GQAAttention
-from .base import (Block, BuildEnv, FeedForward, KVRequest, LayerCache, Mixer, Norm, Part,
-                   PositionEncoding, StateRequest)
+from .attention import ATTENTION_WORK, AttentionWork, GQAAttention
+from .base import (Block, BuildEnv, CacheNeed, FeedForward, KVRequest, LayerCache, Mixer, Norm, Part,
+                   PositionEncoding, StateRequest, StepPlanner)
 from .block import PreNormBlock
 from .embedding import LMHead, TokenEmbedding
 from .mlp import SwiGLU
@@ -19,8 +19,8 @@ register("block", "prenorm", PreNormBlock)
 register("embedding", "token_embedding", TokenEmbedding)
 register("head", "lm_head", LMHead)
 
-__all__ = ["GQAAttention", "Block", "BuildEnv", "FeedForward", "KVRequest", "LayerCache", "Mixer",
-           "Norm", "Part", "PositionEncoding", "StateRequest", "PreNormBlock", "LMHead",
+__all__ = ["ATTENTION_WORK", "AttentionWork", "GQAAttention", "Block", "BuildEnv", "CacheNeed", "FeedForward",
+           "KVRequest", "LayerCache", "Mixer", "Norm", "Part", "PositionEncoding", "StateRequest", "StepPlanner", "PreNormBlock", "LMHead",
            "TokenEmbedding", "SwiGLU", "Layer", "Model", "tensor_specs_of", "RMSNorm", "lookup",
            "register", "register_block", "register_feed_forward", "register_mixer",
            "register_norm", "register_position_encoding", "RotaryEncoding", "rotary_inv_freq",

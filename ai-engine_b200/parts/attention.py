@@ -13,9 +13,43 @@ import math
 
 import torch
 
+import numpy as np
+
 from ..kernels import ops
 from ..weights.loader import TensorSpec
-from .base import KVRequest, Mixer
+from .base import KVRequest, Mixer, StepPlanner
+
+
+class AttentionWork(StepPlanner):
+    """The work lists of the attention kernels, derived from a step's generic arrays: `decode_tokens`
+    (rows of requests that bring one token, for the split-KV kernel), `other_tokens` (rows of all others),
+    `prefill_tiles` [n, 2] = (request row, offset of a tile of `ops.PREFILL_TILE` tokens among the tokens it
+    brings), `n_decode`, and `max_decode_len` (the most keys a lone token reads: of the layout's widest
+    possible request when the step may be replayed from a graph)."""
+
+    key = "attention"
+
+    def plan(self, ctx):
+        q_len, q_start, R, T = ctx.h_q_len, ctx.h_q_start, ctx.R, ctx.T
+        if T == R:        # every request brings one token
+            dec, other = q_start, np.empty(0, dtype=np.int32)
+            n_decode, max_decode_len = R, ctx.max_total_len
+            tiles = np.empty((0, 2), dtype=np.int32)
+        else:
+            is_dec = q_len == 1
+            dec = q_start[is_dec]
+            other = np.nonzero(np.repeat(~is_dec, q_len))[0].astype(np.int32)
+            n_decode = int(dec.shape[0])
+            max_decode_len = int((ctx.h_ctx_len[is_dec] + 1).max()) if n_decode else 0
+            tiles = np.asarray([(r, o) for r in range(R) if q_len[r] != 1
+                                for o in range(0, int(q_len[r]), ops.PREFILL_TILE)], dtype=np.int32).reshape(-1, 2)
+        if ctx.bucketed and n_decode:
+            max_decode_len = ctx.bt_width * ctx.page_size      # a property of the layout, not of the step
+        return (dict(decode_tokens=dec.astype(np.int32), other_tokens=other, prefill_tiles=tiles),
+                dict(n_decode=n_decode, max_decode_len=max_decode_len))
+
+
+ATTENTION_WORK = AttentionWork()
 
 
 class GQAAttention(Mixer):
@@ -37,7 +71,8 @@ class GQAAttention(Mixer):
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.d)
         pe = p.get("position_encoding")
         self.rope = env.position_encodings[pe] if pe else None
-        if self.rope is not None and self.rope.rot_dim > self.d:
+        rot = self.rope.rotation() if self.rope is not None else None
+        if rot is not None and rot[1] > self.d:
             raise ValueError("attention: rotary width exceeds head_dim")
         self.w_qkv = self.w_o = None
         self._no_rope = None
@@ -60,11 +95,19 @@ class GQAAttention(Mixer):
     def weight_bytes(self):
         return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.w_o))
 
+    def flops(self, tokens, keys=0.0):
+        proj = 2.0 * tokens * self.hidden * (2 * self.H + 2 * self.K) * self.d
+        return proj + 4.0 * tokens * keys * self.H * self.d         # q.k and p.v
+
     def cache_request(self):
         return KVRequest(self.K, self.d, self.window)
 
+    def step_planner(self):
+        return ATTENTION_WORK
+
     def forward(self, h, ctx, cache):
-        inv_freq = self.rope.inv_freq if self.rope is not None else self._no_rope
+        rot = self.rope.rotation() if self.rope is not None else None
+        inv_freq = rot[0] if rot is not None else self._no_rope
         # a small bfloat16 step: product, rotation and cache write in one kernel
         q = ops.linear_rope_kv(h, self.w_qkv, cache.k_pages, cache.v_pages, ctx.positions, ctx.token_req,
                                cache.block_table, inv_freq, self.H, self.K, self.d, ctx.err,
@@ -74,6 +117,6 @@ class GQAAttention(Mixer):
             q = ops.rope_kv_write(qkv, cache.k_pages, cache.v_pages, ctx.positions, ctx.token_req,
                                   cache.block_table, inv_freq, self.H, self.K, self.d, ctx.err,
                                   write=cache.writes)
-        a = ops.paged_attention(q, cache.k_pages, cache.v_pages, ctx, cache.block_table,
-                                self.scale, self.window)
+        a = ops.paged_attention(q, cache.k_pages, cache.v_pages, ctx, ctx.plan(ATTENTION_WORK),
+                                cache.block_table, self.scale, self.window)
         return ops.linear_parts(a.view(a.shape[0], self.H * self.d), self.w_o, ctx.err)

@@ -11,15 +11,15 @@ from .base import Block
 
 
 class PreNormBlock(Block):
-    roles = ("mixer_norm", "mixer", "ffn_norm", "ffn")
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "ffn_norm": "norm", "ffn": "feed_forward"}
 
     def __init__(self, spec, env, parts):
         super().__init__(spec, env)
         self.mixer_norm, self.mixer = parts["mixer_norm"], parts["mixer"]
         self.ffn_norm, self.ffn = parts["ffn_norm"], parts["ffn"]
 
-    def forward(self, x, pending, ctx, cache):
+    def forward(self, x, pending, ctx, caches):
         h = self.mixer_norm.forward(x, pending)
-        a = self.mixer.forward(h, ctx, cache)
+        a = self.mixer.forward(h, ctx, caches.get("mixer"))
         h = self.ffn_norm.forward(x, a)
         return x, self.ffn.forward(h, ctx)

@@ -12,7 +12,8 @@ from .base import Part
 
 class TokenEmbedding(Part):
     """params: vocab_size, hidden_size, alternatives (names that may stand in).
-    tensors: weight [vocab, hidden].  forward(ids) -> float32 residual stream."""
+    tensors: weight [vocab, hidden].  forward(ctx) -> float32 residual stream [T, hidden] of the
+    step's tokens (`ctx.token_ids`; an embedding that depends on the place reads `ctx.positions`)."""
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -26,8 +27,8 @@ class TokenEmbedding(Part):
     def load(self, source):
         self.weight = source.get(self.spec.tensors["weight"])
 
-    def forward(self, ids, err):
-        return ops.embed_gather(ids, self.weight, err)
+    def forward(self, ctx):
+        return ops.embed_gather(ctx.token_ids, self.weight, ctx.err)
 
 
 class LMHead(Part):
@@ -50,6 +51,9 @@ class LMHead(Part):
 
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()
+
+    def flops(self, tokens, keys=0.0):
+        return 2.0 * tokens * self.vocab * self.hidden
 
     def forward(self, h, err=None):
         return ops.linear(h, self.weight, torch.float32, err)

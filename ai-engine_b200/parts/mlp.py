@@ -44,6 +44,9 @@ class SwiGLU(FeedForward):
     def weight_bytes(self):
         return sum(w.numel() * w.element_size() for w in (self.w_gu, self.w_down))
 
+    def flops(self, tokens, keys=0.0):
+        return 2.0 * tokens * 3 * self.inter * self.hidden
+
     def forward(self, h, ctx):
         a = ops.linear_swiglu(h, self.w_gu, self.block, ctx.err if ctx is not None else None)
         return ops.linear_parts(a, self.w_down, ctx.err if ctx is not None else None)   # joins the residual in float32

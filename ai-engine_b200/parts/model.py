@@ -11,31 +11,34 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..weights.loader import TensorSpec, WeightSource
-from .base import BuildEnv, KVRequest, Part, StateRequest
+from .base import BuildEnv, CacheNeed, Part, StepPlanner
 from .registry import lookup
 from .spec import LayerSpec, ModelSpec, PartSpec
 
-_ROLE_FAMILY = {"mixer": "mixer", "ffn": "feed_forward", "mixer_norm": "norm", "ffn_norm": "norm"}
-
-
-def _family_of(role: str) -> str:
-    if role in _ROLE_FAMILY:
-        return _ROLE_FAMILY[role]
-    if role.endswith("norm"):
-        return "norm"
-    raise KeyError(f"block role `{role}` has no part family")
-
 
 class Layer:
+    """The parts of one layer, built by the families that its block names for its roles."""
+
     def __init__(self, spec: LayerSpec, env: BuildEnv):
         block_cls = lookup("block", spec.block)
-        missing = [r for r in block_cls.roles if r not in spec.parts]
-        if missing:
-            raise ValueError(f"block `{spec.block}` needs parts for roles {missing}")
+        roles = dict(block_cls.roles)
+        missing = [r for r in roles if r not in spec.parts]
+        unknown = [r for r in spec.parts if r not in roles]
+        if missing or unknown:
+            raise ValueError(f"block `{spec.block}` has the roles {sorted(roles)}: "
+                             f"missing parts for {missing}, no role for {unknown}")
         self.parts: Dict[str, Part] = {
-            role: lookup(_family_of(role), ps.kind)(ps, env) for role, ps in spec.parts.items()}
+            role: lookup(roles[role], spec.parts[role].kind)(spec.parts[role], env) for role in roles}
         self.block = block_cls(PartSpec(spec.block), env, self.parts)
-        self.mixer = self.parts.get("mixer")
+
+    def cache_needs(self):
+        """(role, pages wanted, state wanted) of every part that asks for either."""
+        out = []
+        for role, part in self.parts.items():
+            kv, st = part.cache_request(), part.state_request()
+            if kv is not None or st is not None:
+                out.append((role, kv, st))
+        return out
 
 
 class Model:
@@ -79,25 +82,58 @@ class Model:
         return out
 
     def load(self, source: WeightSource) -> None:
+        wanted: Dict[str, int] = {}
+        for p in self.all_parts():
+            for s in p.tensor_specs():
+                wanted[s.name] = wanted.get(s.name, 0) + 1
+        source.keep_only([n for n, c in wanted.items() if c > 1])
         for p in self.all_parts():
             p.load(source)
         self.loaded = True
 
     # -- what the cache manager must provide ----------------------------------
-    def cache_requests(self) -> List[Tuple[Optional[KVRequest], Optional[StateRequest], Optional[int]]]:
-        """For each entry of the run order: (pages wanted, state wanted, cache_from)."""
+    def cache_requests(self) -> List[CacheNeed]:
+        """What the parts of every run-order entry ask of the cache manager.  An entry that reads
+        another entry's cache gets that entry's pages, role by role, and none of its own."""
         out = []
-        for rs in self.order:
-            m = self.layers[rs.layer].mixer
-            kv = m.cache_request() if m is not None else None
-            st = m.state_request() if m is not None else None
-            out.append((kv if rs.cache_from is None else None, st, rs.cache_from))
+        for i, rs in enumerate(self.order):
+            for role, kv, st in self.layers[rs.layer].cache_needs():
+                if rs.cache_from is not None and kv is not None:
+                    out.append(CacheNeed(i, role, None, st, rs.cache_from))
+                else:
+                    out.append(CacheNeed(i, role, kv, st, None))
         return out
+
+    def step_planners(self) -> List[StepPlanner]:
+        """The planners whose lists the parts read in forward, each once."""
+        out: List[StepPlanner] = []
+        for p in self.all_parts():
+            pl = p.step_planner()
+            if pl is not None and all(pl is not q for q in out):
+                out.append(pl)
+        return out
+
+    def keeps_state(self) -> bool:
+        return any(n.state is not None for n in self.cache_requests())
+
+    def pads_decode_rows(self) -> bool:
+        """Whether decode steps may be rounded up by repeating a row: every part that keeps state
+        skips rows with `ctx.live == 0`."""
+        return all(getattr(p, "skips_padded_rows", False) or p.state_request() is None
+                   for l in self.layers for p in l.parts.values())
 
     def has_host_parts(self) -> bool:
         """True when a part reads step data on the host inside forward (`host_side =
         True` on its class): such a model cannot be replayed from a captured graph."""
         return any(getattr(p, "host_side", False) for p in self.all_parts())
+
+    def step_flops(self, tokens: int, keys: float = 0.0, logit_rows: int = 1) -> float:
+        """Floating-point operations of one step of `tokens` tokens that read `keys` cached positions
+        each on average, with logits at `logit_rows` rows: every part once per run, the head once."""
+        total = self.lm_head.flops(logit_rows) + self.final_norm.flops(logit_rows)
+        for rs in self.order:
+            total += sum(p.flops(tokens, keys) for p in self.layers[rs.layer].parts.values())
+        return total
 
     def step_weight_bytes(self) -> int:
         """Bytes of weights one step reads: every part once per run, the head once."""
@@ -108,7 +144,9 @@ class Model:
 
     # -- the forward pass of one step -----------------------------------------
     def forward(self, ctx, cache) -> torch.Tensor:
-        x = self.embedding.forward(ctx.token_ids, ctx.err)
+        x = self.embedding.forward(ctx)
+        for pe in self.env.position_encodings.values():
+            pe.add_to(x, ctx)
         pending = None
         for i, rs in enumerate(self.order):
             x, pending = self.layers[rs.layer].block.forward(x, pending, ctx, cache.layer_cache(i, ctx))

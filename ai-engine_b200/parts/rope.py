@@ -58,3 +58,6 @@ class RotaryEncoding(PositionEncoding):
 
     def load(self, source):
         self.inv_freq = torch.from_numpy(self.inv_freq_host.copy()).to(self.env.device)
+
+    def rotation(self):
+        return self.inv_freq, self.rot_dim

@@ -48,3 +48,4 @@ class ModelSpec:
     lm_head: PartSpec
     position_encodings: Dict[str, PartSpec] = field(default_factory=dict)
     eos_token_ids: Tuple[int, ...] = ()
+    ignored_tensors: Tuple[str, ...] = ()     # name endings of stored tensors that are no parameters

@@ -7,9 +7,12 @@ folder is compared with the model's whole list first, so one message names all
 missing tensors, all unexpected ones and all wrong shapes.
 
 Dtype policy: compute dtype bfloat16 keeps bf16 as stored, turns f16 into
-bf16, and leaves a tensor stored in 32-bit as it is; integer tables become
-int32.  Compute dtype float32 widens every floating tensor to f32
-(loader.rs:733-744 does the same widening).
+bf16, and leaves a tensor stored in 32-bit as it is; integer tables (a spec
+with `init="int"`) become int32.  Compute dtype float32 widens every floating
+tensor to f32 (loader.rs:733-744 does the same widening).  A weight stored as
+integers where the model wants floating point (a quantised file) is refused in
+the same message, by name, as the reference refuses dtypes it does not take
+(loader.rs:748).
 """
 from __future__ import annotations
 
@@ -97,10 +100,12 @@ class ModelFolder:
 
 
 def check_and_resolve(specs: Sequence[TensorSpec], available: Dict[str, Tuple[torch.dtype, tuple]],
-                      where: str = "") -> Dict[str, str]:
+                      where: str = "", ignored: Sequence[str] = ()) -> Dict[str, str]:
     """Map every wanted name to the stored name that provides it, or raise one
-    WeightError listing missing tensors, unexpected tensors and wrong shapes."""
-    missing, wrong, resolved, used = [], [], {}, set()
+    WeightError listing missing tensors, unexpected tensors, wrong shapes and wrong
+    dtypes.  `ignored`: name endings of stored tensors that are no parameters (buffers
+    that some exporters write) and are passed over."""
+    missing, wrong, wrong_dtype, resolved, used = [], [], [], {}, set()
     for s in specs:
         src = None
         for cand in (s.name,) + tuple(s.alternatives):
@@ -114,11 +119,15 @@ def check_and_resolve(specs: Sequence[TensorSpec], available: Dict[str, Tuple[to
         dt, shape = available[src]
         if tuple(shape) != tuple(s.shape):
             wrong.append(f"{src}: stored {list(shape)}, model wants {list(s.shape)}")
+        if isinstance(dt, torch.dtype) and dt.is_floating_point == (s.init == "int"):
+            want = "integers" if s.init == "int" else "floating point (F32, F16 or BF16)"
+            wrong_dtype.append(f"{src}: stored as {str(dt).replace('torch.', '')}, model wants {want}")
         resolved[s.name] = src
         used.add(src)
     wanted_names = {s.name for s in specs} | {a for s in specs for a in s.alternatives}
-    unexpected = sorted(n for n in available if n not in used and n not in wanted_names)
-    if missing or wrong or unexpected:
+    unexpected = sorted(n for n in available if n not in used and n not in wanted_names
+                        and not any(n.endswith(e) for e in ignored))
+    if missing or wrong or unexpected or wrong_dtype:
         parts = [f"weights{' in ' + where if where else ''} do not fit the model:"]
         if missing:
             parts.append(f"  missing tensors ({len(missing)}): " + "; ".join(missing))
@@ -126,6 +135,8 @@ def check_and_resolve(specs: Sequence[TensorSpec], available: Dict[str, Tuple[to
             parts.append(f"  unexpected tensors ({len(unexpected)}): " + "; ".join(unexpected))
         if wrong:
             parts.append(f"  wrong shapes ({len(wrong)}): " + "; ".join(wrong))
+        if wrong_dtype:
+            parts.append(f"  wrong dtypes ({len(wrong_dtype)}): " + "; ".join(wrong_dtype))
         raise WeightError("\n".join(parts))
     return resolved
 
@@ -139,6 +150,14 @@ class WeightSource:
         self._fetch, self._resolved = fetch, resolved
         self.compute_dtype, self.device = compute_dtype, device
         self._on_device: Dict[str, torch.Tensor] = {}
+        self._shared = None           # None: keep every tensor until release()
+
+    def keep_only(self, names) -> None:
+        """Name the tensors that more than one part reads (a tied head and its embedding): only these
+        are kept until release(), so that both get one device copy.  Every other tensor belongs to the
+        part that fetched it; what that part fuses into another tensor is then freed with the part's
+        last reference, and loading never holds much more than the model itself."""
+        self._shared = {self._resolved.get(n, n) for n in names}
 
     def get(self, name: str) -> torch.Tensor:
         src = self._resolved.get(name, name)
@@ -147,7 +166,8 @@ class WeightSource:
             t = self._fetch(src)
             dt = _storage_dtype(t.dtype, self.compute_dtype)
             t = t.to(device=self.device, dtype=dt).contiguous()
-            self._on_device[src] = t
+            if self._shared is None or src in self._shared:
+                self._on_device[src] = t
         return t
 
     def release(self) -> None:
@@ -155,10 +175,10 @@ class WeightSource:
 
 
 def open_folder(model_dir: str, specs: Sequence[TensorSpec], compute_dtype: torch.dtype,
-                device) -> Tuple[WeightSource, ModelFolder]:
+                device, ignored: Sequence[str] = ()) -> Tuple[WeightSource, ModelFolder]:
     folder = ModelFolder(model_dir)
     available = {n: folder.info(n) for n in folder.names()}
-    resolved = check_and_resolve(specs, available, where=model_dir)
+    resolved = check_and_resolve(specs, available, where=model_dir, ignored=ignored)
     return WeightSource(folder.tensor, resolved, compute_dtype, device), folder
 
 

@@ -191,12 +191,7 @@ def time_prefill(torch, model, tokens, pk):
             ms = s.elapsed_time(e)
             best = ms if best is None else min(best, ms)
     runner.check_errors()
-    c = model.spec
-    lw = sum(p.numel() for l in model.layers for part in l.parts.values()
-             for p in (getattr(part, "w_qkv", None), getattr(part, "w_o", None), getattr(part, "w_gu", None),
-                       getattr(part, "w_down", None)) if p is not None)
-    att = model.layers[0].mixer
-    flops = 2.0 * tokens * lw + 2.0 * tokens * tokens * att.d * att.H * len(model.order) + 2.0 * c.vocab_size * c.hidden_size
+    flops = model.step_flops(tokens, keys=(tokens + 1) / 2.0, logit_rows=1)      # what the parts report
     return dict(value=tokens * 1000.0 / best, tokens=tokens, ms=best,
                 frac=flops / (best * 1e-3) / (pk["bf16_tflops"] * 1e12))
 

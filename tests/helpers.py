@@ -55,7 +55,15 @@ TINY_E = dict(
     max_position_embeddings=2048)
 TINY_E_OPTS = dict(seed=4, norm_std=0.05, block_size=16, qk_gain=4.0)
 
-TINY = {"A": (TINY_A, TINY_A_OPTS), "B": (TINY_B, TINY_B_OPTS), "C": (TINY_C, TINY_C_OPTS),
+# The reference's own golden fixture (tests/golden/toy-llama-3-q8): 4 layers, 4 heads on 2 kv heads of 64,
+# tied with only lm_head stored, rope_theta under rope_parameters; weights dequantised from its int8 file.
+FIXTURE_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "toy-llama-3-q8")
+FIXTURE_PROMPT = [91, 176, 179, 148]       # "The quick brown fox" under the fixture's tokenizer
+with open(os.path.join(FIXTURE_DIR, "config.json")) as _f:
+    TINY_Q = json.load(_f)
+TINY_Q_OPTS = dict(seed=None, norm_std=None, block_size=16, qk_gain=1.0)
+
+TINY = {"A": (TINY_A, TINY_A_OPTS), "Q": (TINY_Q, TINY_Q_OPTS), "B": (TINY_B, TINY_B_OPTS), "C": (TINY_C, TINY_C_OPTS),
         "D": (TINY_D, TINY_D_OPTS), "E": (TINY_E, TINY_E_OPTS)}
 
 # Tolerances (max abs difference of logits; logits here are O(0.1 .. 1)).
@@ -78,6 +86,8 @@ def make_model_dir(tmp_path, name: str, dtype: str = "bfloat16", qk_gain=None) -
     far beyond the tolerance)."""
     import ai_engine_b200 as aie
 
+    if name == "Q":
+        return make_fixture_dir(tmp_path, dtype)
     raw, opts = TINY[name]
     qk_gain = opts["qk_gain"] if qk_gain is None else qk_gain
     cfg = aie.LlamaConfig.from_dict(raw)
@@ -99,9 +109,49 @@ def make_model_dir(tmp_path, name: str, dtype: str = "bfloat16", qk_gain=None) -
     return d
 
 
-def plain_logits(model_dir: str, ids, dtype=torch.float64) -> np.ndarray:
-    """[len(ids), vocab] from the plain implementation."""
-    return pl.forward_dir(model_dir, ids, dtype).to(torch.float64).numpy()
+def fixture_tensors() -> dict:
+    """The fixture's tensors in float32: w = int8 * scale for the Linear weights (one float32 scale per
+    tensor, stored beside it as `<name>.scale`), the bf16 norms widened
+    (crates/ai-engine-runtime/src/loader.rs:733-750 dequantises the same way)."""
+    from safetensors import safe_open
+
+    out = {}
+    with safe_open(os.path.join(FIXTURE_DIR, "model.safetensors"), "pt") as f:
+        for k in f.keys():
+            if k.endswith(".scale"):
+                continue
+            t = f.get_tensor(k)
+            if t.dtype == torch.int8:
+                t = t.to(torch.float32) * f.get_tensor(k + ".scale").to(torch.float32)
+            out[k] = t.to(torch.float32)
+    return out
+
+
+def fixture_reference_logits() -> np.ndarray:
+    """The reference's logits at the last position of FIXTURE_PROMPT (512 float32, from the unquantised
+    weights: crates/ai-engine-runtime/scripts/generate_toy_fixture.py:37-97)."""
+    return np.fromfile(os.path.join(FIXTURE_DIR, "reference_logits.bin"), dtype="<f4")
+
+
+def make_fixture_dir(tmp_path, dtype: str = "bfloat16") -> str:
+    """The fixture as a model folder the engine can load: its config.json as it is, and the
+    dequantised tensors stored in `dtype` (no embed_tokens: the tied table is read from lm_head)."""
+    from safetensors.torch import save_file
+
+    d = os.path.join(str(tmp_path), f"fixture_{dtype}")
+    os.makedirs(d, exist_ok=True)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(TINY_Q, f)
+    dt = dict(bfloat16=torch.bfloat16, float32=torch.float32)[dtype]
+    save_file({k: v.to(dt).contiguous() for k, v in fixture_tensors().items()},
+              os.path.join(d, "model.safetensors"))
+    return d
+
+
+def plain_logits(model_dir: str, ids, dtype=torch.float64, rows=None) -> np.ndarray:
+    """[len(ids), vocab] from the plain implementation ([len(rows), vocab] for chosen rows)."""
+    rows = None if rows is None else torch.as_tensor(list(rows), dtype=torch.long)
+    return pl.forward_dir(model_dir, ids, dtype, rows).to(torch.float64).numpy()
 
 
 def random_ids(n: int, vocab: int, seed: int):

@@ -126,30 +126,35 @@ def rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: np.ndarray) -> torc
     return torch.cat([x1 * cos - x2 * sin, x1 * sin + x2 * cos], dim=-1)
 
 
-def attention(h, wq, wk, wv, wo, positions, cfg, inv_freq, window=None) -> torch.Tensor:
+def attention(h, wq, wk, wv, wo, positions, cfg, inv_freq, window=None, rows=None) -> torch.Tensor:
     """crates/ai-engine-runtime/src/arch/attention.rs:114-166 (forward),
     :177-196 (consecutive KV-head repeat), :203-224 (mask j <= pos[i]).
     h: [S, D].  `window` (keys j > pos-window only) is not in the reference; it
-    serves tests of cache groups with a window."""
+    serves tests of cache groups with a window.  `rows`: queries are computed for
+    these rows of h only (keys and values for all): the same formulas on fewer rows,
+    for sequences whose full score matrix would not fit."""
     S = h.shape[0]
     H, K, d = cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
-    q = (h @ wq.T).view(S, H, d).transpose(0, 1)
+    hq = h if rows is None else h[rows]
+    qpos = positions if rows is None else positions[rows]
+    Q = hq.shape[0]
+    q = (hq @ wq.T).view(Q, H, d).transpose(0, 1)
     k = (h @ wk.T).view(S, K, d).transpose(0, 1)
     v = (h @ wv.T).view(S, K, d).transpose(0, 1)
-    q = rope(q, positions, inv_freq)
+    q = rope(q, qpos, inv_freq)
     k = rope(k, positions, inv_freq)
     rep = H // K
     k = k[:, None].expand(K, rep, S, d).reshape(H, S, d)
     v = v[:, None].expand(K, rep, S, d).reshape(H, S, d)
     scores = (q @ k.transpose(1, 2)) * (1.0 / math.sqrt(d))
     j = positions[None, :]
-    i = positions[:, None]
+    i = qpos[:, None]
     allowed = j <= i
     if window is not None:
         allowed = allowed & (j > i - window)
     scores = scores.masked_fill(~allowed[None], float("-inf"))
     probs = torch.softmax(scores, dim=-1)
-    ctx = (probs @ v).transpose(0, 1).reshape(S, H * d)
+    ctx = (probs @ v).transpose(0, 1).reshape(Q, H * d)
     return ctx @ wo.T
 
 
@@ -160,14 +165,16 @@ def swiglu(h, wg, wu, wd) -> torch.Tensor:
     return ((g * torch.sigmoid(g)) * u) @ wd.T
 
 
-def decoder_layer(x, w: dict, i: int, positions, cfg, inv_freq) -> torch.Tensor:
+def decoder_layer(x, w: dict, i: int, positions, cfg, inv_freq, rows=None) -> torch.Tensor:
     """crates/ai-engine-runtime/src/arch/block.rs:13-27 — pre-norm, two
-    residuals."""
+    residuals.  `rows`: only these rows of the layer's output are computed and
+    returned (their attention still reads every earlier position)."""
     p = f"model.layers.{i}."
     h = rms_norm(x, w[p + "input_layernorm.weight"], cfg["eps"])
-    x = x + attention(h, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.k_proj.weight"],
-                      w[p + "self_attn.v_proj.weight"], w[p + "self_attn.o_proj.weight"],
-                      positions, cfg, inv_freq)
+    a = attention(h, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.k_proj.weight"],
+                  w[p + "self_attn.v_proj.weight"], w[p + "self_attn.o_proj.weight"],
+                  positions, cfg, inv_freq, rows=rows)
+    x = (x if rows is None else x[rows]) + a
     h = rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["eps"])
     x = x + swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
                    w[p + "mlp.down_proj.weight"])
@@ -179,11 +186,14 @@ def embed(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     return table[ids]
 
 
-def forward(w: dict, cfg: dict, ids) -> torch.Tensor:
+def forward(w: dict, cfg: dict, ids, rows=None) -> torch.Tensor:
     """crates/ai-engine-runtime/src/arch/model.rs:209-224 — embedding, blocks,
     final norm, output projection at every position; tied head uses the
     embedding table (model.rs:130-134), and a file without embed_tokens but
-    with lm_head uses that for both (loader.rs:129-151).  Returns [S, V]."""
+    with lm_head uses that for both (loader.rs:129-151).  Returns [S, V].
+    `rows`: logits at these positions only, [len(rows), V]; the last layer, the
+    final norm and the head then run on those rows alone (earlier layers need
+    every row, since later positions read their keys and values)."""
     ids = torch.as_tensor(ids, dtype=torch.long)
     table = w.get("model.embed_tokens.weight")
     if table is None:
@@ -194,13 +204,14 @@ def forward(w: dict, cfg: dict, ids) -> torch.Tensor:
     inv_freq = inv_freq_for(cfg)
     x = embed(ids, table)
     for i in range(cfg["layers"]):
-        x = decoder_layer(x, w, i, positions, cfg, inv_freq)
+        last = i == cfg["layers"] - 1
+        x = decoder_layer(x, w, i, positions, cfg, inv_freq, rows=rows if last else None)
     x = rms_norm(x, w["model.norm.weight"], cfg["eps"])
     return (x @ head.T).to(dtype)
 
 
-def forward_dir(model_dir: str, ids, dtype=torch.float32) -> torch.Tensor:
-    return forward(read_weights(model_dir, dtype), read_config(model_dir), ids)
+def forward_dir(model_dir: str, ids, dtype=torch.float32, rows=None) -> torch.Tensor:
+    return forward(read_weights(model_dir, dtype), read_config(model_dir), ids, rows)
 
 
 # ----------------------------------------------------------------------------

@@ -131,16 +131,22 @@ def test_random_orders_lose_nothing(seed):
     assert c.free_pages(0) == 24 and c.free_pages(1) == 30 and c.free_slots == 5
 
 
-def test_groups_by_what_mixers_ask_for():
-    """Entries with the same need share a group; a window or another head size makes a
-    group of its own; an entry that reads another's cache gets that one's place."""
+def test_groups_by_what_parts_ask_for():
+    """Parts with the same need share a group; a window or another head size makes a group of its
+    own; an entry that reads another's cache gets that one's place; two parts of one entry (two
+    roles) have a cache each."""
+    from ai_engine_b200.parts import CacheNeed
+
     full, win = KVRequest(2, 16, 0), KVRequest(2, 16, 32)
-    reqs = [(full, None, None), (win, None, None), (full, None, None), (None, StateRequest((4,)), None),
-            (None, None, 1)]
+    reqs = [CacheNeed(0, "mixer", full), CacheNeed(1, "mixer", win), CacheNeed(2, "mixer", full),
+            CacheNeed(2, "side", win, StateRequest((3,))), CacheNeed(3, "mixer", None, StateRequest((4,))),
+            CacheNeed(4, "mixer", None, None, 1)]
     c = PagedCache(reqs, page_size=8, num_pages=10, max_seqs=2, max_seq_len=64, dtype=None, allocate=False)
     assert len(c.groups) == 2
-    assert c.groups[0].entries == [0, 2] and c.groups[1].entries == [1]
-    assert c.where[4] == c.where[1] and 3 not in c.where
+    assert c.groups[0].entries == [(0, "mixer"), (2, "mixer")] and c.groups[1].entries == [(1, "mixer"), (2, "side")]
+    assert c.where[4, "mixer"] == c.where[1, "mixer"] and (3, "mixer") not in c.where
+    assert c.writes[1, "mixer"] and not c.writes[4, "mixer"]
+    assert c.roles[2] == ["mixer", "side"]
     assert c.book.group(1).window == 32
     with pytest.raises(ValueError):
-        PagedCache([(None, None, 0)], 8, 10, 2, 64, None, allocate=False)
+        PagedCache([CacheNeed(1, "mixer", None, None, 0)], 8, 10, 2, 64, None, allocate=False)

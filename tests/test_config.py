@@ -101,3 +101,28 @@ def test_spec_has_no_size_of_its_own():
         assert s.layers[0].parts["ffn"].params["intermediate_size"] == c.intermediate_size
         assert s.layers[0].parts["mixer_norm"].params["eps"] == c.rms_norm_eps
         assert s.position_encodings["rope"].params["theta"] == c.rope_theta
+
+
+def test_rotary_frequencies_by_hand_and_the_fixtures_configuration():
+    """The product's frequencies against values worked out by hand (head size 8, theta 10000: 1, 0.1,
+    0.01, 0.001; llama3 with factor 4, low 1, high 4: a wavelength below original / 4 is kept, above
+    original is divided by 4, between the two blended), and the reference fixture's config.json, whose
+    rope_theta is stored under `rope_parameters` only."""
+    import math
+
+    import numpy as np
+
+    from ai_engine_b200.parts.rope import rotary_inv_freq
+    from helpers import TINY_Q
+
+    sc = lambda orig: dict(rope_type="llama3", factor=4.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                           original_max_position_embeddings=orig)
+    assert np.allclose(rotary_inv_freq(8, 10000.0), [1.0, 0.1, 0.01, 0.001], rtol=1e-6)
+    assert np.allclose(rotary_inv_freq(8, 10000.0, sc(32)), [1.0, 0.025, 0.0025, 0.00025], rtol=1e-6)
+    assert np.allclose(rotary_inv_freq(8, 10000.0, sc(256)), [1.0, 0.1, 0.0025, 0.00025], rtol=1e-6)
+    s = (100.0 / (2 * math.pi / 0.1) - 1.0) / 3.0
+    assert np.allclose(rotary_inv_freq(8, 10000.0, sc(100)), [1.0, (1 - s) * 0.025 + s * 0.1, 0.0025, 0.00025],
+                       rtol=1e-6)
+    c = LlamaConfig.from_dict(TINY_Q)
+    assert (c.rope_theta, c.rope_scaling, c.tie_word_embeddings, c.head_dim, c.eos_token_ids) == (
+        10000.0, None, True, 64, (2,))

@@ -342,7 +342,7 @@ def test_mixed_step_decode_and_prefill_kernels_side_by_side():
     i32 = lambda a: torch.tensor(a, device=DEV, dtype=torch.int32)
     ctx.R, ctx.prefill_tiles = 3, i32([[1, 0]])
     ctx.q_start, ctx.q_len, ctx.ctx_len = i32([0, 1, 6]), i32([1, 5, 1]), i32([69, 25, 199])
-    out = ops().paged_attention(s["q"], s["k_pages"], s["v_pages"], ctx, s["bt"], scale, 0)
+    out = ops().paged_attention(s["q"], s["k_pages"], s["v_pages"], ctx, ctx, s["bt"], scale, 0)
     want = attention_reference(s, H, K, d, scale, 0)
     assert (out.double() - want).abs().max() <= 2e-2
 

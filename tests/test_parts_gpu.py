@@ -211,8 +211,9 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     kinds, order = ["ema", "attn", "ema"], [0, 1, 2]
     model, cache, runner, weights = build_toy(kinds, order)
     reqs = model.cache_requests()
-    assert reqs[0][1] is not None and reqs[0][0] is None and reqs[1][0] is not None
-    assert set(cache.state) == {0, 2} and len(cache.groups) == 1
+    assert [(n.run, n.role, n.kv is not None, n.state is not None) for n in reqs] == [
+        (0, "mixer", False, True), (1, "mixer", True, False), (2, "mixer", False, True)]
+    assert set(cache.state) == {(0, "mixer"), (2, "mixer")} and len(cache.groups) == 1
     ids = random_ids(40, 50, 3)
     want = plain_toy_forward(weights, kinds, order, ids)
     whole = run_in_portions(runner, cache, ids, [40])
@@ -233,8 +234,8 @@ def test_a_layer_named_twice_and_a_layer_that_reads_anothers_cache():
     kinds = ["attn", "attn"]
     order = [0, 1, 0, (1, 1)]           # layer 0 runs twice (two caches); the last run reads run 1's cache
     model, cache, runner, weights = build_toy(kinds, order, seed=5)
-    assert len(cache.groups) == 1 and cache.groups[0].entries == [0, 1, 2]
-    assert cache.where[3] == cache.where[1]
+    assert len(cache.groups) == 1 and cache.groups[0].entries == [(0, "mixer"), (1, "mixer"), (2, "mixer")]
+    assert cache.where[3, "mixer"] == cache.where[1, "mixer"] and not cache.writes[3, "mixer"]
     ids = random_ids(33, 50, 6)
     want = plain_toy_forward(weights, kinds, order, ids)
     got = run_in_portions(runner, cache, ids, [5, 2, 17, 1, 8])
@@ -272,7 +273,7 @@ def test_attention_part_alone_over_its_cache(dtype, H, K, d, window):
     """GQAAttention with a rotary encoding, fed in three portions (the last one a single token),
     against plain attention on the whole sequence."""
     from ai_engine_b200.cache import PagedCache
-    from ai_engine_b200.parts import BuildEnv, GQAAttention, PartSpec, RotaryEncoding
+    from ai_engine_b200.parts import BuildEnv, CacheNeed, GQAAttention, PartSpec, RotaryEncoding
 
     torch.manual_seed(H * d)
     D, S = 96, 45
@@ -289,14 +290,14 @@ def test_attention_part_alone_over_its_cache(dtype, H, K, d, window):
     ts = {"q": (torch.randn(H * d, D) * g).to(dtype), "k": (torch.randn(K * d, D) * g).to(dtype),
           "v": (torch.randn(K * d, D) * 0.1).to(dtype), "o": (torch.randn(D, H * d) * 0.06).to(dtype)}
     part.load(source(ts, part.tensor_specs(), dtype))
-    cache = PagedCache([(part.cache_request(), None, None)], 8, 12, 2, 96, dtype, DEV)
+    cache = PagedCache([CacheNeed(0, "mixer", part.cache_request())], 8, 12, 2, 96, dtype, DEV)
     slot = cache.admit()
     h = torch.randn(S, D).to(dtype)
     outs, at = [], 0
     for n in (30, 14, 1):
         assert cache.ensure(slot, at + n)
         ctx, err = _step_ctx(cache, slot, at, n)
-        y = part.forward(h[at:at + n].to(DEV).contiguous(), ctx, cache.layer_cache(0, ctx)).float()
+        y = part.forward(h[at:at + n].to(DEV).contiguous(), ctx, cache.part_cache(0, "mixer", ctx)).float()
         outs.append((y.sum(0) if y.dim() == 3 else y).cpu())      # unjoined parts of a split product
         assert int(err.item()) == 0
         at += n
@@ -325,7 +326,8 @@ def test_embedding_and_head_parts(dtype):
     assert emb.weight.data_ptr() == head.weight.data_ptr()          # one device copy serves both
     ids = torch.tensor([0, 5, 332, 5], dtype=torch.int32, device=DEV)
     err = torch.zeros(1, dtype=torch.int32, device=DEV)
-    x = emb.forward(ids, err)
+    from types import SimpleNamespace
+    x = emb.forward(SimpleNamespace(token_ids=ids, err=err))
     assert x.dtype == torch.float32 and torch.equal(x.cpu(), pl.embed(ids.long().cpu(), table.float()))
     h = torch.randn(3, D).to(dtype)
     logits = head.forward(h.to(DEV), err)
@@ -365,7 +367,9 @@ def test_prenorm_block_alone(dtype):
     src = source(ts, specs, dtype)
     for part in layer.parts.values():
         part.load(src)
-    cache = PagedCache([(layer.mixer.cache_request(), None, None)], 8, 8, 1, 64, dtype, DEV)
+    from ai_engine_b200.parts import CacheNeed
+    assert [n[0] for n in layer.cache_needs()] == ["mixer"]
+    cache = PagedCache([CacheNeed(0, "mixer", layer.parts["mixer"].cache_request())], 8, 8, 1, 64, dtype, DEV)
     slot = cache.admit()
     cache.ensure(slot, S)
     ctx, err = _step_ctx(cache, slot, 0, S)

@@ -9,20 +9,44 @@ import pytest
 import torch
 
 import plain_llama as pl
-from helpers import TINY_A, TINY_B, make_model_dir, random_ids
+from helpers import (FIXTURE_DIR, FIXTURE_PROMPT, TINY_A, TINY_B, fixture_reference_logits, fixture_tensors,
+                     make_model_dir, random_ids)
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def test_golden_fixture_of_the_reference():
-    """Committed by tests/golden/make_reference_fixture_check.py: the reference's
-    reference_logits.bin against the plain implementation on the Q8 fixture, under the
-    reference's own Q8 gate (crates/ai-engine-runtime/tests/quant_reference_logits.rs:67-82)."""
-    ref = np.fromfile(os.path.join(HERE, "golden", "toy_q8_reference_logits.f32"), dtype="<f4")
-    got = np.fromfile(os.path.join(HERE, "golden", "toy_q8_plain_logits.f32"), dtype="<f4")
+    """The reference's reference_logits.bin against the plain implementation, run now, on the reference's
+    Q8 fixture (dequantised), under the reference's own Q8 gate
+    (crates/ai-engine-runtime/tests/quant_reference_logits.rs:67-82: max |a - b| < 3e-2, equal argmax)."""
+    ref = fixture_reference_logits()
+    got = pl.forward(fixture_tensors(), pl.read_config(FIXTURE_DIR), FIXTURE_PROMPT)[-1].numpy()
     assert ref.shape == got.shape == (512,)
-    assert np.abs(ref - got).max() < 3e-2
+    assert np.abs(ref - got).max() < 3e-2, np.abs(ref - got).max()
     assert int(ref.argmax()) == int(got.argmax()) == 150
+    # float64 changes nothing that the gate could see: the difference is the quantisation's
+    w64 = {k: v.double() for k, v in fixture_tensors().items()}
+    got64 = pl.forward(w64, pl.read_config(FIXTURE_DIR), FIXTURE_PROMPT)[-1].numpy()
+    assert np.abs(got64 - got).max() < 1e-5
+
+
+def test_llama3_scaling_values():
+    """llama3 scaling is not in the reference; the values below were worked out by hand from the rule that
+    the config keys name, for head size 8, theta 10000, factor 4, low 1, high 4, original 32: wavelengths
+    2*pi / [1, 0.1, 0.01, 0.001] = [6.28, 62.8, 628, 6283]; below 32/4 = 8: kept; above 32/1 = 32: divided
+    by 4; (none falls between).  And for original 256: bounds 64 and 256, so 62.8 is kept, 628 and 6283 are
+    divided; with original 400 (bounds 100 and 400): 62.8 is kept; with original 100 (bounds 25, 100):
+    62.8 lies between: s = (100 / 62.83 - 1) / 3 = 0.19718, value = (1 - s) * 0.1 / 4 + s * 0.1 = 0.039789."""
+    sc = lambda orig: dict(rope_type="llama3", factor=4.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                           original_max_position_embeddings=orig)
+    assert np.allclose(pl.inv_freq_default(8, 10000.0), [1.0, 0.1, 0.01, 0.001], rtol=1e-6)
+    assert np.allclose(pl.inv_freq_llama3(8, 10000.0, sc(32)), [1.0, 0.025, 0.0025, 0.00025], rtol=1e-6)
+    assert np.allclose(pl.inv_freq_llama3(8, 10000.0, sc(256)), [1.0, 0.1, 0.0025, 0.00025], rtol=1e-6)
+    s = (100.0 / (2 * math.pi / 0.1) - 1.0) / 3.0
+    assert abs(s - 0.19718) < 1e-5
+    assert np.allclose(pl.inv_freq_llama3(8, 10000.0, sc(100)),
+                       [1.0, (1 - s) * 0.025 + s * 0.1, 0.0025, 0.00025], rtol=1e-6)
+    assert abs(float(pl.inv_freq_llama3(8, 10000.0, sc(100))[1]) - 0.039789) < 1e-6
 
 
 def test_rope_position_zero_is_identity_and_positions_differ():
@@ -91,6 +115,14 @@ def test_logits_at_a_position_do_not_depend_on_later_tokens(tmp_path):
     full = pl.forward_dir(d, ids, torch.float64)
     for n in (1, 2, 9, 17):
         assert torch.allclose(pl.forward_dir(d, ids[:n], torch.float64), full[:n], atol=1e-12)
+
+
+def test_chosen_rows_are_the_rows_of_the_whole(tmp_path):
+    d = make_model_dir(tmp_path, "B")
+    ids = random_ids(40, TINY_B["vocab_size"], 2)
+    full = pl.forward_dir(d, ids, torch.float64)
+    rows = torch.tensor([0, 7, 38, 39])
+    assert torch.allclose(pl.forward_dir(d, ids, torch.float64, rows=rows), full[rows], atol=1e-12)
 
 
 def test_window_masks_old_keys():

@@ -12,8 +12,8 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import (TINY, TOL_BF16, TOL_F32, TOL_F32_SCHEDULES, make_model_dir, plain_logits,
-                     random_ids)
+from helpers import (FIXTURE_PROMPT, TINY, TOL_BF16, TOL_F32, TOL_F32_SCHEDULES, fixture_reference_logits,
+                     make_fixture_dir, make_model_dir, plain_logits, random_ids)
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -40,7 +40,7 @@ def whole(rep, rid, ids):
 
 
 CASES = [("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16"),
-         ("D", "float32"), ("D", "bfloat16"), ("E", "bfloat16")]
+         ("D", "float32"), ("D", "bfloat16"), ("E", "bfloat16"), ("Q", "float32"), ("Q", "bfloat16")]
 
 
 @pytest.mark.parametrize("name,dtype", CASES)
@@ -167,6 +167,41 @@ def test_mixed_requests_with_pages_used_again(tmp_path, name, dtype):
     assert rep.cache.book.pages_in_use(0) == 0
 
 
+@pytest.mark.parametrize("stored,dtype", [("float32", "float32"), ("bfloat16", "float32"), ("bfloat16", "bfloat16")])
+def test_the_references_fixture_through_the_engine(tmp_path, stored, dtype):
+    """The reference's golden fixture as a model folder (dequantised; tied with only lm_head stored;
+    rope_theta under rope_parameters): the engine's logits at the prompt's last position against the
+    reference's reference_logits.bin under the reference's own gate for this fixture
+    (crates/ai-engine-runtime/tests/quant_reference_logits.rs:67-82: 3e-2, argmax 150), and at every position
+    against the plain implementation, however the four tokens are cut and whatever runs beside them."""
+    d = make_fixture_dir(tmp_path, stored)
+    ref_last = fixture_reference_logits().astype(np.float64)
+    ids = FIXTURE_PROMPT
+    oracle = plain_logits(d, ids, oracle_dtype(dtype))
+    other = random_ids(70, 512, 3)
+    tol = tol_for(dtype)
+    rep = replayer(d, dtype, "Q", max_tokens=256)
+    runs = {"whole": whole(rep, "w", ids)}
+    runs["three_and_one"] = np.concatenate([
+        rep.run_step([dict(id="a", tokens=ids[:3], want=[0, 1, 2])]).numpy(),
+        rep.run_step([dict(id="a", tokens=ids[3:], want=[0])], end=["a"]).numpy()]).astype(np.float64)
+    runs["two_and_two"] = np.concatenate([
+        rep.run_step([dict(id="b", tokens=ids[:2], want=[0, 1])]).numpy(),
+        rep.run_step([dict(id="b", tokens=ids[2:], want=[0, 1])], end=["b"]).numpy()]).astype(np.float64)
+    out = [rep.run_step([dict(id="o", tokens=other[:40], want=[]), dict(id="c", tokens=ids[:2], want=[0, 1])]).numpy()]
+    out.append(rep.run_step([dict(id="c", tokens=ids[2:3], want=[0]), dict(id="o", tokens=other[40:69], want=[])]).numpy())
+    out.append(rep.run_step([dict(id="o", tokens=other[69:], want=[]), dict(id="c", tokens=ids[3:], want=[0])],
+                            end=["o", "c"]).numpy())
+    runs["mixed"] = np.concatenate(out).astype(np.float64)
+    for how, got in runs.items():
+        assert got.shape == oracle.shape
+        assert np.abs(got - oracle).max() <= tol, (how, np.abs(got - oracle).max())
+        assert int(got[-1].argmax()) == int(ref_last.argmax()) == 150, how
+        if stored == "float32":          # the weights as the reference's Q8 path has them: its own gate
+            assert np.abs(got[-1] - ref_last).max() < 3e-2, (how, np.abs(got[-1] - ref_last).max())
+    assert rep.cache.book.pages_in_use(0) == 0
+
+
 def test_trace_run_program(tmp_path):
     """bin/trace_run as a user starts it: JSON lines in, <step>.f32 out, `done <step>`."""
     d = make_model_dir(tmp_path, "A")
@@ -205,12 +240,20 @@ FULL_SIZE_LAYERS = {
 }
 
 
+# float32 at full width against the float64 plain implementation: the engine sums K = 14,336 products in
+# one float32 accumulator in a fixed order; measured on a B200 the largest difference of a logit is
+# F32_FULL_WIDTH_MEASURED (logits up to 3); the gate leaves a factor of four above it.
+F32_FULL_WIDTH_MEASURED = 5e-4
+F32_FULL_WIDTH_TOL = 4 * F32_FULL_WIDTH_MEASURED
+
+
 @pytest.mark.parametrize("name", sorted(FULL_SIZE_LAYERS))
 def test_full_size_layers(tmp_path, name):
     """Layers with the sizes of Llama-3-8B (three of them), Llama-3.2-3B and Llama-3.2-1B (one each; a reduced
     vocabulary keeps the folder small): the kernel configurations that full-size models take — products cut along K, tcgen05
     attention, grouped decode — against the plain implementation: a request whole, in portions and token by
-    token, with a second request's tokens in the same steps."""
+    token, with other requests' tokens in the same steps; one step of more than 64 tokens holds two prompt
+    portions and a lone decoded token (library products, the tcgen05 prompt kernel and the decode kernel side by side)."""
     import ai_engine_b200 as aie
     from ai_engine_b200.engine.replay import Replayer
 
@@ -218,25 +261,68 @@ def test_full_size_layers(tmp_path, name):
                rope_theta=500000.0, rms_norm_eps=1e-5, max_position_embeddings=8192, **FULL_SIZE_LAYERS[name])
     d = os.path.join(str(tmp_path), name)
     aie.write_random_model(aie.LlamaConfig.from_dict(raw), d, seed=5, dtype="bfloat16")
-    ids, other = random_ids(200, 4096, 31), random_ids(70, 4096, 32)
+    seqs = {"x": random_ids(200, 4096, 31), "y": random_ids(70, 4096, 32), "z": random_ids(41, 4096, 33)}
+    for dtype, odt in (("bfloat16", torch.float32), ("float32", torch.float64)):
+        refs = {k: plain_logits(d, v, odt) for k, v in seqs.items()}
+        scale = max(1.0, max(float(np.abs(r).max()) for r in refs.values()))
+        tol = TOL_BF16 * scale if dtype == "bfloat16" else F32_FULL_WIDTH_TOL * scale
+        rep = Replayer(d, dtype, max_tokens=448, block_size=16)
+        got = {k: [] for k in seqs}
+        fed = {k: 0 for k in seqs}
+
+        def step(*portions):
+            entries = [dict(id=k, tokens=seqs[k][fed[k]:fed[k] + n], want=list(range(n))) for k, n in portions]
+            out = rep.run_step(entries).numpy()
+            row = 0
+            for k, n in portions:
+                got[k].append(out[row:row + n])
+                fed[k] += n
+                row += n
+
+        step(("x", 150), ("z", 30))
+        step(("x", 40), ("y", 60), ("z", 1))          # 101 tokens: two portions and a lone decoded token
+        for _ in range(10):
+            step(("y", 1), ("x", 1), ("z", 1))
+        worst = 0.0
+        for k in seqs:
+            err = np.abs(np.concatenate(got[k]) - refs[k]).max(axis=1)
+            worst = max(worst, float(err.max()))
+            assert err.max() <= tol, (f"{dtype}, request {k}: first wrong token {int(np.argmax(err > tol))}: "
+                                      f"{err.max()} (gate {tol}, logits up to {scale})")
+        print(f"full-size layers {name} {dtype}: largest difference {worst:.3e} (gate {tol:.3e}, logits up to {scale:.2f})")
+
+
+def test_the_real_vocabulary_of_llama3_8b(tmp_path):
+    """One layer of Llama-3-8B's sizes with its real vocabulary of 128,256 (untied: a 1 GB embedding and a 1 GB
+    head of 1,002 weight tiles, the one product of a decode step that is not cut along K): logits rows of a
+    prompt portion, of a mixed step and of decoded tokens against the plain implementation, in both dtypes."""
+    import ai_engine_b200 as aie
+    from ai_engine_b200.engine.replay import Replayer
+
+    raw = dict(architectures=["LlamaForCausalLM"], num_hidden_layers=1, vocab_size=128256, rope_theta=500000.0,
+               rms_norm_eps=1e-5, max_position_embeddings=8192, **FULL_SIZE_LAYERS["llama3_8b"])
+    d = os.path.join(str(tmp_path), "vocab128256")
+    aie.write_random_model(aie.LlamaConfig.from_dict(raw), d, seed=6, dtype="bfloat16")
+    rng = np.random.RandomState(3)
+    ids = [int(t) for t in rng.randint(0, 128256, size=28)]
+    ids[3], ids[20] = 128255, 0                       # the table's last and first rows
+    other = [int(t) for t in rng.randint(0, 128256, size=9)]
     ref, ref_other = plain_logits(d, ids, torch.float32), plain_logits(d, other, torch.float32)
     scale = max(1.0, float(np.abs(ref).max()))
-    for dtype, tol in (("bfloat16", TOL_BF16 * scale), ("float32", 2e-3 * scale)):
-        rep = Replayer(d, dtype, max_tokens=320, block_size=16)
-        got = [rep.run_step([dict(id="x", tokens=ids[:150], want=list(range(150)))]).numpy()]
-        out = rep.run_step([dict(id="x", tokens=ids[150:190], want=list(range(40))),
-                            dict(id="y", tokens=other[:60], want=list(range(60)))]).numpy()
-        got.append(out[:40])
-        got_other = [out[40:]]
-        for k in range(10):
-            out = rep.run_step([dict(id="y", tokens=[other[60 + k]], want=[0]),
-                                dict(id="x", tokens=[ids[190 + k]], want=[0])]).numpy()
-            got_other.append(out[:1])
-            got.append(out[1:])
-        for what, g, r in (("x", got, ref), ("y", got_other, ref_other)):
-            err = np.abs(np.concatenate(g) - r).max(axis=1)
-            assert err.max() <= tol, (f"{dtype}, request {what}: first wrong token {int(np.argmax(err > tol))}: "
-                                      f"{err.max()} (logits up to {scale})")
+    for dtype, tol in (("bfloat16", TOL_BF16 * scale), ("float32", F32_FULL_WIDTH_TOL * scale)):
+        rep = Replayer(d, dtype, max_tokens=128, block_size=16)
+        got = [rep.run_step([dict(id="x", tokens=ids[:20], want=[0, 3, 19])]).numpy()]
+        out = rep.run_step([dict(id="x", tokens=[ids[20]], want=[0]), dict(id="y", tokens=other, want=[8])]).numpy()
+        got.append(out[:1])
+        for t in ids[21:]:
+            got.append(rep.run_step([dict(id="x", tokens=[t], want=[0])]).numpy())
+        g = np.concatenate(got)
+        assert g.shape == (3 + 1 + 7, 128256)
+        err = np.abs(g - ref[[0, 3, 19] + list(range(20, 28))]).max(axis=1)
+        assert err.max() <= tol, f"{dtype}: {err} (gate {tol})"
+        assert np.abs(out[1] - ref_other[8]).max() <= tol
+        del rep
+        torch.cuda.empty_cache()
 
 
 ODD_SIZES = {

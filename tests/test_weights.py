@@ -122,3 +122,43 @@ def test_truncated_file_and_missing_folder(tmp_path):
     with pytest.raises(WeightError) as e:
         ModelFolder(str(tmp_path / "empty"))
     assert "no *.safetensors" in str(e.value)
+
+
+def test_integer_stored_weights_are_refused_at_load_by_name(tmp_path):
+    """A quantised file (int8 weights with scales beside them, as the reference's Q8 fixture) does not reach
+    a kernel: the load fails with the tensors' names (crates/ai-engine-runtime/src/loader.rs:733-750 refuses
+    dtypes it does not take at load as well)."""
+    import shutil
+
+    from helpers import FIXTURE_DIR
+    from ai_engine_b200.config import load_config
+    from ai_engine_b200.parts import tensor_specs_of
+    from ai_engine_b200.weights import ModelFolder
+
+    d = tmp_path / "q8"
+    d.mkdir()
+    for f in ("config.json", "model.safetensors"):
+        shutil.copy(os.path.join(FIXTURE_DIR, f), d / f)
+    arch, cfg = load_config(str(d))
+    folder = ModelFolder(str(d))
+    available = {n: folder.info(n) for n in folder.names()}
+    with pytest.raises(WeightError) as e:
+        check_and_resolve(tensor_specs_of(arch.build_spec(cfg)), available)
+    msg = str(e.value)
+    assert "wrong dtypes (29)" in msg and "lm_head.weight: stored as int8" in msg
+    assert "unexpected tensors (29)" in msg and "lm_head.weight.scale" in msg
+    folder.close()
+
+
+def test_buffers_that_are_no_parameters_are_passed_over():
+    """An older export stores `rotary_emb.inv_freq` in every layer; the architecture names it as ignorable."""
+    from ai_engine_b200.models.llama import build_llama_spec
+    from ai_engine_b200.parts import tensor_specs_of
+
+    spec = build_llama_spec(LlamaConfig.from_dict(TINY_A))
+    specs = tensor_specs_of(spec)
+    available = {s.name: (torch.bfloat16, s.shape) for s in specs}
+    available["model.layers.0.self_attn.rotary_emb.inv_freq"] = (torch.float32, (8,))
+    check_and_resolve(specs, available, ignored=spec.ignored_tensors)
+    with pytest.raises(WeightError, match="unexpected tensors"):
+        check_and_resolve(specs, available)

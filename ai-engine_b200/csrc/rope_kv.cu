@@ -81,11 +81,33 @@ __global__ void rope_kv_write_kernel(const I* __restrict__ qkv, int parts, size_
     }
 }
 
-// Portions of prompts in bfloat16: one block per token.  The token's angles are computed once
+// Eight consecutive elements as floats (the address is 8-element aligned).
+__device__ __forceinline__ void load8(const bf16* p, float* f) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const bf16* e = reinterpret_cast<const bf16*>(&a);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(e[i]);
+}
+__device__ __forceinline__ void load8(const float* p, float* f) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
+}
+__device__ __forceinline__ void store8(bf16* p, const float* f) {
+    uint4 o;
+    bf16* e = reinterpret_cast<bf16*>(&o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) e[i] = __float2bfloat16_rn(f[i]);
+    *reinterpret_cast<uint4*>(p) = o;
+}
+
+// Portions of prompts with a bfloat16 cache: one block per token.  The token's angles are computed once
 // (float32, the same expression as above) and kept in shared memory; every thread rotates 8 pairs
-// of one head with 16-byte loads and stores.  Needs rot_dim % 16 == 0 and d % 8 == 0.
+// of one head with 16-byte loads and stores.  The projection comes in bfloat16 or in float32 (the
+// product's accumulators, so that q and k are rounded once, after the rotation, as in small steps).
+// Needs rot_dim % 16 == 0 and d % 8 == 0.
+template <typename I>
 __global__ void __launch_bounds__(256)
-rope_kv_write_token_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf16* __restrict__ k_pages,
+rope_kv_write_token_kernel(const I* __restrict__ qkv, bf16* __restrict__ q_out, bf16* __restrict__ k_pages,
                            bf16* __restrict__ v_pages, const int* __restrict__ positions,
                            const int* __restrict__ token_req, const int* __restrict__ block_table, int bt_width,
                            int num_pages, int P, int H, int K, int d, int rot_dim,
@@ -112,42 +134,41 @@ rope_kv_write_token_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_ou
         }
     }
     __syncthreads();
-    const bf16* x = qkv + (size_t)t * (H + 2 * K) * d;
+    const I* x = qkv + (size_t)t * (H + 2 * K) * d;
     const size_t slot = page >= 0 ? ((size_t)page * K * P + (pos % P)) * d : 0;      // + kv head * P * d
     const int cph = half / 8, heads = H + (page >= 0 ? K : 0);
     for (int w = tid; w < heads * cph; w += blockDim.x) {
         const int head = w / cph, c = (w % cph) * 8;
-        const bf16* src = x + (size_t)head * d + c;
+        const I* src = x + (size_t)head * d + c;
         bf16* dst = head < H ? q_out + ((size_t)t * H + head) * d + c : k_pages + slot + (size_t)(head - H) * P * d + c;
-        const uint4 a = *reinterpret_cast<const uint4*>(src), b = *reinterpret_cast<const uint4*>(src + half);
-        const bf16* x1 = reinterpret_cast<const bf16*>(&a);
-        const bf16* x2 = reinterpret_cast<const bf16*>(&b);
-        uint4 oa, ob;
-        bf16* o1 = reinterpret_cast<bf16*>(&oa);
-        bf16* o2 = reinterpret_cast<bf16*>(&ob);
+        float x1[8], x2[8], o1[8], o2[8];
+        load8(src, x1);
+        load8(src + half, x2);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             const float cs = rope_cs[c + e], sn = rope_cs[half + c + e];
-            const float u = to_f32<bf16>(x1[e]), v = to_f32<bf16>(x2[e]);
-            o1[e] = from_f32<bf16>(u * cs - v * sn);
-            o2[e] = from_f32<bf16>(u * sn + v * cs);
+            o1[e] = x1[e] * cs - x2[e] * sn;
+            o2[e] = x1[e] * sn + x2[e] * cs;
         }
-        *reinterpret_cast<uint4*>(dst) = oa;
-        *reinterpret_cast<uint4*>(dst + half) = ob;
+        store8(dst, o1);
+        store8(dst + half, o2);
     }
-    // what is not rotated: the tails of q and k heads, and the v heads (16-byte copies)
+    // what is not rotated: the tails of q and k heads, and the v heads
     const int tail = (d - rot_dim) / 8;
     for (int w = tid; w < heads * tail; w += blockDim.x) {
         const int head = w / tail, c = rot_dim + (w % tail) * 8;
         bf16* dst = head < H ? q_out + ((size_t)t * H + head) * d + c : k_pages + slot + (size_t)(head - H) * P * d + c;
-        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(x + (size_t)head * d + c);
+        float v[8];
+        load8(x + (size_t)head * d + c, v);
+        store8(dst, v);
     }
     if (page >= 0) {
         const int dc = d / 8;
         for (int w = tid; w < K * dc; w += blockDim.x) {
             const int kh = w / dc, c = (w % dc) * 8;
-            *reinterpret_cast<uint4*>(v_pages + slot + (size_t)kh * P * d + c) =
-                *reinterpret_cast<const uint4*>(x + (size_t)(H + K + kh) * d + c);
+            float v[8];
+            load8(x + (size_t)(H + K + kh) * d + c, v);
+            store8(v_pages + slot + (size_t)kh * P * d + c, v);
         }
     }
 }
@@ -159,16 +180,21 @@ extern "C" int aie_rope_kv_write(const void* qkv, int in_dtype, int parts, long 
                                  int write, unsigned* err, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (rot_dim % 2 || rot_dim > d || rot_dim < 0) return AIE_BAD_ARG;
-    if (T >= 64 && dtype == AIE_BF16 && in_dtype == AIE_BF16 && parts == 1 && rot_dim % 16 == 0 && d % 8 == 0 &&
+    if (T >= 64 && dtype == AIE_BF16 && parts == 1 && rot_dim % 16 == 0 && d % 8 == 0 &&
         !((size_t)qkv & 15) && !((size_t)q_out & 15) && !((size_t)k_pages & 15) && !((size_t)v_pages & 15))
     {
         // one pass over the token's rotated chunks when they fit a block: (H + K) heads x rot_dim / 16 chunks
         int threads = ((H + K) * (rot_dim / 16) + 31) / 32 * 32;
         threads = threads < 64 ? 64 : (threads > 256 ? ((threads + 1) / 2 + 31) / 32 * 32 : threads);
         if (threads > 256) threads = 256;
-        return (int)launch_pdl(rope_kv_write_token_kernel, dim3(T), dim3(threads), (size_t)rot_dim * sizeof(float), stream,
-                               (const bf16*)qkv, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, positions, token_req,
-                               block_table, bt_width, num_pages, P, H, K, d, rot_dim, inv_freq, write, err);
+        if (in_dtype == AIE_BF16)
+            return (int)launch_pdl(rope_kv_write_token_kernel<bf16>, dim3(T), dim3(threads), (size_t)rot_dim * sizeof(float),
+                                   stream, (const bf16*)qkv, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, positions,
+                                   token_req, block_table, bt_width, num_pages, P, H, K, d, rot_dim, inv_freq, write, err);
+        if (in_dtype == AIE_F32)
+            return (int)launch_pdl(rope_kv_write_token_kernel<float>, dim3(T), dim3(threads), (size_t)rot_dim * sizeof(float),
+                                   stream, (const float*)qkv, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, positions,
+                                   token_req, block_table, bt_width, num_pages, P, H, K, d, rot_dim, inv_freq, write, err);
     }
     // few tokens: one warp per block, so that the work spreads over the machine; many: 8 warps
     const int warps = T >= 256 ? 8 : 1;

@@ -5,7 +5,7 @@ what an engine without a server needs: token ids in, token ids out.
     ai-engine --model DIR [--config provider.toml|json] [--check]
               (--prompt-ids 1,2,3 | --prompt-file prompts.jsonl)
               [--max-tokens N] [--temperature T] [--top-k K] [--top-p P] [--seed S]
-              [--ignore-eos] [--stats]
+              [--ignore-eos] [--stats] [--profile [--peaks GB/s,TFLOP/s]]
 
 The config file is the local-provider block of the reference's ai-engine.toml
 (crates/ai-engine-config/src/lib.rs:97-140): either a `[[provider]]` table (the
@@ -72,6 +72,12 @@ def parse_args(argv=None):
     ap.add_argument("--ignore-eos", action="store_true")
     ap.add_argument("--dtype", choices=["bf16", "fp32", "bfloat16", "float32"], default=None)
     ap.add_argument("--stats", action="store_true", help="print engine counters to stderr at the end")
+    ap.add_argument("--profile", action="store_true",
+                    help="time every kernel launch with CUDA events (eager launches, no graphs) and print "
+                         "time, bytes, flops and roofline fraction per class of kernel to stderr")
+    ap.add_argument("--peaks", default="7700,2250",
+                    help="memory bandwidth in GB/s and bf16 TFLOP/s that --profile's fractions are taken "
+                         "against (default: the B200's nominal 7700,2250)")
     return ap.parse_args(argv)
 
 
@@ -115,11 +121,17 @@ def main(argv=None) -> int:
         from ..sampling.params import SamplingParams
         from .engine import Engine
 
+        if args.profile:
+            from ..kernels import profile
+            profile.start()
         engine = Engine(None, **options)
         sp = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                             seed=args.seed, max_tokens=args.max_tokens, ignore_eos=args.ignore_eos)
         for out in engine.generate(prompts, sp):
             print(",".join(str(t) for t in out), flush=True)
+        if args.profile:
+            gbs, tf = (float(x) for x in args.peaks.split(","))
+            print(profile.table(profile.stop(gbs, tf)), file=sys.stderr)
         if args.stats:
             print(json.dumps(engine.stats()), file=sys.stderr)
         return 0

@@ -225,8 +225,9 @@ class StepRunner:
         self.last_ctx: Optional[StepContext] = None
         self.buffers: dict = {"staging": _Staging(self.device.type == "cuda")}
         if use_graphs is None:
+            from ..kernels import profile
             use_graphs = (model.dtype == torch.bfloat16 and not model.has_host_parts()
-                          and not os.environ.get("AI_ENGINE_B200_NO_GRAPHS"))
+                          and not os.environ.get("AI_ENGINE_B200_NO_GRAPHS") and not profile.enabled())
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
         # decode steps are rounded up by repeating a row only if every part that keeps state skips such rows
         self.pad_decode = model.pads_decode_rows() if hasattr(model, "pads_decode_rows") else True

@@ -10,6 +10,7 @@ from typing import Optional
 import torch
 
 from .loader import KernelError, check, library, require_cuda
+from .profile import enabled as _profiling, region
 
 F32, BF16 = 0, 1
 
@@ -36,6 +37,11 @@ def _stream():
     if _raw_stream is not None:
         return c_void_p(_raw_stream(0))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _nb(*ts) -> int:
+    """Bytes of the given tensors (what a kernel that touches each once has to move)."""
+    return sum(t.numel() * t.element_size() for t in ts if t is not None)
 
 
 def _dev(*ts):
@@ -66,8 +72,9 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, err: torch.Tensor,
     if out is None:
         out = torch.empty((T, D), dtype=torch.float32, device=table.device)
     lib = library("elementwise.cu")
-    check(lib.aie_embed_gather(_p(ids), _p(table), c_int(dtype_code(table)), _p(out), c_int(T),
-                               c_int(D), c_int(V), _p(err), _stream()), "embed_gather")
+    with region("embed_gather", T * D * table.element_size() + _nb(out)):
+        check(lib.aie_embed_gather(_p(ids), _p(table), c_int(dtype_code(table)), _p(out), c_int(T),
+                                   c_int(D), c_int(V), _p(err), _stream()), "embed_gather")
     return out
 
 
@@ -103,12 +110,14 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
     if out is None:
         out = torch.empty((n, D), dtype=out_dtype, device=x.device)
     lib = library("elementwise.cu")
-    check(lib.aie_add_rmsnorm(_p(x), _p(delta), c_int(dtype_code(delta) if delta is not None else 0),
-                              _p(weight), c_int(dtype_code(weight)), _p(out),
-                              c_int(dtype_code(out)), _p(rows), c_int(n), c_int(D), c_float(eps),
-                              c_int(1 if (write_back and rows is None) else 0), c_int(parts),
-                              c_longlong(part_stride), _stream()),
-          "add_rmsnorm")
+    stored = write_back and rows is None
+    with region("add_rmsnorm", n * D * 4 * (2 if stored else 1) + (_nb(delta) if rows is None else 0) + _nb(out)):
+        check(lib.aie_add_rmsnorm(_p(x), _p(delta), c_int(dtype_code(delta) if delta is not None else 0),
+                                  _p(weight), c_int(dtype_code(weight)), _p(out),
+                                  c_int(dtype_code(out)), _p(rows), c_int(n), c_int(D), c_float(eps),
+                                  c_int(1 if stored else 0), c_int(parts),
+                                  c_longlong(part_stride), _stream()),
+              "add_rmsnorm")
     return out
 
 
@@ -121,8 +130,9 @@ def silu_mul(gu: torch.Tensor, out: Optional[torch.Tensor] = None, block: int = 
     if out is None:
         out = torch.empty((T, F), dtype=gu.dtype, device=gu.device)
     lib = library("elementwise.cu")
-    check(lib.aie_silu_mul(_p(gu), _p(out), c_int(dtype_code(gu)), c_int(T), c_int(F), c_int(block),
-                           _stream()), "silu_mul")
+    with region("silu_mul", _nb(gu, out)):
+        check(lib.aie_silu_mul(_p(gu), _p(out), c_int(dtype_code(gu)), c_int(T), c_int(F), c_int(block),
+                               _stream()), "silu_mul")
     return out
 
 
@@ -132,8 +142,9 @@ def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     _dev(x)
     out = torch.empty(x.shape, dtype=dtype, device=x.device)
     lib = library("elementwise.cu")
-    check(lib.aie_cast(_p(x), c_int(dtype_code(x)), _p(out), c_int(dtype_code(out)),
-                       c_longlong(x.numel()), _stream()), "cast")
+    with region("cast", _nb(x, out)):
+        check(lib.aie_cast(_p(x), c_int(dtype_code(x)), _p(out), c_int(dtype_code(out)),
+                           c_longlong(x.numel()), _stream()), "cast")
     return out
 
 
@@ -152,8 +163,9 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, rows: Optional[torch.Tensor] = No
     if out is None:
         out = torch.empty((M, N), dtype=torch.float32, device=a.device)
     lib = library("gemm_f32.cu")
-    check(lib.aie_gemm_f32(_p(a), _p(w), c_int(dtype_code(w)), _p(out), _p(rows), c_int(M), c_int(N),
-                           c_int(K), c_int(out.stride(0)), _stream()), "gemm_f32")
+    with region("gemm_f32", _nb(w, out) + M * K * 4, 2.0 * M * N * K):
+        check(lib.aie_gemm_f32(_p(a), _p(w), c_int(dtype_code(w)), _p(out), _p(rows), c_int(M), c_int(N),
+                               c_int(K), c_int(out.stride(0)), _stream()), "gemm_f32")
     return out
 
 
@@ -208,9 +220,10 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, err: torch
         splits = min(splits, 8)              # joined inside a cluster of at most 8 CTAs
         out = torch.empty((T, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
     lib = library("gemm_tc.cu")
-    check(lib.aie_gemm_tc(_p(x), _p(w), _p(out), c_int(dtype_code(out)), c_int(T), c_int(N), c_int(K),
-                          c_int(out.stride(-2)), c_int(bn), c_int(splits), c_int(1 if swiglu else 0),
-                          c_int(1 if raw_parts else 0), _p(err), _stream()), "gemm_tc")
+    with region("gemm_tc_swiglu" if swiglu else "gemm_tc", _nb(x, w, out), 2.0 * T * N * K):
+        check(lib.aie_gemm_tc(_p(x), _p(w), _p(out), c_int(dtype_code(out)), c_int(T), c_int(N), c_int(K),
+                              c_int(out.stride(-2)), c_int(bn), c_int(splits), c_int(1 if swiglu else 0),
+                              c_int(1 if raw_parts else 0), _p(err), _stream()), "gemm_tc")
     return out
 
 
@@ -247,9 +260,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         if y is not None:
             return y
     _dev(x, w)
-    if out_dtype == torch.float32:
-        return torch.mm(x, w.t(), out_dtype=torch.float32)
-    return torch.mm(x, w.t())
+    with region("gemm_library", _nb(x, w) + x.shape[0] * w.shape[0] * (4 if out_dtype == torch.float32 else 2),
+                2.0 * x.shape[0] * w.shape[0] * w.shape[1]):
+        if out_dtype == torch.float32:
+            return torch.mm(x, w.t(), out_dtype=torch.float32)
+        return torch.mm(x, w.t())
 
 
 def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor, block: int = 0,
@@ -290,11 +305,12 @@ def linear_rope_kv(x: torch.Tensor, w_qkv: torch.Tensor, k_pages: torch.Tensor, 
     splits = -(-kb // -(-kb // splits))
     q_out = torch.empty((T, H, d), dtype=torch.bfloat16, device=x.device)
     lib = library("gemm_tc.cu")
-    check(lib.aie_gemm_tc_rope(_p(x), _p(w_qkv), c_int(T), c_int(N), c_int(Kin), c_int(bn), c_int(splits),
-                               _p(q_out), _p(k_pages), _p(v_pages), _p(positions), _p(token_req),
-                               _p(block_table), c_int(block_table.shape[1]), c_int(num_pages), c_int(P),
-                               c_int(H), c_int(K), c_int(d), _p(inv_freq), c_int(1 if write else 0), _p(err),
-                               _stream()), "gemm_tc_rope")
+    with region("gemm_tc_rope", _nb(x, w_qkv) + T * N * 2, 2.0 * T * N * Kin):
+        check(lib.aie_gemm_tc_rope(_p(x), _p(w_qkv), c_int(T), c_int(N), c_int(Kin), c_int(bn), c_int(splits),
+                                   _p(q_out), _p(k_pages), _p(v_pages), _p(positions), _p(token_req),
+                                   _p(block_table), c_int(block_table.shape[1]), c_int(num_pages), c_int(P),
+                                   c_int(H), c_int(K), c_int(d), _p(inv_freq), c_int(1 if write else 0), _p(err),
+                                   _stream()), "gemm_tc_rope")
     return q_out
 
 
@@ -321,12 +337,13 @@ def rope_kv_write(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     if q_out is None:
         q_out = torch.empty((T, H, d), dtype=k_pages.dtype, device=qkv.device)
     lib = library("rope_kv.cu")
-    check(lib.aie_rope_kv_write(_p(qkv), c_int(dtype_code(qkv)), c_int(parts), c_longlong(part_stride),
-                                _p(q_out), _p(k_pages), _p(v_pages), c_int(dtype_code(k_pages)),
-                                _p(positions), _p(token_req), _p(block_table),
-                                c_int(block_table.shape[1]), c_int(num_pages), c_int(P), c_int(T),
-                                c_int(H), c_int(K), c_int(d), c_int(rot), _p(inv_freq),
-                                c_int(1 if write else 0), _p(err), _stream()), "rope_kv_write")
+    with region("rope_kv_write", _nb(qkv) + T * (H + 2 * K) * d * k_pages.element_size()):
+        check(lib.aie_rope_kv_write(_p(qkv), c_int(dtype_code(qkv)), c_int(parts), c_longlong(part_stride),
+                                    _p(q_out), _p(k_pages), _p(v_pages), c_int(dtype_code(k_pages)),
+                                    _p(positions), _p(token_req), _p(block_table),
+                                    c_int(block_table.shape[1]), c_int(num_pages), c_int(P), c_int(T),
+                                    c_int(H), c_int(K), c_int(d), c_int(rot), _p(inv_freq),
+                                    c_int(1 if write else 0), _p(err), _stream()), "rope_kv_write")
     return q_out
 
 
@@ -334,7 +351,7 @@ def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
                           positions: torch.Tensor, token_req: torch.Tensor,
                           block_table: torch.Tensor, scale: float, window: int, err: torch.Tensor,
                           out: Optional[torch.Tensor] = None,
-                          token_list: Optional[torch.Tensor] = None) -> torch.Tensor:
+                          token_list: Optional[torch.Tensor] = None, cost=(0.0, 0.0)) -> torch.Tensor:
     """softmax(q.k * scale over keys j <= pos (and j > pos - window)) . v per query
     token and head, keys read through the block table.  q, out: [T, H, d].
     `token_list`: only these tokens are computed (the others' rows of out are left)."""
@@ -348,14 +365,15 @@ def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
     if out is None:
         out = torch.empty_like(q)
     lib = library("attention_plain.cu")
-    check(lib.aie_paged_attention_plain(_p(q), _p(k_pages), _p(v_pages), _p(out),
-                                        c_int(dtype_code(q)), _p(positions), _p(token_req),
-                                        _p(block_table), c_int(block_table.shape[1]),
-                                        c_int(num_pages), c_int(P),
-                                        c_int(T if token_list is None else token_list.shape[0]),
-                                        c_int(H), c_int(K), c_int(d), c_int(window), c_float(scale),
-                                        _p(token_list), _p(err), _stream()),
-          "paged_attention_plain")
+    with region("attention_plain", *cost):
+        check(lib.aie_paged_attention_plain(_p(q), _p(k_pages), _p(v_pages), _p(out),
+                                            c_int(dtype_code(q)), _p(positions), _p(token_req),
+                                            _p(block_table), c_int(block_table.shape[1]),
+                                            c_int(num_pages), c_int(P),
+                                            c_int(T if token_list is None else token_list.shape[0]),
+                                            c_int(H), c_int(K), c_int(d), c_int(window), c_float(scale),
+                                            _p(token_list), _p(err), _stream()),
+              "paged_attention_plain")
     return out
 
 
@@ -382,7 +400,7 @@ def _decode_counters(device, n: int):
 
 def paged_attention_decode(q, k_pages, v_pages, dec_tokens, positions, token_req, block_table,
                            scale: float, window: int, splits: int, err, out,
-                           join_in_kernel: bool = False) -> None:
+                           join_in_kernel: bool = False, cost=(0.0, 0.0)) -> None:
     """bfloat16 split-KV attention for the tokens in `dec_tokens` (requests that bring
     one token).  Head sizes 64 and 128.  Uses scratch for the parts when splits > 1; they are
     joined by a second kernel, or (join_in_kernel) by whichever CTA finishes last — measured
@@ -398,19 +416,20 @@ def paged_attention_decode(q, k_pages, v_pages, dec_tokens, positions, token_req
         if join_in_kernel:
             counters = _decode_counters(q.device, n * K * ((H // K + 7) // 8))
     lib = library("attention_fast.cu")
-    check(lib.aie_paged_attention_decode(_p(q), _p(k_pages), _p(v_pages), _p(out), _p(part_o),
-                                         _p(part_lse), _p(dec_tokens), c_int(n), _p(positions),
-                                         _p(token_req), _p(block_table), c_int(block_table.shape[1]),
-                                         c_int(num_pages), c_int(P), c_int(H), c_int(K), c_int(d),
-                                         c_int(window), c_float(scale), c_int(splits), _p(counters),
-                                         _p(err), _stream()), "paged_attention_decode")
+    with region("attention_decode", *cost):
+        check(lib.aie_paged_attention_decode(_p(q), _p(k_pages), _p(v_pages), _p(out), _p(part_o),
+                                             _p(part_lse), _p(dec_tokens), c_int(n), _p(positions),
+                                             _p(token_req), _p(block_table), c_int(block_table.shape[1]),
+                                             c_int(num_pages), c_int(P), c_int(H), c_int(K), c_int(d),
+                                             c_int(window), c_float(scale), c_int(splits), _p(counters),
+                                             _p(err), _stream()), "paged_attention_decode")
 
 
 PREFILL_TILE = 128       # query tokens per CTA of the tensor-core attention kernel
 
 
 def paged_attention_prefill(q, k_pages, v_pages, tiles, q_start, q_len, ctx_len, block_table,
-                            scale: float, window: int, err, out) -> None:
+                            scale: float, window: int, err, out, cost=(0.0, 0.0)) -> None:
     """bfloat16 tensor-core attention for requests that bring more than one token.
     `tiles`: int32 [n, 2] = (request row, offset of a PREFILL_TILE-token tile in its tokens).
     Head sizes 64 and 128."""
@@ -418,16 +437,17 @@ def paged_attention_prefill(q, k_pages, v_pages, tiles, q_start, q_len, ctx_len,
     T, H, d = q.shape
     num_pages, K, P, _ = k_pages.shape
     lib = library("attention_fast.cu")
-    check(lib.aie_paged_attention_prefill(_p(q), _p(k_pages), _p(v_pages), _p(out), _p(tiles),
-                                          c_int(tiles.shape[0]), _p(q_start), _p(q_len), _p(ctx_len),
-                                          _p(block_table), c_int(block_table.shape[1]),
-                                          c_int(num_pages), c_int(P), c_int(H), c_int(K), c_int(d),
-                                          c_int(window), c_float(scale), _p(err), _stream()),
-          "paged_attention_prefill")
+    with region("attention_prefill_mma", *cost):
+        check(lib.aie_paged_attention_prefill(_p(q), _p(k_pages), _p(v_pages), _p(out), _p(tiles),
+                                              c_int(tiles.shape[0]), _p(q_start), _p(q_len), _p(ctx_len),
+                                              _p(block_table), c_int(block_table.shape[1]),
+                                              c_int(num_pages), c_int(P), c_int(H), c_int(K), c_int(d),
+                                              c_int(window), c_float(scale), _p(err), _stream()),
+              "paged_attention_prefill")
 
 
 def paged_attention_prefill_tc(q, k_pages, v_pages, tiles, q_start, q_len, ctx_len, block_table,
-                               scale: float, window: int, err, out) -> bool:
+                               scale: float, window: int, err, out, cost=(0.0, 0.0)) -> bool:
     """The tcgen05 version of paged_attention_prefill (scores and outputs in tensor memory,
     operands by TMA).  Takes head sizes 64 and 128, pages of 8 .. 128 keys that divide 128, no window; returns
     False when it does not take the sizes (nothing was launched)."""
@@ -437,11 +457,12 @@ def paged_attention_prefill_tc(q, k_pages, v_pages, tiles, q_start, q_len, ctx_l
     if d not in (64, 128) or window > 0 or P < 8 or P > 128 or 128 % P:
         return False
     lib = library("attention_prefill_tc.cu")
-    rc = lib.aie_paged_attention_prefill_tc(_p(q), _p(k_pages), _p(v_pages), _p(out), _p(tiles),
-                                            c_int(tiles.shape[0]), _p(q_start), _p(q_len), _p(ctx_len),
-                                            _p(block_table), c_int(block_table.shape[1]),
-                                            c_int(num_pages), c_int(P), c_int(T), c_int(H), c_int(K),
-                                            c_int(d), c_int(window), c_float(scale), _p(err), _stream())
+    with region("attention_prefill_tcgen05", *cost):
+        rc = lib.aie_paged_attention_prefill_tc(_p(q), _p(k_pages), _p(v_pages), _p(out), _p(tiles),
+                                                c_int(tiles.shape[0]), _p(q_start), _p(q_len), _p(ctx_len),
+                                                _p(block_table), c_int(block_table.shape[1]),
+                                                c_int(num_pages), c_int(P), c_int(T), c_int(H), c_int(K),
+                                                c_int(d), c_int(window), c_float(scale), _p(err), _stream())
     if rc == -2:
         return False
     check(rc, "paged_attention_prefill_tc")
@@ -459,19 +480,32 @@ def paged_attention(q, k_pages, v_pages, ctx, work, block_table, scale: float, w
     T, H, d = q.shape
     K = k_pages.shape[1]
     fast = q.dtype == torch.bfloat16 and d in (64, 128)
+    dec_cost = pre_cost = (0.0, 0.0)
+    if _profiling() and hasattr(ctx, "h_q_len"):      # keys read and products done, from the host's lengths
+        ql, cl = ctx.h_q_len.astype(float), ctx.h_ctx_len.astype(float)
+        if window > 0:
+            cl = cl.clip(max=float(window))
+        es = k_pages.element_size()
+        lone = ql == 1
+        keys = float((cl[lone] + 1).sum())
+        dec_cost = (keys * K * d * 2 * es, 4.0 * keys * H * d)
+        pairs = float((ql[~lone] * cl[~lone] + ql[~lone] * (ql[~lone] + 1) / 2).sum())
+        pre_cost = (float((cl[~lone] + ql[~lone]).sum()) * K * d * 2 * es + float(ql[~lone].sum()) * H * d * 2 * es,
+                    4.0 * pairs * H * d)
     if not fast:
         return paged_attention_plain(q, k_pages, v_pages, ctx.positions, ctx.token_req, block_table,
-                                     scale, window, ctx.err)
+                                     scale, window, ctx.err,
+                                     cost=(dec_cost[0] + pre_cost[0], dec_cost[1] + pre_cost[1]))
     out = torch.empty_like(q)
     if work.n_decode:
         keys = work.max_decode_len if window <= 0 else min(window, work.max_decode_len)
         paged_attention_decode(q, k_pages, v_pages, work.decode_tokens, ctx.positions, ctx.token_req,
                                block_table, scale, window,
                                decode_splits(work.n_decode, K, H // K, keys, block_table.shape[1]),
-                               ctx.err, out)
+                               ctx.err, out, cost=dec_cost)
     if work.n_decode < ctx.R:
         if not paged_attention_prefill_tc(q, k_pages, v_pages, work.prefill_tiles, ctx.q_start, ctx.q_len,
-                                          ctx.ctx_len, block_table, scale, window, ctx.err, out):
+                                          ctx.ctx_len, block_table, scale, window, ctx.err, out, cost=pre_cost):
             paged_attention_prefill(q, k_pages, v_pages, work.prefill_tiles, ctx.q_start, ctx.q_len,
-                                    ctx.ctx_len, block_table, scale, window, ctx.err, out)
+                                    ctx.ctx_len, block_table, scale, window, ctx.err, out, cost=pre_cost)
     return out

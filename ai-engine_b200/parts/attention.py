@@ -113,7 +113,10 @@ class GQAAttention(Mixer):
                                cache.block_table, inv_freq, self.H, self.K, self.d, ctx.err,
                                write=cache.writes)
         if q is None:
-            qkv = ops.linear_parts(h, self.w_qkv, ctx.err, self.env.dtype)
+            # the projection reaches the rotation in float32 whatever the step's size (unjoined parts of a
+            # small step, the library product's float32 output of a large one): q and k are rounded to
+            # the cache's dtype once, after the rotation, so a key's bits do not depend on how its prompt was cut
+            qkv = ops.linear_parts(h, self.w_qkv, ctx.err, torch.float32)
             q = ops.rope_kv_write(qkv, cache.k_pages, cache.v_pages, ctx.positions, ctx.token_req,
                                   cache.block_table, inv_freq, self.H, self.K, self.d, ctx.err,
                                   write=cache.writes)

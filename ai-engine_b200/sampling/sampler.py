@@ -8,7 +8,8 @@ import numpy as np
 import torch
 
 from ..kernels.loader import check, library
-from ..kernels.ops import _dev, _p, _stream
+from ..kernels.ops import _dev, _nb, _p, _stream
+from ..kernels.profile import region
 from .params import SamplingParams
 from .rng import uniform
 
@@ -23,9 +24,10 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Te
     N, V = logits.shape
     out = torch.empty(N, dtype=torch.int32, device=logits.device)
     lib = library("sampling.cu")
-    check(lib.aie_sample_rows(_p(logits), c_int(N), c_int(V), c_int(logits.stride(0)),
-                              _p(temperature), _p(top_k), _p(top_p), _p(draws), _p(out), _stream()),
-          "sample_rows")
+    with region("sample_rows", _nb(logits)):
+        check(lib.aie_sample_rows(_p(logits), c_int(N), c_int(V), c_int(logits.stride(0)),
+                                  _p(temperature), _p(top_k), _p(top_p), _p(draws), _p(out), _stream()),
+              "sample_rows")
     return out
 
 
@@ -38,8 +40,9 @@ def argmax_rows(logits: torch.Tensor, scratch) -> torch.Tensor:
     N, V = logits.shape
     out = torch.empty(N, dtype=torch.int32, device=logits.device)
     lib = library("sampling.cu")
-    check(lib.aie_argmax_rows(_p(logits), c_int(N), c_int(V), c_int(logits.stride(0)), _p(scratch[0]), _p(scratch[1]),
-                              _p(out), _stream()), "argmax_rows")
+    with region("argmax_rows", _nb(logits)):
+        check(lib.aie_argmax_rows(_p(logits), c_int(N), c_int(V), c_int(logits.stride(0)), _p(scratch[0]), _p(scratch[1]),
+                                  _p(out), _stream()), "argmax_rows")
     return out
 
 

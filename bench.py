@@ -6,18 +6,24 @@ Default run: the layer sizes of Llama-3-8B (32 layers, hidden 4096, 32 heads, 8 
 heads, head size 128, intermediate 14336, vocabulary 128256, bf16, random weights
 N(0, 0.02)), 8 requests with 1,024-token prompts in the cache of an 8,192-token
 context, KV page 16.  A step is one decode step of the whole batch.  Prints ONE
-JSON line: `value` = decoded tokens per second on the device (CUDA events around K
-steps), `e2e` = the same through Engine.add_request()/Engine.step() with host
-tokens in and out, `prefill` = one 2,048-token prompt in one step, `roofline` = the
-bytes a decode step has to read (every weight once + the live requests' cache)
-over its time against the measured copy bandwidth, `points` = decode at batch 1
-and 64.
+JSON line: `value` = decoded tokens per second on the device (CUDA events around
+blocks of K steps: the median of five blocks, their spread in `spread`), `e2e` = the same
+through Engine.add_request()/Engine.step() with host tokens in and out, `prefill` = one
+2,048-token prompt in one step (the median of five), `roofline` = the bytes a decode
+step has to read (every weight once + the live requests' cache) over its time against
+the measured copy bandwidth, `points` = decode at batch 1 and 64 and at 8,192 tokens of
+context, and the headline figures of the two serving workloads.
 
 Parts alone (one line each, for profiles): `--only decode|prefill` (with `--layers`,
 `--batch`), `--only gemm` (each projection at `--batch` tokens: library product and
 the tcgen05 kernel), `--only attention` (the prompt-attention kernels), `--only peaks`
 (a device copy and a library bf16 product on this box).  The other
-configurations of the baseline through Engine.generate(): `--workload serving1b|long3b`.
+configurations of the baseline through the engine's scheduler: `--workload serving1b|long3b`
+(per phase: bytes a step had to read and the fraction of the copy bandwidth, prompt TFLOP/s
+against the library product's peak, what the steps were made of, how often the device
+waited for the host).  `--profile`: CUDA-event time per class of kernel for one prefill
+step and for decode steps, launched eagerly, with bytes, flops and the fraction of the
+roofline for each class.
 """
 import argparse
 import json
@@ -44,10 +50,11 @@ def peaks():
         try:
             m = json.load(open(p))
             return dict(hbm_gbs=float(m["hbm_gbs"]), bf16_tflops=float(m["bf16_tflops"]),
+                        bf16_tflops_sustained=float(m.get("bf16_tflops_sustained", m["bf16_tflops"])),
                         source="measured")
         except Exception:
             pass
-    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
 
 
 class ClockSampler:
@@ -90,15 +97,17 @@ class ClockSampler:
                     sm_max_mhz=self.max_mhz, reasons=sorted(self.reasons))
 
 
-def time_decode(torch, aie, model, batch, prompt_len, steps, warmup, ctx_cap):
-    """Device time of `steps` decode steps of `batch` requests that each hold
-    prompt_len tokens.  The cache is filled by a real prefill through the step function."""
+def time_decode(torch, aie, model, batch, prompt_len, steps, warmup, ctx_cap, blocks=5):
+    """Device time of decode steps of `batch` requests that each hold prompt_len tokens: `blocks` blocks
+    of `steps` steps, each between a pair of CUDA events; the median block is the result, the fastest and
+    slowest are its spread.  The cache is filled by a real prefill through the step function."""
     from ai_engine_b200.cache import PagedCache
     from ai_engine_b200.engine.step import StepEntry, StepRunner
     from ai_engine_b200.kernels.loader import LAUNCHES
     from ai_engine_b200.sampling.sampler import Sampler
 
-    total = prompt_len + warmup + steps + 1
+    total = min(prompt_len + warmup + steps * blocks + 1, ctx_cap)
+    blocks = max(1, min(blocks, (total - prompt_len - warmup - 1) // steps))
     pages = batch * ((total + PAGE - 1) // PAGE) + 4
     cache = PagedCache(model.cache_requests(), PAGE, pages, batch, ctx_cap, model.dtype, model.device)
     runner = StepRunner(model, cache)
@@ -126,30 +135,35 @@ def time_decode(torch, aie, model, batch, prompt_len, steps, warmup, ctx_cap):
     tokens = out.cpu().tolist()
     torch.cuda.synchronize()
     l0, g0 = LAUNCHES[0], runner.graph_launches
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for i in range(steps):
-        out = one(warmup + i)
-    end.record()
-    torch.cuda.synchronize()
-    ms = start.elapsed_time(end) / steps
+    per_block = []
+    for blk in range(blocks):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            out = one(warmup + blk * steps + i)
+        end.record()
+        torch.cuda.synchronize()
+        per_block.append(start.elapsed_time(end) / steps)
     runner.check_errors()
-    launches = LAUNCHES[0] - l0 + runner.graph_launches - g0      # launched afresh + replayed from graphs
-    ctx_tokens = batch * (prompt_len + warmup + steps / 2.0)
+    launches = (LAUNCHES[0] - l0 + runner.graph_launches - g0) // blocks     # launched afresh + replayed, per block
+    ms = statistics.median(per_block)
+    ctx_tokens = batch * (prompt_len + warmup + steps * blocks / 2.0)
     bytes_step = model.step_weight_bytes() + cache.kv_bytes_per_token() * ctx_tokens
     del cache, runner
     torch.cuda.empty_cache()
-    return dict(ms=ms, tok_s=batch * 1000.0 / ms, launches=launches, bytes=bytes_step)
+    return dict(ms=ms, ms_min=min(per_block), ms_max=max(per_block), blocks=blocks, tok_s=batch * 1000.0 / ms,
+                launches=launches, bytes=bytes_step)
 
 
-def time_e2e(torch, aie, model_cfg, batch, prompt_len, steps, warmup, layers):
+def time_e2e(torch, aie, model_cfg, batch, prompt_len, steps, warmup, layers, blocks=5):
     """Through the public API: add_request(host ids) then step() — every step copies its
-    inputs from pinned host memory and reads the sampled tokens back."""
+    inputs from pinned host memory and reads the sampled tokens back.  Wall clock around blocks of
+    `steps` calls of Engine.step(); the median block is the result."""
     eng = aie.Engine(model_cfg, dtype="bf16", random_weights=True, seed=0, max_num_seqs=batch,
-                     block_size=PAGE, kv_cache_blocks=batch * ((prompt_len + steps + warmup + 32) // PAGE + 2),
+                     block_size=PAGE, kv_cache_blocks=batch * ((prompt_len + steps * blocks + warmup + 32) // PAGE + 2),
                      max_num_batched_tokens=2048, max_seq_len=CONTEXT)
     g = torch.Generator().manual_seed(1)
-    sp = aie.SamplingParams(max_tokens=steps + warmup + 8, ignore_eos=True)
+    sp = aie.SamplingParams(max_tokens=steps * blocks + warmup + 8, ignore_eos=True)
     for _ in range(batch):
         eng.add_request(torch.randint(0, model_cfg["vocab_size"], (prompt_len,), generator=g).tolist(), sp)
     while eng.scheduler.num_waiting or any(eng.scheduler.computed(r) < prompt_len for r in eng.scheduler.running()):
@@ -158,16 +172,18 @@ def time_e2e(torch, aie, model_cfg, batch, prompt_len, steps, warmup, layers):
         eng.step()
     torch.cuda.synchronize()
     c0 = dict(eng.counters)
-    t0 = time.perf_counter()
-    n = 0
-    for _ in range(steps):
-        n += len(eng.step())
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
+    rates = []
+    for _ in range(blocks):
+        t0 = time.perf_counter()
+        n = 0
+        for _ in range(steps):
+            n += len(eng.step())
+        torch.cuda.synchronize()
+        rates.append(n / (time.perf_counter() - t0))
     c1 = eng.counters
-    return dict(value=n / dt, unit="tokens/s",
-                h2d_bytes_per_step=(c1["h2d_bytes"] - c0["h2d_bytes"]) // steps,
-                d2h_bytes_per_step=(c1["d2h_bytes"] - c0["d2h_bytes"]) // steps), eng
+    return dict(value=statistics.median(rates), unit="tokens/s", value_min=round(min(rates), 1), value_max=round(max(rates), 1),
+                h2d_bytes_per_step=(c1["h2d_bytes"] - c0["h2d_bytes"]) // (steps * blocks),
+                d2h_bytes_per_step=(c1["d2h_bytes"] - c0["d2h_bytes"]) // (steps * blocks)), eng
 
 
 def time_prefill(torch, model, tokens, pk):
@@ -177,8 +193,8 @@ def time_prefill(torch, model, tokens, pk):
     cache = PagedCache(model.cache_requests(), PAGE, tokens // PAGE + 2, 1, CONTEXT, model.dtype, model.device)
     runner = StepRunner(model, cache)
     ids = torch.randint(0, model.spec.vocab_size, (tokens,), generator=torch.Generator().manual_seed(2)).tolist()
-    best = None
-    for it in range(4):
+    times = []
+    for it in range(7):           # two warm-up steps, then five timed ones: the median is reported
         slot = cache.admit()
         cache.ensure(slot, tokens)
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -187,12 +203,12 @@ def time_prefill(torch, model, tokens, pk):
         e.record()
         torch.cuda.synchronize()
         cache.finish(slot)
-        if it >= 1:
-            ms = s.elapsed_time(e)
-            best = ms if best is None else min(best, ms)
+        if it >= 2:
+            times.append(s.elapsed_time(e))
     runner.check_errors()
+    best = statistics.median(times)
     flops = model.step_flops(tokens, keys=(tokens + 1) / 2.0, logit_rows=1)      # what the parts report
-    return dict(value=tokens * 1000.0 / best, tokens=tokens, ms=best,
+    return dict(value=tokens * 1000.0 / best, tokens=tokens, ms=best, ms_min=min(times), ms_max=max(times),
                 frac=flops / (best * 1e-3) / (pk["bf16_tflops"] * 1e12))
 
 
@@ -333,10 +349,15 @@ LLAMA32_1B = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermed
 LLAMA32_3B = dict(LLAMA32_1B, hidden_size=3072, num_hidden_layers=28, num_attention_heads=24, head_dim=128)
 
 
-def run_workload(torch, aie, name):
-    """The two serving workloads of the baseline's other configurations, through Engine.generate():
+def run_workload(torch, aie, name, pk):
+    """The two serving workloads of the baseline's other configurations, through the engine's scheduler
+    (add_request + step, as Engine.generate() does):
     serving1b — Llama-3.2-1B shape, 64 concurrent requests, prompts uniform in [128, 4096], 256 tokens each;
-    long3b    — Llama-3.2-3B shape, one 32,768-token prompt in 2,048-token portions, then 512 greedy tokens."""
+    long3b    — Llama-3.2-3B shape, one 32,768-token prompt in 2,048-token portions, then 512 greedy tokens.
+    Every step is put down with its wall-clock time (between returns of Engine.step(), which runs a step
+    ahead of the device), what it was made of, the bytes it had to read (every weight once and the cache of
+    its requests) and its flops; steps in which every request brings one token are the decode phase, the
+    others the prompt phase."""
     g = torch.Generator().manual_seed(0)
     if name == "serving1b":
         cfg, n, new = LLAMA32_1B, 64, 256
@@ -353,16 +374,107 @@ def run_workload(torch, aie, name):
     sp = aie.SamplingParams(max_tokens=new, ignore_eos=True)
     eng.generate([prompts[0][:64]], aie.SamplingParams(max_tokens=4, ignore_eos=True))      # warm-up: kernels, graphs
     torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    outs = eng.generate(prompts, sp)
+    model, kv_tok = eng.model, eng.cache.kv_bytes_per_token()
+    wbytes = model.step_weight_bytes()
+    stream = torch.cuda.current_stream()
+    phases = {k: dict(steps=0, s=0.0, tokens=0, requests=0, max_tokens=0, bytes=0.0, flops=0.0, graph=0, host_bound=0)
+              for k in ("decode", "prompt")}
+    rids = [eng.add_request(p, sp) for p in prompts]
+    generated = 0
+    g0 = eng.runner.graph_launches
+    t0 = last = time.perf_counter()
+    while eng.has_unfinished() or eng._inflight:
+        idle = stream.query()              # nothing left on the device before this step is launched: it waited for the host
+        steps_before, gl = eng.counters["steps"], eng.runner.graph_launches
+        generated += sum(1 for _, tok, _ in eng.step() if tok is not None)
+        now = time.perf_counter()
+        if eng.counters["steps"] == steps_before:
+            last = now
+            continue
+        ctx = eng.runner.last_ctx
+        R, T = ctx.real_R, ctx.real_T
+        ph = phases["decode" if T == R else "prompt"]
+        held = float((ctx.h_ctx_len[:R] + ctx.h_q_len[:R]).sum())
+        keys = float((ctx.h_q_len[:R] * ctx.h_ctx_len[:R] + ctx.h_q_len[:R] * (ctx.h_q_len[:R] + 1) / 2.0).sum()) / T
+        ph["steps"] += 1
+        ph["s"] += now - last
+        ph["tokens"] += T
+        ph["requests"] += R
+        ph["max_tokens"] = max(ph["max_tokens"], T)
+        ph["bytes"] += wbytes + kv_tok * held
+        ph["flops"] += model.step_flops(T, keys, logit_rows=ctx.num_logit_rows)
+        ph["graph"] += int(eng.runner.graph_launches > gl)
+        ph["host_bound"] += int(bool(idle) and ph["steps"] > 1)
+        last = now
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    outs = [eng.take(r) for r in rids]
     st = eng.stats()
-    assert all(len(o) == new for o in outs)
-    return {"workload": name, "requests": n, "prompt_tokens": sum(lens), "generated_tokens": n * new,
-            "seconds": round(dt, 3), "generated_tok_s": round(n * new / dt, 1),
-            "total_tok_s": round((sum(lens) + n * new) / dt, 1), "steps": st["steps"],
-            "preemptions": st["preemptions"], "mean_batch_tokens": round(st["batch_tokens"] / max(st["steps"], 1), 1)}
+    assert all(len(o) == new for o in outs) and generated == n * new
+    out = {"workload": name, "requests": n, "prompt_tokens": sum(lens), "generated_tokens": n * new,
+           "seconds": round(dt, 3), "generated_tok_s": round(n * new / dt, 1),
+           "total_tok_s": round((sum(lens) + n * new) / dt, 1), "steps": st["steps"], "preemptions": st["preemptions"],
+           "peaks": pk["source"]}
+    for k, ph in phases.items():
+        if not ph["steps"]:
+            continue
+        sec = max(ph["s"], 1e-9)
+        out[k] = {"steps": ph["steps"], "seconds": round(sec, 4), "tokens_per_s": round(ph["tokens"] / sec, 1),
+                  "mean_tokens": round(ph["tokens"] / ph["steps"], 1), "max_tokens": ph["max_tokens"],
+                  "mean_requests": round(ph["requests"] / ph["steps"], 1),
+                  "gb_per_step": round(ph["bytes"] / ph["steps"] / 1e9, 3),
+                  "hbm_gb_s": round(ph["bytes"] / sec / 1e9, 1), "hbm_frac": round(ph["bytes"] / sec / 1e9 / pk["hbm_gbs"], 4),
+                  "tflop_s": round(ph["flops"] / sec / 1e12, 1),
+                  "bf16_frac": round(ph["flops"] / sec / 1e12 / pk["bf16_tflops"], 4),
+                  "graph_replayed_share": round(ph["graph"] / ph["steps"], 3),
+                  "host_bound_share": round(ph["host_bound"] / ph["steps"], 3)}
+    del eng
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_profile(torch, aie, model, batch, pk):
+    """CUDA-event time per class of kernel, launched eagerly: one 2,048-token prefill step, then 8 decode steps
+    of `batch` requests with 1,024 cached tokens each.  Bytes and flops are what each launch has to move and do;
+    frac is the larger of the two against the measured peaks, over the time."""
+    from ai_engine_b200.cache import PagedCache
+    from ai_engine_b200.engine.step import StepEntry, StepRunner
+    from ai_engine_b200.kernels import profile
+    from ai_engine_b200.sampling.sampler import Sampler
+
+    g = torch.Generator().manual_seed(3)
+    vocab = model.spec.vocab_size
+    pages = (batch * (PROMPT_LEN + 32) + PREFILL_TOKENS) // PAGE + 8
+    cache = PagedCache(model.cache_requests(), PAGE, pages, batch + 1, CONTEXT, model.dtype, model.device)
+    runner = StepRunner(model, cache, use_graphs=False)
+    sampler = Sampler(model.device)
+    greedy = [aie.SamplingParams(max_tokens=1)] * batch
+    slots = [cache.admit() for _ in range(batch + 1)]
+    for s in slots[:batch]:
+        cache.ensure(s, PROMPT_LEN + 32)
+        runner.step([StepEntry(s, 0, torch.randint(0, vocab, (PROMPT_LEN,), generator=g).tolist(), [])])
+    cache.ensure(slots[batch], PREFILL_TOKENS)
+    ids = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=g).tolist()
+    runner.step([StepEntry(slots[batch], 0, ids, [PREFILL_TOKENS - 1])])          # warm-up of the large step
+    out = {}
+    profile.start()
+    runner.step([StepEntry(slots[batch], 0, ids, [PREFILL_TOKENS - 1])])
+    out["prefill_2048"] = profile.stop(pk["hbm_gbs"], pk["bf16_tflops"])
+    toks = torch.randint(0, vocab, (batch,), generator=g).tolist()
+    step = lambda i: sampler.sample(runner.step([StepEntry(s, PROMPT_LEN + i, [toks[j]], [0])
+                                                 for j, s in enumerate(slots[:batch])]), greedy, [0] * batch)
+    for i in range(3):
+        step(i)
+    profile.start()
+    for i in range(3, 11):
+        step(i)
+    rows = profile.stop(pk["hbm_gbs"], pk["bf16_tflops"])
+    for r in rows:          # per step
+        for k in ("calls", "ms", "gb", "gflop"):
+            r[k] = round(r[k] / 8, 4)
+    out[f"decode_b{batch}_per_step"] = rows
+    runner.check_errors()
+    return out
 
 
 def config_record(layers, batch, peaks_source):
@@ -390,6 +502,9 @@ def main():
                     help="run one of the serving workloads through Engine.generate() and print its numbers")
     ap.add_argument("--only", choices=["decode", "prefill", "gemm", "attention", "peaks"], default=None,
                     help="time one part only and print its numbers (for profiling)")
+    ap.add_argument("--profile", action="store_true",
+                    help="CUDA-event time, bytes, flops and roofline fraction per class of kernel (eager launches)")
+    ap.add_argument("--skip-workloads", action="store_true", help="leave the 1B and 3B serving workloads out of `points`")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -407,7 +522,7 @@ def main():
     warmup = max(a.warmup, 3)
     pk = peaks()
     if a.workload:
-        print(json.dumps(run_workload(torch, aie, a.workload)))
+        print(json.dumps(run_workload(torch, aie, a.workload, pk)))
         return 0
     if a.only == "gemm":
         for k, v in time_gemms(torch, a.batch).items():
@@ -427,6 +542,12 @@ def main():
     cfg = dict(LLAMA3_8B)
     cfg["num_hidden_layers"] = a.layers
     model, _ = random_model(cfg, seed=0, dtype="bf16")
+    if a.profile:
+        from ai_engine_b200.kernels import profile
+        for what, rows in run_profile(torch, aie, model, a.batch, pk).items():
+            print(json.dumps({"profile": what, "layers": a.layers, "peaks": pk["source"], "rows": rows}))
+            print(f"-- {what} ({a.layers} layers)\n" + profile.table(rows), file=sys.stderr)
+        return 0
     if a.only:
         r = (time_decode(torch, aie, model, a.batch, PROMPT_LEN, a.steps, warmup, CONTEXT) if a.only == "decode"
              else time_prefill(torch, model, PREFILL_TOKENS, pk))
@@ -438,17 +559,34 @@ def main():
     prefill = time_prefill(torch, model, PREFILL_TOKENS, pk)
     if not a.skip_points:
         for b in (1, 64):
-            points[f"decode_b{b}"] = round(time_decode(torch, aie, model, b, PROMPT_LEN, min(a.steps, 32), 3, CONTEXT)["tok_s"], 1)
-        long = time_decode(torch, aie, model, a.batch, CONTEXT - 64, min(a.steps, 32), 3, CONTEXT)
+            pt = time_decode(torch, aie, model, b, PROMPT_LEN, min(a.steps, 32), 3, CONTEXT, blocks=3)
+            points[f"decode_b{b}"] = round(pt["tok_s"], 1)
+            points[f"decode_b{b}_hbm_frac"] = round(pt["bytes"] / (pt["ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        long = time_decode(torch, aie, model, a.batch, CONTEXT - 128, min(a.steps, 32), 3, CONTEXT, blocks=3)
         points[f"decode_b{a.batch}_ctx{CONTEXT}"] = round(long["tok_s"], 1)
+        points[f"decode_b{a.batch}_ctx{CONTEXT}_hbm_frac"] = round(long["bytes"] / (long["ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
     del model
     torch.cuda.empty_cache()
     e2e, eng = time_e2e(torch, aie, cfg, a.batch, PROMPT_LEN, a.steps, warmup, a.layers)
+    del eng
+    torch.cuda.empty_cache()
+    if not a.skip_points and not a.skip_workloads and a.layers == LLAMA3_8B["num_hidden_layers"]:
+        w1 = run_workload(torch, aie, "serving1b", pk)
+        points["serving1b_total_tok_s"] = w1["total_tok_s"]
+        points["serving1b_decode_hbm_frac"] = w1.get("decode", {}).get("hbm_frac")
+        points["serving1b_prompt_bf16_frac"] = w1.get("prompt", {}).get("bf16_frac")
+        w3 = run_workload(torch, aie, "long3b", pk)
+        points["long3b_prompt_tok_s"] = w3.get("prompt", {}).get("tokens_per_s")
+        points["long3b_prompt_bf16_frac"] = w3.get("prompt", {}).get("bf16_frac")
+        points["long3b_decode_tok_s"] = w3.get("decode", {}).get("tokens_per_s")
+        points["long3b_decode_hbm_frac"] = w3.get("decode", {}).get("hbm_frac")
     achieved = main_pt["bytes"] / (main_pt["ms"] * 1e-3) / 1e9
     line = {
         "metric": "decode tok/s at batch 8 (Llama-3-8B shape, bf16, 1,024-token prompts, context 8,192)",
         "value": round(main_pt["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": a.steps,
-        "warmup": warmup, "ms_per_step": round(main_pt["ms"], 4), "higher_is_better": True,
+        "warmup": warmup, "ms_per_step": round(main_pt["ms"], 4),
+        "spread": {"blocks": main_pt["blocks"], "ms_min": round(main_pt["ms_min"], 4), "ms_max": round(main_pt["ms_max"], 4)},
+        "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0, 0.02), uniform random token ids",
         "impl": "ours",
@@ -456,7 +594,8 @@ def main():
         "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": main_pt["launches"],
         "prefill": {"value": round(prefill["value"], 1), "tokens": prefill["tokens"],
-                    "ms": round(prefill["ms"], 3), "frac": round(prefill["frac"], 4)},
+                    "ms": round(prefill["ms"], 3), "frac": round(prefill["frac"], 4),
+                    "ms_min": round(prefill["ms_min"], 3), "ms_max": round(prefill["ms_max"], 3)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,

@@ -314,14 +314,42 @@ def test_command_line(tmp_path):
     exe = [sys.executable, os.path.join(ROOT, "bin", "ai-engine")]
     assert subprocess.run(exe + ["-c", str(cfg), "--check"], capture_output=True, text=True).stdout.strip() == "ok"
     p = subprocess.run(exe + ["-c", str(cfg), "--prompt-ids", "5,17,3", "--prompt-ids", "9,9", "--max-tokens", "6",
-                              "--ignore-eos", "--stats"], capture_output=True, text=True, timeout=600)
+                              "--ignore-eos", "--stats", "--profile"], capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, p.stderr[-1500:]
+    assert "kernel class" in p.stderr and "gemm_f32" in p.stderr and "attention_plain" in p.stderr
     lines = [[int(t) for t in l.split(",")] for l in p.stdout.strip().splitlines()]
     assert len(lines) == 2 and all(len(l) == 6 for l in lines)
     want, margins = greedy_with_margin(d, [5, 17, 3], 6, torch.float64, TOL_F32)
     assert_same_until_a_close_call(lines[0], want, margins, TOL_F32)
     bad = subprocess.run(exe + ["--model", str(tmp_path / "none"), "--prompt-ids", "1"], capture_output=True, text=True)
     assert bad.returncode == 1 and "error" in bad.stderr
+
+
+def test_kernel_classes_are_timed_on_request(tmp_path):
+    """Profiling on: every launch of a step sits between two CUDA events under its class's name, with the
+    bytes and flops it has to move and do; off (the default): nothing is recorded."""
+    from ai_engine_b200.engine.replay import Replayer
+    from ai_engine_b200.kernels import profile
+
+    d = make_model_dir(tmp_path, "E")
+    rep = Replayer(d, "bfloat16", max_tokens=512, block_size=16)
+    ids = random_ids(200, 260, 2)
+    rep.run_step([dict(id="x", tokens=ids[:150], want=[149])])
+    assert not profile.enabled() and not profile._RECORDS
+    profile.start()
+    rep.run_step([dict(id="y", tokens=ids[:150], want=[149])])
+    rep.run_step([dict(id="y", tokens=ids[150:151], want=[0]), dict(id="x", tokens=ids[150:151], want=[0])])
+    rows = {r["kernel"]: r for r in profile.stop(6500.0, 1600.0)}
+    assert not profile.enabled()
+    for cls in ("embed_gather", "add_rmsnorm", "gemm_library", "rope_kv_write", "attention_prefill_tcgen05", "silu_mul",
+                "gemm_tc", "gemm_tc_rope", "gemm_tc_swiglu", "attention_decode"):
+        assert cls in rows and rows[cls]["ms"] > 0 and rows[cls]["gb"] > 0, (cls, sorted(rows))
+    L, D, F = 2, 256, 320
+    assert rows["gemm_library"]["calls"] == 4 * L         # qkv, o, gate_up, down of the 150-token step (its one logits row: gemm_tc)
+    assert abs(rows["gemm_library"]["gflop"] - 2 * 150 * L * (D * (4 + 4) * 128 + 4 * 128 * D + 3 * F * D) / 1e9) < 0.01
+    assert abs(rows["attention_prefill_tcgen05"]["gflop"] - 4 * 128 * 4 * (150 * 151 / 2) * L / 1e9) < 0.01
+    assert abs(rows["attention_decode"]["gb"] - 2 * 151 * 2 * 128 * 2 * 2 * L / 1e9) < 1e-4
+    assert abs(sum(r["share"] for r in rows.values()) - 1.0) < 1e-2
 
 
 def test_decode_steps_replayed_from_a_graph_match_eager_steps(tmp_path):

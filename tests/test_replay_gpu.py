@@ -96,6 +96,35 @@ def test_portions_of_changing_size(tmp_path, name, dtype):
     assert err.max() <= tol_for(dtype), f"first wrong token {int(np.argmax(err > tol_for(dtype)))}: {err.max()}"
 
 
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_cached_keys_do_not_depend_on_how_the_prompt_was_cut(tmp_path, name):
+    """bfloat16: the keys and values a prompt leaves in its pages, fed whole (one step of 150 tokens: library
+    products) and in portions (steps of 40, 64, 30, 13 and 3 tokens: this package's products, the last with the
+    rotation in the product's epilogue).  The projection reaches the rotation in float32 either way and is
+    rounded once, so the pages agree to the last bit almost everywhere, and nowhere differ by more than one
+    step of bfloat16 (products that sum in another order may land on the other side of a rounding boundary)."""
+    d = make_model_dir(tmp_path, name)
+    ids = random_ids(150, TINY[name][0]["vocab_size"], 44)
+    pools = []
+    for portions in ([150], [40, 64, 30, 13, 3]):
+        rep = replayer(d, "bfloat16", name, max_tokens=192)
+        at = 0
+        for n in portions:
+            rep.run_step([dict(id="x", tokens=ids[at:at + n], want=[])])
+            at += n
+        pages = (150 + 15) // 16
+        pool = rep.cache.groups[0].pool[:, :, :pages].float().cpu()       # [runs, k|v, pages, K, page, d]
+        pools.append(pool.permute(0, 1, 2, 4, 3, 5).reshape(pool.shape[0], 2, pages * 16, -1)[:, :, :150])
+    a, b = pools
+    assert not torch.isnan(a).any() and not torch.isnan(b).any()
+    first_layer_differs = float((a[0] != b[0]).float().mean())
+    assert first_layer_differs <= 0.01, first_layer_differs       # same inputs: only rounding boundaries
+    step = torch.maximum(a[0].abs(), b[0].abs()) * 2.0 ** -7           # one step of bfloat16 at that size
+    assert bool(((a[0] - b[0]).abs() <= step + 1e-30).all())
+    # later layers read hidden states that already differ by such steps: bounded like the logits
+    assert float((a - b).abs().max()) <= TOL_BF16 * max(1.0, float(a.abs().max()))
+
+
 def mixed_trace(lengths, vocab, seed):
     """Up to four live requests; each is fed in portions of changing size and then
     token by token while others are mid-prompt; finished requests leave and new

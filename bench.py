@@ -433,10 +433,10 @@ def run_workload(torch, aie, name, pk):
     return out
 
 
-def run_profile(torch, aie, model, batch, pk):
+def run_profile(torch, aie, model, batch, pk, prompt_len=PROMPT_LEN, context=CONTEXT):
     """CUDA-event time per class of kernel, launched eagerly: one 2,048-token prefill step, then 8 decode steps
-    of `batch` requests with 1,024 cached tokens each.  Bytes and flops are what each launch has to move and do;
-    frac is the larger of the two against the measured peaks, over the time."""
+    of `batch` requests with `prompt_len` cached tokens each.  Bytes and flops are what each launch has to move
+    and do; frac is the larger of the two against the measured peaks, over the time."""
     from ai_engine_b200.cache import PagedCache
     from ai_engine_b200.engine.step import StepEntry, StepRunner
     from ai_engine_b200.kernels import profile
@@ -444,7 +444,8 @@ def run_profile(torch, aie, model, batch, pk):
 
     g = torch.Generator().manual_seed(3)
     vocab = model.spec.vocab_size
-    pages = (batch * (PROMPT_LEN + 32) + PREFILL_TOKENS) // PAGE + 8
+    PROMPT_LEN, CONTEXT = prompt_len, max(context, prompt_len + 64)
+    pages = (batch * (PROMPT_LEN + 32 + PAGE) + PREFILL_TOKENS) // PAGE + 8
     cache = PagedCache(model.cache_requests(), PAGE, pages, batch + 1, CONTEXT, model.dtype, model.device)
     runner = StepRunner(model, cache, use_graphs=False)
     sampler = Sampler(model.device)
@@ -452,7 +453,9 @@ def run_profile(torch, aie, model, batch, pk):
     slots = [cache.admit() for _ in range(batch + 1)]
     for s in slots[:batch]:
         cache.ensure(s, PROMPT_LEN + 32)
-        runner.step([StepEntry(s, 0, torch.randint(0, vocab, (PROMPT_LEN,), generator=g).tolist(), [])])
+        ids = torch.randint(0, vocab, (PROMPT_LEN,), generator=g).tolist()
+        for a in range(0, PROMPT_LEN, 2048):
+            runner.step([StepEntry(s, a, ids[a:a + 2048], [])])
     cache.ensure(slots[batch], PREFILL_TOKENS)
     ids = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=g).tolist()
     runner.step([StepEntry(slots[batch], 0, ids, [PREFILL_TOKENS - 1])])          # warm-up of the large step
@@ -504,6 +507,9 @@ def main():
                     help="time one part only and print its numbers (for profiling)")
     ap.add_argument("--profile", action="store_true",
                     help="CUDA-event time, bytes, flops and roofline fraction per class of kernel (eager launches)")
+    ap.add_argument("--shape", choices=["8b", "1b", "3b"], default="8b",
+                    help="layer sizes for --profile and --only decode|prefill (the headline run is always the 8B shape)")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="cached tokens per request for --profile / --only decode")
     ap.add_argument("--skip-workloads", action="store_true", help="leave the 1B and 3B serving workloads out of `points`")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -539,19 +545,27 @@ def main():
             for k, v in time_attention(torch, tokens, context).items():
                 print(k, json.dumps(v))
         return 0
-    cfg = dict(LLAMA3_8B)
-    cfg["num_hidden_layers"] = a.layers
+    cfg = dict({"8b": LLAMA3_8B, "1b": LLAMA32_1B, "3b": LLAMA32_3B}[a.shape] if (a.profile or a.only) else LLAMA3_8B)
+    if a.layers != LLAMA3_8B["num_hidden_layers"] or a.shape == "8b":
+        cfg["num_hidden_layers"] = a.layers
+    layers = cfg["num_hidden_layers"]
     model, _ = random_model(cfg, seed=0, dtype="bf16")
     if a.profile:
         from ai_engine_b200.kernels import profile
-        for what, rows in run_profile(torch, aie, model, a.batch, pk).items():
-            print(json.dumps({"profile": what, "layers": a.layers, "peaks": pk["source"], "rows": rows}))
-            print(f"-- {what} ({a.layers} layers)\n" + profile.table(rows), file=sys.stderr)
+        for what, rows in run_profile(torch, aie, model, a.batch, pk, a.prompt_len).items():
+            print(json.dumps({"profile": what, "shape": a.shape, "layers": layers, "prompt_len": a.prompt_len,
+                              "peaks": pk["source"], "rows": rows}))
+            print(f"-- {what} ({a.shape} shape, {layers} layers, {a.prompt_len} cached tokens a request)\n"
+                  + profile.table(rows), file=sys.stderr)
         return 0
     if a.only:
-        r = (time_decode(torch, aie, model, a.batch, PROMPT_LEN, a.steps, warmup, CONTEXT) if a.only == "decode"
+        ctx_cap = max(CONTEXT, a.prompt_len + warmup + 5 * a.steps + 64)
+        r = (time_decode(torch, aie, model, a.batch, a.prompt_len, a.steps, warmup, ctx_cap) if a.only == "decode"
              else time_prefill(torch, model, PREFILL_TOKENS, pk))
-        print(json.dumps({"only": a.only, "layers": a.layers, **{k: round(v, 4) for k, v in r.items()}}))
+        if a.only == "decode":
+            r["hbm_frac"] = r["bytes"] / (r["ms"] * 1e-3) / 1e9 / pk["hbm_gbs"]
+        print(json.dumps({"only": a.only, "shape": a.shape, "layers": layers, "batch": a.batch, "prompt_len": a.prompt_len,
+                          **{k: round(v, 4) for k, v in r.items()}}))
         return 0
     with ClockSampler() as clocks:
         main_pt = time_decode(torch, aie, model, a.batch, PROMPT_LEN, a.steps, warmup, CONTEXT)

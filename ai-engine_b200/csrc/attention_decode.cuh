@@ -296,25 +296,51 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     }
 }
 
-// out[t, h, :] = sum_s w_s * part_o[s] / sum_s w_s with w_s = exp(lse_s - max lse)
+// out[t, h, :] = sum_s w_s * part_o[s] / sum_s w_s with w_s = exp(lse_s - max lse).  One block per
+// (request, head).  The weights are worked out once (the first warp, lanes over the parts) and kept in
+// shared memory; then every thread sums its element over the parts with eight loads in flight (a loop
+// of one dependent load after another took 12 us at 37 parts, more than the bytes of the keys it joins).
+#define DEC_MAX_SPLITS 64
 __global__ void decode_reduce_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                      bf16* __restrict__ out, const int* __restrict__ dec_tokens,
                                      int H, int D, int S) {
+    __shared__ float w_s[DEC_MAX_SPLITS];
+    __shared__ float wsum_s;
     pdl_launch_dependents();
-    pdl_wait();
     const int di = blockIdx.x, h = blockIdx.y;
     const int t = dec_tokens[di];
     const size_t base = ((size_t)di * H + h) * S;
-    float M = -INFINITY;
-    for (int s = 0; s < S; ++s) M = fmaxf(M, part_lse[base + s]);
+    pdl_wait();
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        const float l0 = lane < S ? part_lse[base + lane] : -INFINITY;
+        const float l1 = lane + 32 < S ? part_lse[base + lane + 32] : -INFINITY;
+        float M = fmaxf(l0, l1);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        const float w0 = (l0 == -INFINITY) ? 0.f : __expf(l0 - M);
+        const float w1 = (l1 == -INFINITY) ? 0.f : __expf(l1 - M);
+        if (lane < S) w_s[lane] = w0;
+        if (lane + 32 < S) w_s[lane + 32] = w1;
+        float W = w0 + w1;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) W += __shfl_xor_sync(0xffffffffu, W, o);
+        if (lane == 0) wsum_s = W;
+    }
+    __syncthreads();
+    const float W = wsum_s;
     for (int e = threadIdx.x; e < D; e += blockDim.x) {
-        float A = 0.f, W = 0.f;
-        for (int s = 0; s < S; ++s) {
-            const float lse = part_lse[base + s];
-            const float w = (lse == -INFINITY) ? 0.f : __expf(lse - M);
-            W += w;
-            A += w * part_o[(base + s) * D + e];
+        const float* src = part_o + base * D + e;
+        float A = 0.f;
+        int s = 0;
+        for (; s + 8 <= S; s += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = src[(size_t)(s + u) * D];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) A += w_s[s + u] * v[u];
         }
+        for (; s < S; ++s) A += w_s[s] * src[(size_t)s * D];
         out[((size_t)t * H + h) * D + e] = __float2bfloat16_rn(W > 0.f ? A / W : 0.f);
     }
 }

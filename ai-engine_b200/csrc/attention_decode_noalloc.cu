@@ -29,6 +29,7 @@ extern "C" int aie_paged_attention_decode_noalloc(const void* q, const void* k_p
     const int gchunks = (G + GC - 1) / GC;
     if (K * gchunks > 65535 || n_dec > 65535) return AIE_UNSUPPORTED;
     if ((bt_width + S - 1) / S + 2 > DEC_MAX_PAGES) return AIE_UNSUPPORTED;   // more splits needed
+    if (S > DEC_MAX_SPLITS) return AIE_UNSUPPORTED;
 
     float* part_o = nullptr;
     float* part_lse = nullptr;

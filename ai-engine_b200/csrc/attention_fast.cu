@@ -32,6 +32,7 @@ extern "C" int aie_paged_attention_decode(const void* q, const void* k_pages, co
     if (K <= 0 || H % K || S < 1) return AIE_BAD_ARG;
     if (d != 64 && d != 128) return AIE_UNSUPPORTED;
     if (S > 1 && (!part_o || !part_lse)) return AIE_BAD_ARG;
+    if (S > DEC_MAX_SPLITS) return AIE_UNSUPPORTED;
     const int G = H / K;
     const int GC = G >= DEC_HEADS ? DEC_HEADS : G;
     const int gchunks = (G + GC - 1) / GC;

@@ -340,6 +340,54 @@ def time_attention(torch, tokens, context):
     return {f"attention[{tokens} tokens after {context}]": row}
 
 
+def time_decode_attention(torch, H, K, d, lens):
+    """The decode attention kernels alone for one layer's lone tokens over cached contexts of `lens` tokens (pages
+    of 16): the split-KV kernel with the number of parts the engine would choose, median of 10 with L2 flushed
+    between runs; GB/s counts the keys and values read once."""
+    from ai_engine_b200.kernels import ops
+
+    P, dev = PAGE, "cuda"
+    R = len(lens)
+    pages_per = [(n + P - 1) // P for n in lens]
+    n_pages = sum(pages_per) + 1
+    torch.manual_seed(0)
+    kp = (torch.randn(n_pages, K, P, d, device=dev) * 0.5).bfloat16()
+    vp = torch.randn(n_pages, K, P, d, device=dev).bfloat16()
+    q = torch.randn(R, H, d, device=dev).bfloat16()
+    perm = torch.randperm(n_pages, device=dev).int()
+    bt = torch.zeros((R, max(pages_per)), dtype=torch.int32, device=dev)
+    at = 0
+    for r, n in enumerate(pages_per):
+        bt[r, :n] = perm[at:at + n]
+        at += n
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=dev)
+    pos, req, dec = i32([n - 1 for n in lens]), i32(list(range(R))), i32(list(range(R)))
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    splits = ops.decode_splits(R, K, H // K, max(lens), bt.shape[1])
+    outs = {"split": torch.zeros_like(q)}
+    impls = {"split": lambda: ops.paged_attention_decode(q, kp, vp, dec, pos, req, bt, d ** -0.5, 0, splits, err, outs["split"])}
+    nbytes = sum(lens) * K * d * 2 * 2
+    row = {}
+    for name, fn in impls.items():
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(10):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3)
+        us = sorted(ts)[len(ts) // 2]
+        row[name] = dict(us=round(us, 1), gb_s=round(nbytes / us / 1e3, 1))
+    assert int(err.item()) == 0
+    row["split_parts"] = splits
+    return {f"decode attention[{R} requests, {sum(lens)} keys, H{H} K{K} d{d}]": row}
+
+
 LLAMA32_1B = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermediate_size=8192,
                   num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
                   vocab_size=128256, max_position_embeddings=131072, rope_theta=500000.0, rms_norm_eps=1e-5,
@@ -543,6 +591,12 @@ def main():
     if a.only == "attention":
         for tokens, context in ((PREFILL_TOKENS, 0), (PREFILL_TOKENS, 6144), (512, 0), (200, 1000)):
             for k, v in time_attention(torch, tokens, context).items():
+                print(k, json.dumps(v))
+        g = torch.Generator().manual_seed(0)
+        mixed = torch.randint(128, 4353, (64,), generator=g).tolist()
+        for H, K, d, lens in ((32, 8, 128, [1024] * 8), (32, 8, 128, [1024] * 64), (32, 8, 128, [8192] * 8), (32, 8, 128, [1024]),
+                              (32, 8, 64, [2600] * 56), (32, 8, 64, mixed), (24, 8, 128, [32768])):
+            for k, v in time_decode_attention(torch, H, K, d, lens).items():
                 print(k, json.dumps(v))
         return 0
     cfg = dict({"8b": LLAMA3_8B, "1b": LLAMA32_1B, "3b": LLAMA32_3B}[a.shape] if (a.profile or a.only) else LLAMA3_8B)

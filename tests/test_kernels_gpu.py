@@ -133,6 +133,35 @@ def paged_setup(dtype, H, K, d, P, lens, q_lens, seed, num_pages=None, shuffle=T
                 bt=torch.tensor(bt, device=DEV), lens=lens, q_lens=q_lens)
 
 
+def paged_setup_fast(dtype, H, K, d, P, lens, q_lens, seed):
+    """paged_setup without its loop over positions (for many or long requests)."""
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    R = len(lens)
+    pages_per = [(n + P - 1) // P for n in lens]
+    num_pages = sum(pages_per) + 3
+    perm = torch.randperm(num_pages, generator=g, device=DEV)
+    bt = -torch.ones((R, max(pages_per)), dtype=torch.int32, device=DEV)
+    k_pages = torch.full((num_pages, K, P, d), float("nan"), device=DEV, dtype=dtype)
+    v_pages = torch.full_like(k_pages, float("nan"))
+    ks, vs, at = [], [], 0
+    for r, n in enumerate(lens):
+        bt[r, :pages_per[r]] = perm[at:at + pages_per[r]].int()
+        at += pages_per[r]
+        ks.append((torch.randn(n, K, d, generator=g, device=DEV) * 1.5).to(dtype))
+        vs.append(torch.randn(n, K, d, generator=g, device=DEV).to(dtype))
+        pos = torch.arange(n, device=DEV)
+        k_pages[bt[r, pos // P].long(), :, pos % P] = ks[r]
+        v_pages[bt[r, pos // P].long(), :, pos % P] = vs[r]
+    q = torch.randn(sum(q_lens), H, d, generator=g, device=DEV).to(dtype)
+    positions, token_req = [], []
+    for r, (n, ql) in enumerate(zip(lens, q_lens)):
+        positions += list(range(n - ql, n))
+        token_req += [r] * ql
+    return dict(q=q, k_pages=k_pages, v_pages=v_pages, ks=ks, vs=vs,
+                positions=torch.tensor(positions, device=DEV, dtype=torch.int32),
+                token_req=torch.tensor(token_req, device=DEV, dtype=torch.int32), bt=bt, lens=lens, q_lens=q_lens)
+
+
 def attention_reference(s, H, K, d, scale, window):
     """[T, H, d] in float64 from the unpaged keys and values."""
     out = []
@@ -219,6 +248,36 @@ def test_paged_attention_decode_split_kv(shape):
     ops().paged_attention_decode(s["q"], s["k_pages"], s["v_pages"], dec, s["positions"], s["token_req"],
                                  s["bt"], scale, window, splits, e, out3, join_in_kernel=True)
     assert torch.equal(out3, out)
+
+
+MANY_SHAPES = [  # H, K, d, P, lens, window, splits
+    (32, 8, 64, 16, [2600, 130, 4095, 17, 900, 1, 16, 15, 33, 2048] * 6, 0, 1),      # 60 requests of mixed lengths
+    (32, 8, 64, 16, [2600, 130, 4095, 17, 900, 1, 16, 15, 33, 2048] * 2, 0, 37),     # more parts than some requests have tiles
+    (8, 2, 128, 64, [700, 64, 65, 1000], 0, 3),                                      # pages of 64
+    (8, 2, 64, 8, [500, 90, 31], 60, 2),                                             # a window that starts mid-tile
+    (20, 2, 128, 16, [333, 20], 0, 64),                                              # a group of 10; the most parts
+]
+
+
+@pytest.mark.parametrize("shape", MANY_SHAPES)
+def test_paged_attention_decode_many_requests_and_parts(shape):
+    H, K, d, P, lens, window, splits = shape
+    s = paged_setup_fast(torch.bfloat16, H, K, d, P, lens, [1] * len(lens), seed=H + d + len(lens))
+    scale = 1.0 / math.sqrt(d)
+    e = err_word()
+    want = attention_reference(s, H, K, d, scale, window)
+    # a subset of the step's tokens, in another order; rows that are not asked for are not written
+    pick = torch.tensor(list(range(len(lens)))[::-2], device=DEV, dtype=torch.int32)
+    out = torch.full_like(s["q"], float("nan"))
+    ops().paged_attention_decode(s["q"], s["k_pages"], s["v_pages"], pick, s["positions"], s["token_req"], s["bt"],
+                                 scale, window, splits, e, out)
+    torch.cuda.synchronize()
+    assert int(e.item()) == 0
+    err = (out[pick.long()].double() - want[pick.long()]).abs().amax(dim=(1, 2))
+    assert err.max() <= 2e-2, f"first wrong request {int(pick[int((err > 2e-2).nonzero()[0])])}: {float(err.max())}"
+    rest = torch.ones(len(lens), dtype=torch.bool, device=DEV)
+    rest[pick.long()] = False
+    assert torch.isnan(out[rest]).all()
 
 
 PREFILL_SHAPES = [  # H, K, d, P, lens, q_lens, window

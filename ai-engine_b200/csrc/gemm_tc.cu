@@ -96,6 +96,17 @@ __device__ __forceinline__ float ld_peer(unsigned addr, unsigned rank) {
     asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(peer) : "memory");
     return v;
 }
+// the sum over the cluster's CTAs, in rank order, of the float at `addr` in each: all loads are issued before
+// the first is used (a load from another CTA's shared memory takes some hundred cycles)
+__device__ __forceinline__ float sum_peers(unsigned addr, int parts) {
+    float v[8];
+#pragma unroll
+    for (int p = 0; p < 8; ++p) v[p] = p < parts ? ld_peer(addr, p) : 0.f;
+    float acc = 0.f;
+#pragma unroll
+    for (int p = 0; p < 8; ++p) acc += v[p];
+    return acc;
+}
 
 template <int BN, int EPI, typename OT>
 __global__ void __launch_bounds__(TC_THREADS)
@@ -249,11 +260,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     const int hh = j / half, i = j % half;
                     const int c1 = hh * hd + i, c2 = c1 + half;
                     const int slot = blockIdx.x * (TC_BM / hd) + hh;
-                    float x1 = 0.f, x2 = 0.f;
-                    for (int p = 0; p < parts; ++p) {
-                        x1 += ld_peer(tile_addr + (tt * TC_BM + c1) * 4, p);
-                        x2 += ld_peer(tile_addr + (tt * TC_BM + c2) * 4, p);
-                    }
+                    float x1 = sum_peers(tile_addr + (tt * TC_BM + c1) * 4, parts);
+                    float x2 = sum_peers(tile_addr + (tt * TC_BM + c2) * 4, parts);
                     const int t = t0 + tt;
                     const int pos = rope.positions[t];
                     if (slot >= rope.H + 2 * rope.K) continue;
@@ -287,15 +295,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 float out;
                 if (EPI == TC_EPI_STORE) {
-                    float acc = 0.f;
-                    for (int p = 0; p < parts; ++p) acc += ld_peer(tile_addr + (tt * TC_BM + j) * 4, p);
-                    out = acc;
+                    out = sum_peers(tile_addr + (tt * TC_BM + j) * 4, parts);
                 } else {     // rows 0..63 of the tile are gate rows, rows 64..127 their up rows
-                    float g = 0.f, u = 0.f;
-                    for (int p = 0; p < parts; ++p) {
-                        g += ld_peer(tile_addr + (tt * TC_BM + j) * 4, p);
-                        u += ld_peer(tile_addr + (tt * TC_BM + 64 + j) * 4, p);
-                    }
+                    const float g = sum_peers(tile_addr + (tt * TC_BM + j) * 4, parts);
+                    const float u = sum_peers(tile_addr + (tt * TC_BM + 64 + j) * 4, parts);
                     // sigmoid by ex2.approx and rcp.approx (relative error about 1e-6; the result is rounded to bf16)
                     float e, r;
                     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));

@@ -110,7 +110,7 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
     if out is None:
         out = torch.empty((n, D), dtype=out_dtype, device=x.device)
     lib = library("elementwise.cu")
-    stored = write_back and rows is None
+    stored = write_back and rows is None and delta is not None      # without a branch to add, the stream is as it was
     with region("add_rmsnorm", n * D * 4 * (2 if stored else 1) + (_nb(delta) if rows is None else 0) + _nb(out)):
         check(lib.aie_add_rmsnorm(_p(x), _p(delta), c_int(dtype_code(delta) if delta is not None else 0),
                                   _p(weight), c_int(dtype_code(weight)), _p(out),
@@ -242,6 +242,20 @@ def linear_parts(x: torch.Tensor, w: torch.Tensor, err: Optional[torch.Tensor] =
         if y is not None:
             return y
     return linear(x, w, out_dtype, err)
+
+
+def linear_add(stream: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
+    """stream [T, N] float32 += x . w^T in place, the sum taken in float32 inside the library product (its
+    epilogue reads the stream and writes it back), for bfloat16 steps of more than 64 tokens: the branch
+    output never travels through memory on its own.  False when the step is not of that kind (nothing
+    was done): the caller takes `linear_parts` and lets the next norm add."""
+    if (x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or stream.dtype != torch.float32
+            or x.shape[0] <= TC_MAX_TOKENS or stream.shape != (x.shape[0], w.shape[0]) or not stream.is_contiguous()):
+        return False
+    _dev(x, w, stream)
+    with region("gemm_library", _nb(x, w) + 2 * _nb(stream), 2.0 * x.shape[0] * w.shape[0] * w.shape[1]):
+        torch.addmm(stream, x, w.t(), out_dtype=torch.float32, out=stream)
+    return True
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,

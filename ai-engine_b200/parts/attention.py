@@ -105,7 +105,9 @@ class GQAAttention(Mixer):
     def step_planner(self):
         return ATTENTION_WORK
 
-    def forward(self, h, ctx, cache):
+    adds_in_place = True
+
+    def forward(self, h, ctx, cache, add_to=None):
         rot = self.rope.rotation() if self.rope is not None else None
         inv_freq = rot[0] if rot is not None else self._no_rope
         # a small bfloat16 step: product, rotation and cache write in one kernel
@@ -122,4 +124,7 @@ class GQAAttention(Mixer):
                                   write=cache.writes)
         a = ops.paged_attention(q, cache.k_pages, cache.v_pages, ctx, ctx.plan(ATTENTION_WORK),
                                 cache.block_table, self.scale, self.window)
-        return ops.linear_parts(a.view(a.shape[0], self.H * self.d), self.w_o, ctx.err)
+        a = a.view(a.shape[0], self.H * self.d)
+        if add_to is not None and ops.linear_add(add_to, a, self.w_o):
+            return None
+        return ops.linear_parts(a, self.w_o, ctx.err)

@@ -124,6 +124,9 @@ class Mixer(Part):
 
     host_side = False
     skips_padded_rows = False
+    # True: forward takes `add_to=stream` (the float32 residual stream) and may add its output there itself,
+    # returning None instead of the output (a block then hands no pending branch to the next norm)
+    adds_in_place = False
 
     def forward(self, h: torch.Tensor, ctx, cache: LayerCache) -> torch.Tensor:
         raise NotImplementedError
@@ -131,6 +134,8 @@ class Mixer(Part):
 
 class FeedForward(Part):
     """Token-local: forward(h [T, hidden], ctx) -> [T, hidden], float32 or the compute dtype."""
+
+    adds_in_place = False      # as for a Mixer
 
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
         raise NotImplementedError

@@ -20,6 +20,11 @@ class PreNormBlock(Block):
 
     def forward(self, x, pending, ctx, caches):
         h = self.mixer_norm.forward(x, pending)
-        a = self.mixer.forward(h, ctx, caches.get("mixer"))
+        if self.mixer.adds_in_place:      # a large step's output projection adds to the stream itself: a is None then
+            a = self.mixer.forward(h, ctx, caches.get("mixer"), add_to=x)
+        else:
+            a = self.mixer.forward(h, ctx, caches.get("mixer"))
         h = self.ffn_norm.forward(x, a)
+        if self.ffn.adds_in_place:
+            return x, self.ffn.forward(h, ctx, add_to=x)
         return x, self.ffn.forward(h, ctx)

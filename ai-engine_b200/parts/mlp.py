@@ -47,6 +47,11 @@ class SwiGLU(FeedForward):
     def flops(self, tokens, keys=0.0):
         return 2.0 * tokens * 3 * self.inter * self.hidden
 
-    def forward(self, h, ctx):
-        a = ops.linear_swiglu(h, self.w_gu, self.block, ctx.err if ctx is not None else None)
-        return ops.linear_parts(a, self.w_down, ctx.err if ctx is not None else None)   # joins the residual in float32
+    adds_in_place = True
+
+    def forward(self, h, ctx, add_to=None):
+        err = ctx.err if ctx is not None else None
+        a = ops.linear_swiglu(h, self.w_gu, self.block, err)
+        if add_to is not None and ops.linear_add(add_to, a, self.w_down):
+            return None
+        return ops.linear_parts(a, self.w_down, err)   # joins the residual in float32, inside the next norm

@@ -172,10 +172,62 @@ add_rmsnorm_row_kernel(float* __restrict__ x, const A* __restrict__ delta, const
     }
 }
 
+// Many rows (portions of prompts, bfloat16 out): a quarter of the threads per row, four float4 each, all loads
+// issued before the first use, so that eight blocks sit on an SM and keep 128 KB of loads in flight (with a
+// thread per float4 two blocks of 1,024 threads fit, and the memory system idles through their reductions).
+template <typename A, typename W, typename O>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_row4_kernel(float* __restrict__ x, const A* __restrict__ delta, const W* __restrict__ w,
+                        O* __restrict__ out, const int* __restrict__ rows, int D, float eps, int write_back) {
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int o = blockIdx.x;
+    const size_t r = rows ? (size_t)rows[o] : (size_t)o;
+    const int i = threadIdx.x, nt = blockDim.x;       // D == 16 * nt
+    float4 s[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) s[k] = reinterpret_cast<const float4*>(x + r * D)[i + k * nt];
+    if (delta) {
+        float4 dl[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) dl[k] = load4<A>(delta + r * D + 4 * (i + k * nt));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            s[k].x += dl[k].x;
+            s[k].y += dl[k].y;
+            s[k].z += dl[k].z;
+            s[k].w += dl[k].w;
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        ss += s[k].x * s[k].x;
+        ss += s[k].y * s[k].y;
+        ss += s[k].z * s[k].z;
+        ss += s[k].w * s[k].w;
+    }
+    ss = block_sum(ss, red);
+    const float rinv = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (write_back) reinterpret_cast<float4*>(x + r * D)[i + k * nt] = s[k];
+        const float4 wv = load4<W>(w + 4 * (i + k * nt));
+        store4<O>(out + (size_t)o * D + 4 * (i + k * nt),
+                  make_float4((s[k].x * rinv) * wv.x, (s[k].y * rinv) * wv.y, (s[k].z * rinv) * wv.z, (s[k].w * rinv) * wv.w));
+    }
+}
+
 template <typename A, typename W>
 static int launch_rmsnorm_o(float* x, const void* delta, const void* w, void* out, int out_dtype,
                             const int* rows, int n, int D, float eps, int write_back, int parts,
                             size_t part_stride, cudaStream_t stream) {
+    if (n >= 256 && parts == 1 && out_dtype == AIE_BF16 && D % 512 == 0 && D <= 4096) {
+        launch_pdl(add_rmsnorm_row4_kernel<A, W, bf16>, dim3(n), dim3(D / 16), 0, stream, x, (const A*)delta, (const W*)w,
+                   (bf16*)out, rows, D, eps, write_back);
+        AIE_LAUNCH_CHECK();
+    }
     if (D % 4 == 0 && D <= 4096) {
         const int threads = ((D / 4) + 31) / 32 * 32;
         if (out_dtype == AIE_F32)

@@ -402,10 +402,11 @@ def run_workload(torch, aie, name, pk):
     (add_request + step, as Engine.generate() does):
     serving1b — Llama-3.2-1B shape, 64 concurrent requests, prompts uniform in [128, 4096], 256 tokens each;
     long3b    — Llama-3.2-3B shape, one 32,768-token prompt in 2,048-token portions, then 512 greedy tokens.
-    Every step is put down with its wall-clock time (between returns of Engine.step(), which runs a step
-    ahead of the device), what it was made of, the bytes it had to read (every weight once and the cache of
-    its requests) and its flops; steps in which every request brings one token are the decode phase, the
-    others the prompt phase."""
+    Every step is put down with its time on the device (a CUDA event behind every step's launches: the host
+    runs ahead of the device, through prompt portions that sample nothing by many steps, so wall-clock times
+    of the calls say nothing about a step), what it was made of, the bytes it had to read (every weight once
+    and the cache of its requests) and its flops; steps in which every request brings one token are the decode
+    phase, the others the prompt phase."""
     g = torch.Generator().manual_seed(0)
     if name == "serving1b":
         cfg, n, new = LLAMA32_1B, 64, 256
@@ -420,7 +421,9 @@ def run_workload(torch, aie, name, pk):
     eng = aie.Engine(cfg, dtype="bf16", random_weights=True, seed=0, block_size=PAGE, **opts)
     prompts = [torch.randint(0, cfg["vocab_size"], (l,), generator=g).tolist() for l in lens]
     sp = aie.SamplingParams(max_tokens=new, ignore_eos=True)
-    eng.generate([prompts[0][:64]], aie.SamplingParams(max_tokens=4, ignore_eos=True))      # warm-up: kernels, graphs
+    # warm-up: a prompt of more than one full portion and a few tokens (kernels and library products of both step sizes)
+    warm = torch.randint(0, cfg["vocab_size"], (2048 + 100,), generator=g).tolist()
+    eng.generate([warm], aie.SamplingParams(max_tokens=4, ignore_eos=True))
     torch.cuda.synchronize()
     model, kv_tok = eng.model, eng.cache.kv_bytes_per_token()
     wbytes = model.step_weight_bytes()
@@ -430,22 +433,26 @@ def run_workload(torch, aie, name, pk):
     rids = [eng.add_request(p, sp) for p in prompts]
     generated = 0
     g0 = eng.runner.graph_launches
-    t0 = last = time.perf_counter()
+    marks = [torch.cuda.Event(enable_timing=True)]
+    marks[0].record()
+    owners = []
+    t0 = time.perf_counter()
     while eng.has_unfinished() or eng._inflight:
         idle = stream.query()              # nothing left on the device before this step is launched: it waited for the host
         steps_before, gl = eng.counters["steps"], eng.runner.graph_launches
         generated += sum(1 for _, tok, _ in eng.step() if tok is not None)
-        now = time.perf_counter()
         if eng.counters["steps"] == steps_before:
-            last = now
             continue
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        marks.append(ev)
         ctx = eng.runner.last_ctx
         R, T = ctx.real_R, ctx.real_T
         ph = phases["decode" if T == R else "prompt"]
+        owners.append(ph)
         held = float((ctx.h_ctx_len[:R] + ctx.h_q_len[:R]).sum())
         keys = float((ctx.h_q_len[:R] * ctx.h_ctx_len[:R] + ctx.h_q_len[:R] * (ctx.h_q_len[:R] + 1) / 2.0).sum()) / T
         ph["steps"] += 1
-        ph["s"] += now - last
         ph["tokens"] += T
         ph["requests"] += R
         ph["max_tokens"] = max(ph["max_tokens"], T)
@@ -453,9 +460,10 @@ def run_workload(torch, aie, name, pk):
         ph["flops"] += model.step_flops(T, keys, logit_rows=ctx.num_logit_rows)
         ph["graph"] += int(eng.runner.graph_launches > gl)
         ph["host_bound"] += int(bool(idle) and ph["steps"] > 1)
-        last = now
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    for i, ph in enumerate(owners):
+        ph["s"] += marks[i].elapsed_time(marks[i + 1]) * 1e-3
     outs = [eng.take(r) for r in rids]
     st = eng.stats()
     assert all(len(o) == new for o in outs) and generated == n * new

@@ -21,6 +21,27 @@ def err_word():
     return torch.zeros(1, dtype=torch.int32, device=DEV)
 
 
+@pytest.mark.parametrize("D", [512, 2048, 3072, 4096])
+@pytest.mark.parametrize("delta_kind", ["none", "bf16", "f32"])
+def test_add_rmsnorm_many_rows(D, delta_kind):
+    """Portions of prompts: hundreds of rows take a kernel of their own (four float4 per thread)."""
+    torch.manual_seed(D)
+    n = 300
+    x = torch.randn(n, D, device=DEV) * 3
+    delta = None if delta_kind == "none" else torch.randn(n, D, device=DEV).to(torch.bfloat16 if delta_kind == "bf16" else torch.float32)
+    w = (1 + 0.1 * torch.randn(D, device=DEV)).bfloat16()
+    s = x.double() + (delta.double() if delta is not None else 0)
+    want = pl.rms_norm(s, w.double(), 1e-5)
+    x_in = x.clone()
+    out = ops().add_rmsnorm(x_in, delta, w, 1e-5, torch.bfloat16)
+    assert torch.allclose(x_in.double(), s, atol=1e-6)
+    assert (out.double() - want).abs().max() <= 2e-2 * max(1.0, float(want.abs().max()))
+    rows = torch.arange(n - 1, -1, -1, device=DEV, dtype=torch.int32)
+    out2 = ops().add_rmsnorm(x.clone(), None, w, 1e-5, torch.bfloat16, rows=rows, write_back=False)
+    want2 = pl.rms_norm(x.double().flip(0), w.double(), 1e-5)
+    assert (out2.double() - want2).abs().max() <= 2e-2 * max(1.0, float(want2.abs().max()))
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("V,D", [(77, 24), (1000, 4096), (130, 200)])
 def test_embed_gather(dtype, V, D):

@@ -218,8 +218,11 @@ class StepRunner:
     brings one token (decode) are captured once per layout as a CUDA graph and
     replayed: the launch cost of some hundred kernels a step is paid once."""
 
-    def __init__(self, model, cache, use_graphs: Optional[bool] = None):
+    def __init__(self, model, cache, use_graphs: Optional[bool] = None, capture_at_use: int = 2):
+        """capture_at_use: a decode layout is captured at this use of it (2: a layout seen once is not worth a
+        capture; batches rounded up to a multiple of 8 and block-table widths in powers of two keep layouts few)."""
         self.model, self.cache = model, cache
+        self.capture_at_use = max(1, int(capture_at_use))
         self.device = model.device
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.last_ctx: Optional[StepContext] = None
@@ -277,7 +280,7 @@ class StepRunner:
             return self.model.forward(ctx, self.cache)
         buf = ctx.buffers
         if buf.graph is None:
-            if buf.uses < 3:                       # a layout seen once or twice is not worth a capture
+            if buf.uses < self.capture_at_use:     # a layout seen only once is not worth a capture
                 return self.model.forward(ctx, self.cache)
             from ..kernels.loader import LAUNCHES
             # This step runs eagerly (which is also the warm-up that a capture needs: library set-up) and

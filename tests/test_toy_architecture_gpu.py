@@ -244,7 +244,7 @@ def test_toy_architecture_replayed_whole_in_portions_and_mixed(tmp_path, dtype):
 
 
 def test_a_captured_step_updates_state_once(tmp_path):
-    """Decode steps of one layout: the first two run eagerly, the third runs eagerly and is captured, the
+    """Decode steps of one layout: the first runs eagerly, the second runs eagerly and is captured, the
     rest are replayed.  With a mixer that keeps state, every step must update it exactly once: the
     logits are those of the runner that never captures, at every step."""
     from ai_engine_b200.cache import PagedCache

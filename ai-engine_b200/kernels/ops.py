@@ -187,9 +187,14 @@ def tc_splits(T: int, N: int, K: int, bn: int) -> int:
     kb = (K + 63) // 64
     if tiles >= sm_count():
         return 1
-    return max(1, min((3 * sm_count()) // tiles, kb // 12))
+    return max(1, min((_TC_CTAS_PER_SM * sm_count()) // tiles, kb // _TC_MIN_KB))
 
 
+# split K: at least this many K blocks of 64 a part, at most this many CTAs an SM.  Swept inside whole decode steps
+# of 1, 8 and 64 requests (8B shape): (12, 3) and (12, 2) are equal and best; 8 or 6 blocks a part cost 0-2 %,
+# 20 / 32 / 56 blocks a part 2 / 7 / 20 %, four CTAs an SM 4-7 %.
+_TC_MIN_KB = 12
+_TC_CTAS_PER_SM = 3
 TC_SWIGLU_BLOCK = 64     # gate/up rows per half of a 128-row weight tile
 
 

@@ -383,3 +383,101 @@ def test_prenorm_block_alone(dtype):
                             pl.inv_freq_default(d, 10000.0))
     assert int(err.item()) == 0
     assert (got - want).abs().max() <= (1e-4 if dtype == torch.float32 else 5e-2)
+
+
+def test_a_toy_feed_forward_with_routing_is_registered_built_and_stepped():
+    """A feed-forward with experts and a router, defined here: router logits and the softmax over the chosen
+    experts in float32, the top two of three experts per token, each expert a SwiGLU of the package (the toy
+    composes parts; a real one would bring a grouped product).  Registered from outside, chosen for one layer
+    of two, fed in portions: the logits are the plain formulas'."""
+    from ai_engine_b200.cache import PagedCache
+    from ai_engine_b200.engine.step import StepRunner
+    from ai_engine_b200.kernels import ops
+    from ai_engine_b200.parts import (FeedForward, LayerSpec, Model, ModelSpec, PartSpec, RunStep, SwiGLU,
+                                      register_feed_forward)
+    from ai_engine_b200.weights import TensorSpec, from_tensors, random_tensors
+
+    E, TOPK, D, F, V = 3, 2, 32, 64, 50
+
+    class ToyRouted(FeedForward):
+        def __init__(self, spec, env):
+            super().__init__(spec, env)
+            self.experts = [SwiGLU(PartSpec("swiglu", dict(hidden_size=D, intermediate_size=F),
+                                            {k: f"{spec.tensors['prefix']}.e{e}.{k}" for k in ("gate", "up", "down")}), env)
+                            for e in range(E)]
+
+        def tensor_specs(self):
+            return [TensorSpec(self.spec.tensors["router"], (E, D))] + [s for x in self.experts for s in x.tensor_specs()]
+
+        def load(self, source):
+            self.router = source.get(self.spec.tensors["router"])
+            for x in self.experts:
+                x.load(source)
+
+        def flops(self, tokens, keys=0.0):
+            return 2.0 * tokens * E * D + TOPK * self.experts[0].flops(tokens)
+
+        def forward(self, h, ctx):
+            logits = ops.linear(h, self.router, torch.float32, ctx.err)              # [T, E] float32
+            top = torch.topk(logits, TOPK, dim=-1)
+            gate = torch.softmax(top.values, dim=-1)                                  # float32, over the chosen experts
+            out = torch.zeros(h.shape, dtype=torch.float32, device=h.device)
+            for e, x in enumerate(self.experts):
+                w = (gate * (top.indices == e)).sum(-1)                               # [T]: the token's weight for expert e
+                rows = torch.nonzero(w > 0).flatten()
+                if rows.numel():
+                    y = x.forward(h[rows].contiguous(), ctx)
+                    y = y.float().sum(0) if y.dim() == 3 else y.float()
+                    out.index_add_(0, rows, y * w[rows, None])
+            return out
+
+    register_feed_forward("toy_routed", ToyRouted)
+    layers = []
+    for i in range(2):
+        ffn = (PartSpec("toy_routed", {}, dict(router=f"l{i}.router", prefix=f"l{i}")) if i == 1 else
+               PartSpec("swiglu", dict(hidden_size=D, intermediate_size=48), dict(gate=f"l{i}.g", up=f"l{i}.u", down=f"l{i}.d")))
+        layers.append(LayerSpec("prenorm", {
+            "mixer_norm": PartSpec("rmsnorm", dict(size=D, eps=1e-5), dict(weight=f"l{i}.n1")),
+            "mixer": PartSpec("gqa_attention", dict(hidden_size=D, num_heads=2, num_kv_heads=1, head_dim=16, window=0,
+                                                    scale=None, position_encoding="rope"),
+                              dict(q=f"l{i}.q", k=f"l{i}.k", v=f"l{i}.v", o=f"l{i}.o")),
+            "ffn_norm": PartSpec("rmsnorm", dict(size=D, eps=1e-5), dict(weight=f"l{i}.n2")), "ffn": ffn}))
+    spec = ModelSpec(hidden_size=D, vocab_size=V, max_position=256,
+                     embedding=PartSpec("token_embedding", dict(vocab_size=V, hidden_size=D), dict(weight="emb")),
+                     layers=layers, order=[RunStep(0), RunStep(1)],
+                     final_norm=PartSpec("rmsnorm", dict(size=D, eps=1e-5), dict(weight="fn")),
+                     lm_head=PartSpec("lm_head", dict(vocab_size=V, hidden_size=D), dict(weight="head")),
+                     position_encodings={"rope": PartSpec("rotary", dict(rot_dim=16, theta=10000.0, scaling=None))})
+    model = Model(spec, torch.float32, DEV)
+    specs = model.tensor_specs()
+    stored = dict(random_tensors(specs, 4, torch.float32, "cpu", std=0.2, norm_std=0.1))
+    model.load(from_tensors(stored, specs, torch.float32, DEV))
+    assert model.step_flops(10) > 0 and model.layers[1].parts["ffn"].flops(1) == 2.0 * E * D + TOPK * 2.0 * 3 * F * D
+    cache = PagedCache(model.cache_requests(), 8, 16, 2, 128, torch.float32, DEV)
+    runner = StepRunner(model, cache)
+    ids = random_ids(37, V, 9)
+    got = run_in_portions(runner, cache, ids, [5, 2, 17, 1, 12])
+    # the plain formulas
+    w = {k: v.double() for k, v in stored.items()}
+    cfg = dict(heads=2, kv_heads=1, head_dim=16)
+    f = pl.inv_freq_default(16, 10000.0)
+    pos = torch.arange(len(ids))
+    x = pl.embed(torch.tensor(ids), w["emb"])
+    for i in range(2):
+        h = pl.rms_norm(x, w[f"l{i}.n1"], 1e-5)
+        x = x + pl.attention(h, w[f"l{i}.q"], w[f"l{i}.k"], w[f"l{i}.v"], w[f"l{i}.o"], pos, cfg, f)
+        h = pl.rms_norm(x, w[f"l{i}.n2"], 1e-5)
+        if i == 0:
+            x = x + pl.swiglu(h, w["l0.g"], w["l0.u"], w["l0.d"])
+        else:
+            logits = h @ w["l1.router"].T
+            top = torch.topk(logits, TOPK, dim=-1)
+            gate = torch.softmax(top.values, dim=-1)
+            y = torch.zeros_like(x)
+            for t in range(len(ids)):
+                for k in range(TOPK):
+                    e = int(top.indices[t, k])
+                    y[t] += gate[t, k] * pl.swiglu(h[t:t + 1], w[f"l1.e{e}.gate"], w[f"l1.e{e}.up"], w[f"l1.e{e}.down"])[0]
+            x = x + y
+    want = pl.rms_norm(x, w["fn"], 1e-5) @ w["head"].T
+    assert (got - want).abs().max() <= 1e-4, float((got - want).abs().max())

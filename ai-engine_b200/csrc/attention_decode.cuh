@@ -34,9 +34,14 @@ __device__ __forceinline__ unsigned dec_pack(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
+// A stage of a warp's ring holds SUB tiles of 16 keys: two at head size 64, so that a stage is 8 KB at both head
+// sizes (what a warp pays per stage — index arithmetic, the wait, the hand-over — does not depend on the
+// stage's bytes: with 4 KB stages the head-size-64 kernel ran at 3.3 TB/s where head size 128 ran at 4.9).
+template <int D> struct DecodeSub { static constexpr int value = D <= 64 ? 2 : 1; };
+
 // Shared memory of the decode kernel for head size D with NST stages per warp.
 template <int D, int NST> struct DecodeSmem {
-    static constexpr size_t stage_bytes = (size_t)2 * DEC_TILE * D * sizeof(bf16);      // keys + values
+    static constexpr size_t stage_bytes = (size_t)2 * DecodeSub<D>::value * DEC_TILE * D * sizeof(bf16);      // keys + values
     static constexpr size_t bytes = DEC_WARPS * NST * stage_bytes + DEC_MAX_PAGES * sizeof(int);
 };
 
@@ -59,9 +64,11 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     constexpr int CH = D / 8;       // 16-byte chunks per row
     constexpr int KPL = 32 / CH;    // keys one round of 32 copies covers
     constexpr int KS = D / 16;      // k-steps of q.k
+    constexpr int SUB = DecodeSub<D>::value;       // 16-key tiles per stage
+    constexpr int STILE = SUB * DEC_TILE;          // keys per stage
     static_assert(D % 64 == 0, "head size of the fast path");
     extern __shared__ __align__(128) unsigned char dec_smem[];
-    __shared__ int ok_s[DEC_WARPS][NST][DEC_TILE];
+    __shared__ int ok_s[DEC_WARPS][NST][STILE];
     __shared__ float mrg_m[DEC_WARPS][DEC_HEADS], mrg_l[DEC_WARPS][DEC_HEADS];
 
     // Everything up to the first use of q reads only what earlier steps left (the step's index
@@ -79,20 +86,20 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     const int hbase = kvh * G + g0;
     const int qrow = lane >> 2, qcol = (lane & 3) * 2;      // this lane's row and column pair of an MMA tile
 
-    bf16* stage0 = reinterpret_cast<bf16*>(dec_smem) + (size_t)warp * NST * 2 * DEC_TILE * D;
+    bf16* stage0 = reinterpret_cast<bf16*>(dec_smem) + (size_t)warp * NST * 2 * STILE * D;
     int* bt_s = reinterpret_cast<int*>(dec_smem + DEC_WARPS * NST * DecodeSmem<D, NST>::stage_bytes);
 
     int lo = 0;
     if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
     const int hi = pos + 1;
-    const int tiles_total = (hi - lo + DEC_TILE - 1) / DEC_TILE;
+    const int tiles_total = (hi - lo + STILE - 1) / STILE;       // stages' worth of keys
     const int tps = (tiles_total + S - 1) / S;
     const int tile_begin = s * tps, tile_end = min((s + 1) * tps, tiles_total);
 
     // the block-table entries of this CTA's keys, once
-    const int pg0 = (lo + tile_begin * DEC_TILE) / P;
+    const int pg0 = (lo + tile_begin * STILE) / P;
     {
-        const int last_key = min(hi, lo + tile_end * DEC_TILE) - 1;
+        const int last_key = min(hi, lo + tile_end * STILE) - 1;
         const int npg = tile_end > tile_begin ? last_key / P - pg0 + 1 : 0;
         const int* bt = block_table + (size_t)row * bt_width;
         for (int i = tid; i < npg && i < DEC_MAX_PAGES; i += DEC_WARPS * 32)
@@ -103,36 +110,40 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     const int first = tile_begin + warp;
     const int n_my = first < tile_end ? (tile_end - first + DEC_WARPS - 1) / DEC_WARPS : 0;
 
-    // stage the keys and values of this warp's i-th tile (zero-filled where there is no key)
+    // stage the keys and values of this warp's i-th stage (zero-filled where there is no key)
     auto issue = [&](int i) {
         if (i < n_my) {
             const int st = i % NST;
-            const int kbase = lo + (first + i * DEC_WARPS) * DEC_TILE;
-            if (!waited && kbase + DEC_TILE > pos) {      // this tile holds the token written in this step
+            const int kbase0 = lo + (first + i * DEC_WARPS) * STILE;
+            if (!waited && kbase0 + STILE > pos) {      // this stage holds the token written in this step
                 pdl_wait();
                 waited = true;
             }
-            int prow = -1;
-            if (lane < DEC_TILE) {
-                const int key = kbase + lane;
-                if (key < hi) {
-                    const int pidx = key / P;
-                    const int page = (pidx - pg0 < DEC_MAX_PAGES) ? bt_s[pidx - pg0] : -1;
-                    if (page >= 0 && page < num_pages) prow = (page * K + kvh) * P + (key - pidx * P);
-                    else atomicOr(err, AIE_DEV_PAGE_OOB);
-                }
-                ok_s[warp][st][lane] = prow >= 0;
-            }
-            bf16* ks = stage0 + (size_t)st * 2 * DEC_TILE * D;
-            bf16* vs = ks + DEC_TILE * D;
-            const int cc = lane % CH, kq = lane / CH;
+            bf16* ks = stage0 + (size_t)st * 2 * STILE * D;
+            bf16* vs = ks + STILE * D;
 #pragma unroll
-            for (int r = 0; r < DEC_TILE / KPL; ++r) {
-                const int kidx = kq + r * KPL;
-                const int pr = __shfl_sync(0xffffffffu, prow, kidx);
-                const size_t off = (size_t)(pr >= 0 ? pr : 0) * D + cc * 8;
-                dec_cp_async16(dec_at<D>(ks, kidx, cc), k_pages + off, pr >= 0);
-                dec_cp_async16(dec_at<D>(vs, kidx, cc), v_pages + off, pr >= 0);
+            for (int sub = 0; sub < SUB; ++sub) {
+                const int kbase = kbase0 + sub * DEC_TILE;
+                int prow = -1;
+                if (lane < DEC_TILE) {
+                    const int key = kbase + lane;
+                    if (key < hi) {
+                        const int pidx = key / P;
+                        const int page = (pidx - pg0 < DEC_MAX_PAGES) ? bt_s[pidx - pg0] : -1;
+                        if (page >= 0 && page < num_pages) prow = (page * K + kvh) * P + (key - pidx * P);
+                        else atomicOr(err, AIE_DEV_PAGE_OOB);
+                    }
+                    ok_s[warp][st][sub * DEC_TILE + lane] = prow >= 0;
+                }
+                const int cc = lane % CH, kq = lane / CH;
+#pragma unroll
+                for (int r = 0; r < DEC_TILE / KPL; ++r) {
+                    const int kidx = kq + r * KPL;
+                    const int pr = __shfl_sync(0xffffffffu, prow, kidx);
+                    const size_t off = (size_t)(pr >= 0 ? pr : 0) * D + cc * 8;
+                    dec_cp_async16(dec_at<D>(ks + sub * DEC_TILE * D, kidx, cc), k_pages + off, pr >= 0);
+                    dec_cp_async16(dec_at<D>(vs + sub * DEC_TILE * D, kidx, cc), v_pages + off, pr >= 0);
+                }
             }
         }
         asm volatile("cp.async.commit_group;\n" ::);
@@ -169,8 +180,10 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         asm volatile("cp.async.wait_group %0;\n" ::"n"(NST - 1));
         __syncwarp();
         const int st = i % NST;
-        bf16* ks_t = stage0 + (size_t)st * 2 * DEC_TILE * D;
-        bf16* vs_t = ks_t + DEC_TILE * D;
+#pragma unroll
+        for (int sub = 0; sub < SUB; ++sub) {
+        bf16* ks_t = stage0 + (size_t)st * 2 * STILE * D + sub * DEC_TILE * D;
+        bf16* vs_t = stage0 + (size_t)st * 2 * STILE * D + STILE * D + sub * DEC_TILE * D;
 
         // scores of the 16 keys: two 8-key column tiles
         float sc[2][4];
@@ -191,7 +204,7 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         for (int j = 0; j < 2; ++j)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const bool valid = ok_s[warp][st][j * 8 + qcol + e] != 0;
+                const bool valid = ok_s[warp][st][sub * DEC_TILE + j * 8 + qcol + e] != 0;
                 sc[j][e] = valid ? sc[j][e] * scale : -INFINITY;
                 tmax = fmaxf(tmax, sc[j][e]);
             }
@@ -223,6 +236,7 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
             dec_ldsm_x4_t(b0, b1, b2, b3, dec_at<D>(vs_t, (mid & 1) * 8 + (lane & 7), jd + (mid >> 1)));
             dec_mma(o[jd], pa0, 0u, pa2, 0u, b0, b1);
             dec_mma(o[jd + 1], pa0, 0u, pa2, 0u, b2, b3);
+        }
         }
         __syncwarp();      // the stage is free again
     }
@@ -351,7 +365,9 @@ static int launch_decode(int GC, dim3 grid, cudaStream_t st, const bf16* q, cons
                          const int* bt, int btw, int np, int P, int H, int K, int G, int window, float scale,
                          int S, int* counters, unsigned* err) {
     if (GC < 1 || GC > DEC_HEADS) return AIE_UNSUPPORTED;
-    constexpr int NST = D >= 128 ? 3 : 4;
+    // stages of 8 KB (two 16-key tiles at head size 64, one at 128), rings of 3, two CTAs to an SM (at head size 64,
+    // rings of 2 with three CTAs to an SM were measured 2 % slower in a whole step)
+    constexpr int NST = 3;
     constexpr size_t smem = DecodeSmem<D, NST>::bytes;
     auto kern = paged_decode_kernel<D, NST>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

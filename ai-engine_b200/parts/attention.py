@@ -24,7 +24,9 @@ class AttentionWork(StepPlanner):
     """The work lists of the attention kernels, derived from a step's generic arrays: `decode_tokens`
     (rows of requests that bring one token, for the split-KV kernel), `other_tokens` (rows of all others),
     `prefill_tiles` [n, 2] = (request row, offset of a tile of `ops.PREFILL_TILE` tokens among the tokens it
-    brings), `n_decode`, and `max_decode_len` (the most keys a lone token reads: of the layout's widest
+    brings), `n_decode`, and `max_decode_len`.  The lone-token rows are listed longest context first: the
+    decode kernel's CTAs start in that order, so when there are more of them than fit the machine at once the
+    long requests do not start last (the most keys a lone token reads: of the layout's widest
     possible request when the step may be replayed from a graph)."""
 
     key = "attention"
@@ -32,12 +34,12 @@ class AttentionWork(StepPlanner):
     def plan(self, ctx):
         q_len, q_start, R, T = ctx.h_q_len, ctx.h_q_start, ctx.R, ctx.T
         if T == R:        # every request brings one token
-            dec, other = q_start, np.empty(0, dtype=np.int32)
+            dec, other = q_start[np.argsort(-ctx.h_ctx_len, kind="stable")], np.empty(0, dtype=np.int32)
             n_decode, max_decode_len = R, ctx.max_total_len
             tiles = np.empty((0, 2), dtype=np.int32)
         else:
             is_dec = q_len == 1
-            dec = q_start[is_dec]
+            dec = q_start[is_dec][np.argsort(-ctx.h_ctx_len[is_dec], kind="stable")]
             other = np.nonzero(np.repeat(~is_dec, q_len))[0].astype(np.int32)
             n_decode = int(dec.shape[0])
             max_decode_len = int((ctx.h_ctx_len[is_dec] + 1).max()) if n_decode else 0

@@ -361,7 +361,8 @@ def time_decode_attention(torch, H, K, d, lens):
         bt[r, :n] = perm[at:at + n]
         at += n
     i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=dev)
-    pos, req, dec = i32([n - 1 for n in lens]), i32(list(range(R))), i32(list(range(R)))
+    # lone-token rows in the order the engine lists them: longest context first
+    pos, req, dec = i32([n - 1 for n in lens]), i32(list(range(R))), i32(sorted(range(R), key=lambda r: -lens[r]))
     err = torch.zeros(1, dtype=torch.int32, device=dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     splits = ops.decode_splits(R, K, H // K, max(lens), bt.shape[1])

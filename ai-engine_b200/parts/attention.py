@@ -43,8 +43,10 @@ class AttentionWork(StepPlanner):
             other = np.nonzero(np.repeat(~is_dec, q_len))[0].astype(np.int32)
             n_decode = int(dec.shape[0])
             max_decode_len = int((ctx.h_ctx_len[is_dec] + 1).max()) if n_decode else 0
-            tiles = np.asarray([(r, o) for r in range(R) if q_len[r] != 1
-                                for o in range(0, int(q_len[r]), ops.PREFILL_TILE)], dtype=np.int32).reshape(-1, 2)
+            # tiles by the keys they read, fewest first: the prompt kernels start their CTAs from the end of the list
+            tiles = sorted(((int(ctx.h_ctx_len[r]) + o, r, o) for r in range(R) if q_len[r] != 1
+                            for o in range(0, int(q_len[r]), ops.PREFILL_TILE)))
+            tiles = np.asarray([(r, o) for _, r, o in tiles], dtype=np.int32).reshape(-1, 2)
         if ctx.bucketed and n_decode:
             max_decode_len = ctx.bt_width * ctx.page_size      # a property of the layout, not of the step
         return (dict(decode_tokens=dec.astype(np.int32), other_tokens=other, prefill_tiles=tiles),

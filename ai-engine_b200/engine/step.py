@@ -259,11 +259,12 @@ class StepRunner:
         graphed = self.use_graphs and decode_only
         n_real, real_rows = len(entries), None
         if graphed and self.pad_decode and n_real > 8 and n_real % 8:
-            # the number of requests of a decode step is rounded up to a multiple of 8 by repeating the first
-            # entry (the same token at the same place: it writes the same key and value again), so that
-            # batches that shrink and grow request by request share their layouts, and with them their graphs
+            # the number of requests of a decode step is rounded up to a multiple of 8 by repeating the entry
+            # with the fewest cached tokens (the same token at the same place: it writes the same key and value
+            # again, and reads the shortest cache), so that batches that shrink and grow request by request share
+            # their layouts, and with them their graphs
             real_rows = sum(len(e.want) for e in entries)
-            e0 = entries[0]
+            e0 = min(entries, key=lambda e: e.start)
             entries = list(entries) + [StepEntry(e0.slot, e0.start, e0.tokens, [0], e0.src)] * (8 - n_real % 8)
         ctx = StepContext(entries, self.cache, self.device, self.err, self.buffers, bucket_width=graphed,
                           planners=self.planners, n_live=n_real)

@@ -385,7 +385,7 @@ def test_decode_steps_replayed_from_a_graph_match_eager_steps(tmp_path):
 
 
 def test_decode_batches_rounded_up_to_a_multiple_of_eight_share_a_graph(tmp_path):
-    """Decode steps of 9 to 16 requests run as 16 rows (the first entry repeated): one layout, one graph, and
+    """Decode steps of 9 to 16 requests run as 16 rows (the entry with the shortest cache repeated): one layout, one graph, and
     the logits of every live row are what the step of exactly those rows gives, and the plain implementation's."""
     from ai_engine_b200.cache import PagedCache
     from ai_engine_b200.engine.loading import load_model

@@ -68,8 +68,8 @@ extern "C" int aie_paged_attention_prefill(const void* q, const void* k_pages, c
     if (n_tiles <= 0) return 0;
     if (K <= 0 || H % K) return AIE_BAD_ARG;
     if (d != 64 && d != 128) return AIE_UNSUPPORTED;
-    if (H > 65535) return AIE_UNSUPPORTED;
-    dim3 grid(n_tiles, H);
+    if (n_tiles > 65535) return AIE_UNSUPPORTED;
+    dim3 grid(H, n_tiles);
     if (d == 64) {
         const size_t smem = prefill_smem_bytes<64>();
         cudaFuncSetAttribute(paged_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -71,9 +71,10 @@ paged_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_page
     int* row_s = reinterpret_cast<int*>(v_s + 2 * PF_N * D);   // [2][64] page rows of the tile's keys
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int tile_i = (int)gridDim.x - 1 - (int)blockIdx.x;      // the list holds the tiles fewest keys first: start the longest
+    // the list holds the tiles fewest keys first: start the longest, for all heads (heads run fastest in the grid)
+    const int tile_i = (int)gridDim.y - 1 - (int)blockIdx.y;
     const int r = tiles[2 * tile_i], q_off = tiles[2 * tile_i + 1];
-    const int h = blockIdx.y, kvh = h / (H / K);
+    const int h = blockIdx.x, kvh = h / (H / K);
     const int t0 = q_start[r] + q_off;
     const int rows_valid = min(PF_M, q_len[r] - q_off);
     const int p0 = ctx_len[r] + q_off;              // position of the tile's first query

@@ -136,9 +136,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     unsigned char* v_s = sm + AtSmem<HD>::v_off;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tile_i = n_tiles - 1 - (int)blockIdx.x;      // later tiles hold more keys: start them first
+    // later tiles hold more keys: start them first, for all heads (heads run fastest in the grid, so the heads
+    // of a group, which read the same keys, start side by side)
+    const int tile_i = n_tiles - 1 - (int)blockIdx.y;
     const int r = tiles[2 * tile_i], q_off = tiles[2 * tile_i + 1];
-    const int h = blockIdx.y, kvh = h / (H / K);
+    const int h = blockIdx.x, kvh = h / (H / K);
     const int t0 = q_start[r] + q_off;
     const int rows_valid = min(AT_M, q_len[r] - q_off);
     const int p0 = ctx_len[r] + q_off;                 // position of the tile's first query
@@ -437,7 +439,7 @@ static int launch_prefill_tc(const void* q, const void* k_pages, const void* v_p
     rc = tc_make_map_rows8(&mv, v_pages, rows, HD / 64, P / 8);
     if (rc) return rc;
     cudaFuncSetAttribute(paged_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, AtSmem<HD>::bytes);
-    paged_prefill_tc_kernel<HD><<<dim3(n_tiles, H), AT_THREADS, AtSmem<HD>::bytes, stream>>>(
+    paged_prefill_tc_kernel<HD><<<dim3(H, n_tiles), AT_THREADS, AtSmem<HD>::bytes, stream>>>(
         mq, mk, mv, (bf16*)out, tiles, n_tiles, q_start, q_len, ctx_len, block_table, bt_width, num_pages, P, H, K,
         scale, err);
     AIE_LAUNCH_CHECK();
@@ -454,7 +456,7 @@ extern "C" int aie_paged_attention_prefill_tc(const void* q, const void* k_pages
                                               float scale, unsigned* err, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (K <= 0 || H % K) return AIE_BAD_ARG;
-    if ((d != 64 && d != 128) || P < 8 || P > 128 || 128 % P || H > 65535 || window > 0) return AIE_UNSUPPORTED;
+    if ((d != 64 && d != 128) || P < 8 || P > 128 || 128 % P || n_tiles > 65535 || window > 0) return AIE_UNSUPPORTED;
     if (((size_t)q & 15) || ((size_t)k_pages & 15) || ((size_t)v_pages & 15)) return AIE_UNSUPPORTED;
 #define ARGS q, k_pages, v_pages, out, tiles, n_tiles, q_start, q_len, ctx_len, block_table, bt_width, num_pages, P, T, H, K, \
              scale, err, stream

@@ -425,6 +425,414 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     }
 }
 
+// ---------------------------------------------------------------------------
+// The same for two tiles of 128 queries of one head per CTA (256 consecutive tokens of a request).
+// Tensor memory holds one score buffer and one output per query tile (2 x 128 + 2 x head size columns);
+// the alternation is between the tiles, not between two buffers of one tile: while the softmax warps of
+// tile A exponentiate, the tensor pipe multiplies for tile B.  Keys and values are loaded once for both
+// tiles, into one ring of slots (K0 V0 K1 V1 ...), each slot with its own full / empty barrier.
+//   warps 0-3   softmax of tile A, one thread per query row
+//   warps 4-7   softmax of tile B
+//   warp 8      loader (as above)
+//   warp 9      one lane issues tile A's products: per key tile j its P . V, then its scores for j + 1, which
+//               go over the tile's own P (the tensor pipe runs what one thread issues in order, so the
+//               P . V has read it)
+//   warp 10     the same for tile B: one issuing thread for both tiles was busy all the time (each mbarrier
+//               test costs it some hundred cycles while the pipe reads shared memory), and the tiles' chains
+//               softmax -> P . V -> scores -> softmax waited for it
+//   warp 11     nothing: it fills the third warpgroup, which hands most of its registers to the softmax
+//               warpgroups (setmaxnreg), whose threads keep a row of 128 scores each
+// Tile B sees 128 more keys than tile A: A takes part in key tiles 0 .. nA - 1, B in all of the unit's.
+#define AT2_THREADS 384
+#define AT2_BAR_P 1         // named barriers 1, 2: the probabilities of tile A / B are in tensor memory
+
+template <int HD> struct At2Smem {
+    static constexpr int HV = HD / 64;
+    static constexpr int tile = HV * AT_HALF_BYTES;
+    static constexpr int NS = HD >= 128 ? 5 : 8;      // slots of the key / value ring
+    // [alignment slack | 1 KB: barriers | Q of tile A | Q of tile B | NS slots]
+    static constexpr int q_off = 1024, kv_off = q_off + 2 * tile, end = kv_off + NS * tile;
+    static constexpr int bytes = 1024 + end;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(AT2_THREADS, 1)
+paged_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
+                             const int* __restrict__ units, int n_units, const int* __restrict__ q_start,
+                             const int* __restrict__ q_len, const int* __restrict__ ctx_len,
+                             const int* __restrict__ block_table, int bt_width, int num_pages, int P, int H, int K,
+                             float scale, unsigned* err) {
+    extern __shared__ unsigned char at_raw[];
+    unsigned char* sm = reinterpret_cast<unsigned char*>(((size_t)at_raw + 1023) & ~(size_t)1023);
+    constexpr int NS = At2Smem<HD>::NS;
+    unsigned long long* q_full = reinterpret_cast<unsigned long long*>(sm);
+    unsigned long long* full = q_full + 1;         // [NS] the slot's keys or values have landed
+    unsigned long long* empty = full + NS;         // [NS] the products have read the slot
+    unsigned long long* s_full = empty + NS;       // [2] scores of tile A / B
+    unsigned long long* o_done = s_full + 2;       // [2] the last P . V of tile A / B landed
+    unsigned long long* v_fixed = o_done + 2;
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(v_fixed + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    constexpr int HV = HD / 64;
+    constexpr int TILE = At2Smem<HD>::tile;
+    constexpr int GROUP = HV * 1024;
+    unsigned char* q_s = sm + At2Smem<HD>::q_off;      // tile t at + t * TILE
+    unsigned char* kv_s = sm + At2Smem<HD>::kv_off;    // slot s at + s * TILE
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int unit_i = n_units - 1 - (int)blockIdx.y;      // later units hold more keys: start them first
+    const int r = units[2 * unit_i], q_off = units[2 * unit_i + 1];
+    const int h = blockIdx.x, kvh = h / (H / K);
+    const int t0 = q_start[r] + q_off;
+    const int rows_all = min(2 * AT_M, q_len[r] - q_off);
+    const int rows_a = min(AT_M, rows_all), rows_b = rows_all - rows_a;
+    const int p0 = ctx_len[r] + q_off;                 // position of the unit's first query
+    const int p_last = p0 + rows_all - 1;              // and of its last valid one
+    const int n_kt = p_last / AT_N + 1;                // key tiles 0 .. n_kt - 1
+    const int n_a = (p0 + rows_a - 1) / AT_N + 1;      // of these, tile A reads the first n_a,
+    const int n_b = rows_b > 0 ? n_kt : 0;             // tile B all (none when the unit has no tile B)
+    const int ppt = AT_N / P;
+
+    if (tid == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(&s_full[t], 1);
+            mbar_init(&o_done[t], 1);
+        }
+        mbar_init(v_fixed, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 9) {    // tensor memory: scores (and P) of tile t at columns [128 t, 128 t + 128), outputs at
+                        // [256 + t * head size, ...)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(tmem_slot)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_base = *tmem_slot;
+
+    // registers: the launch allots 168 to each of the 384 threads; the third warpgroup keeps 88 and the softmax
+    // warpgroups take 208 each.  88 + 2 x 208 = 3 x 168: an increase waits, without a limit, for registers that a
+    // decrease has released, so the three must never sum to more than the launch allotted.
+    if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;\n");
+    if (warp == 8) {
+        if (lane == 0) {
+            // queries: rows t0 .. t0 + 255 of q [T, H * head size], columns of head h (rows past T read as zeros)
+            mbar_expect_tx(q_full, 2 * TILE);
+            for (int t = 0; t < 2; ++t)
+                for (int hv = 0; hv < HV; ++hv)
+                    tma_load_2d(q_s + t * TILE + hv * AT_HALF_BYTES, &map_q, q_full, h * HD + hv * 64, t0 + t * AT_M);
+        }
+        const int* bt = block_table + (size_t)r * bt_width;
+        const int lp = 31 - __clz(P);
+        auto page_of = [&](int jj) {
+            const int pidx = jj * ppt + lane;
+            return (lane < ppt && (pidx << lp) <= p_last && pidx < bt_width) ? bt[pidx] : -1;
+        };
+        int page = page_of(0);
+        bool ok = true;
+        int slot = 0, ph = 0;           // ring position of the next item (K0 V0 K1 V1 ...)
+        for (int j = 0; j < n_kt && ok; ++j) {
+            const int page_next = j + 1 < n_kt ? page_of(j + 1) : -1;
+            const int n_pages = min(ppt, ((p_last - j * AT_N) >> lp) + 1);
+            const bool have = lane < n_pages;
+            const bool valid = have && page >= 0 && page < num_pages;
+            if (have && !valid) atomicOr(err, AIE_DEV_PAGE_OOB);
+            const int group0 = (((valid ? page : 0) * K + kvh) << lp) >> 3;
+#pragma unroll
+            for (int item = 0; item < 2; ++item) {
+                if (lane == 0) {
+                    ok = mbar_wait(&empty[slot], (unsigned)(ph ^ 1), abort_flag, err);
+                    if (ok) mbar_expect_tx(&full[slot], (unsigned)n_pages * (unsigned)P * (unsigned)(HD * 2));
+                }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+                if (have)
+                    tma_load_4d(kv_s + slot * TILE + lane * P * (HD * 2), item == 0 ? &map_k : &map_v, &full[slot], 0, 0, 0,
+                                group0);
+                __syncwarp();
+                if (++slot == NS) {
+                    slot = 0;
+                    ph ^= 1;
+                }
+            }
+            page = page_next;
+        }
+        __syncwarp();
+        // the last tile: zero the value rows of keys past the sequence's end (whole warp)
+        {
+            const int item = 2 * (n_kt - 1) + 1, st = item % NS;
+            const int first_bad = p_last + 1 - (n_kt - 1) * AT_N;
+            bool ok2 = ok;
+            if (ok2 && first_bad < AT_N) {
+                if (lane == 0) ok2 = mbar_wait(&full[st], (unsigned)((item / NS) & 1), abort_flag, err);
+                ok2 = __shfl_sync(0xffffffffu, ok2 ? 1 : 0, 0) != 0;
+                if (ok2) {
+                    unsigned char* vd = kv_s + st * TILE;
+                    const int n_bad = AT_N - first_bad;
+                    for (int i = lane; i < n_bad * HV * 8; i += 32) {
+                        const int row = first_bad + i / (HV * 8), c = i % (HV * 8);
+                        *reinterpret_cast<uint4*>(vd + (row >> 3) * GROUP + (c >> 3) * 1024 + (row & 7) * 128 + (c & 7) * 16) =
+                            make_uint4(0, 0, 0, 0);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive_plain(v_fixed);
+        }
+    } else if (warp == 9) {
+        // The whole warp walks the tiles (it meets the softmax warps at a named barrier); lane 0 issues.
+        const unsigned idesc_s = umma_idesc(AT_N), idesc_o = umma_idesc(HD, true);
+        const unsigned long long dq0 = umma_desc(q_s), dk0 = umma_desc(kv_s, GROUP), dv0 = umma_desc_mn(kv_s, 1024, GROUP);
+        // S_t = Q_t . K^T with the keys of ring slot `slot`
+        auto issue_scores = [&](int t, int slot) {
+            const unsigned long long dq = dq0 + (unsigned long long)((t * TILE) >> 4);
+            const unsigned long long dk = dk0 + (unsigned long long)((slot * TILE) >> 4);
+            const unsigned ts = tmem_base + (unsigned)(t * AT_N);
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks)
+                umma(ts, dq + (unsigned long long)((((ks >> 2) * AT_HALF_BYTES) >> 4) + 2 * (ks & 3)),
+                     dk + (unsigned long long)((((ks >> 2) * 1024) >> 4) + 2 * (ks & 3)), idesc_s, ks > 0 ? 1u : 0u);
+        };
+        // O_t += P_t . V with the values of ring slot `slot`
+        auto issue_pv = [&](int t, int slot, bool first) {
+            const unsigned long long dv = dv0 + (unsigned long long)((slot * TILE) >> 4);
+            const unsigned tp = tmem_base + (unsigned)(t * AT_N), to = tmem_base + 256u + (unsigned)(t * HD);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+                umma_a_tmem(to, tp + (unsigned)(ks * 8), dv + (unsigned long long)((ks * 2 * GROUP) >> 4), idesc_o,
+                            (!first || ks > 0) ? 1u : 0u);
+        };
+        auto advance = [&](int& s_, int& p_) {
+            if (++s_ == NS) {
+                s_ = 0;
+                p_ ^= 1;
+            }
+        };
+        int sv = 0, pv = 0;             // ring position of K(0), then of V(j)
+        bool ok = true;                 // lane 0's; once false, the warp only keeps its appointments at the barriers
+        if (lane == 0) {
+            ok = mbar_wait(q_full, 0, abort_flag, err);
+            if (ok) ok = mbar_wait(&full[sv], 0, abort_flag, err);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                issue_scores(0, sv);
+                umma_commit(&s_full[0]);
+                if (n_b > 0) {
+                    issue_scores(1, sv);
+                    umma_commit(&s_full[1]);
+                }
+                umma_commit(&empty[sv]);
+            }
+        }
+        advance(sv, pv);
+        for (int j = 0; j < n_kt; ++j) {
+            int sk1 = sv, pk1 = pv;     // ring position of K(j + 1)
+            advance(sk1, pk1);
+            const bool in_b = j < n_b, next_b = j + 1 < n_b;
+            // operands first: the values of this tile and the keys of the next landed long ago as a rule, and
+            // nothing but the probabilities then stands between the end of a softmax and its products
+            if (lane == 0 && ok) {
+                ok = mbar_wait(&full[sv], (unsigned)pv, abort_flag, err);
+                if (ok && j == n_kt - 1) ok = mbar_wait(v_fixed, 0, abort_flag, err);
+                if (ok && j + 1 < n_kt) ok = mbar_wait(&full[sk1], (unsigned)pk1, abort_flag, err);
+            }
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                const int n_t = t == 0 ? n_a : n_b;
+                if (j >= n_t) continue;
+                // the tile's probabilities are written: its 128 softmax threads arrive, this warp waits.  A
+                // hardware barrier: an mbarrier test costs the issuing thread some hundred cycles while the
+                // tensor pipe reads shared memory, and stood between every softmax and its products.
+                asm volatile("bar.sync %0, %1;\n" ::"r"(AT2_BAR_P + t), "r"(AT_M + 32) : "memory");
+                if (lane != 0 || !ok) continue;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                // P . V, then at once the next scores over the same columns (which the P . V has read: the
+                // pipe runs what one thread issues in order); the commits follow both
+                issue_pv(t, sv, j == 0);
+                if (j + 1 < n_t) {
+                    issue_scores(t, sk1);
+                    umma_commit(&s_full[t]);        // covers the P . V too: the softmax may rescale O once it sees it
+                } else {
+                    umma_commit(&o_done[t]);        // the tile's last product
+                }
+                if (t == 1 || !in_b) umma_commit(&empty[sv]);                          // last reader of the values
+                if (j + 1 < n_t && (t == 1 || !next_b)) umma_commit(&empty[sk1]);     // and of the next keys
+            }
+            sv = sk1;
+            pv = pk1;
+            advance(sv, pv);
+        }
+    }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;\n");
+        // softmax of tile t = warp / 4: one thread per query row (warp w reads lanes 32 * (w % 4) .. + 31)
+        const int t = warp >> 2;
+        const int n_t = t == 0 ? n_a : n_b;
+        const int rows_valid = t == 0 ? rows_a : rows_b;
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const int p0_t = p0 + t * AT_M;
+        const int qpos = p0_t + row;
+        const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
+        const unsigned tmem_s = tmem_base + (unsigned)(t * AT_N);
+        const unsigned tmem_o = tmem_base + 256u + (unsigned)(t * HD);
+        const float sl2 = scale * 1.4426950408889634f;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_t; ++j) {
+            // (a warp that gave up still arrives at the barrier for every tile: the issuing warp waits there
+            // without a limit)
+            if (ok) {
+                if (lane == 0) ok = mbar_wait(&s_full[t], (unsigned)(j & 1), abort_flag, err);
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            }
+            if (!ok) {
+                asm volatile("bar.arrive %0, %1;\n" ::"r"(AT2_BAR_P + t), "r"(AT_M + 32) : "memory");
+                continue;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int kbase = j * AT_N;
+            const bool edge = kbase + AT_N - 1 > p0_t;
+            unsigned sv[128];
+            AT_LD32((sv + 0), tmem_s + lane_addr + 0);
+            AT_LD32((sv + 32), tmem_s + lane_addr + 32);
+            AT_LD32((sv + 64), tmem_s + lane_addr + 64);
+            AT_LD32((sv + 96), tmem_s + lane_addr + 96);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            if (edge) {
+#pragma unroll
+                for (int i = 0; i < 128; ++i)
+                    if (kbase + i > qpos) sv[i] = 0xff800000u;
+            }
+            float tmax = -INFINITY, tmax2 = -INFINITY, tmax3 = -INFINITY, tmax4 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 128; i += 8) {
+                tmax = at_max3(tmax, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+                tmax2 = at_max3(tmax2, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+                tmax3 = at_max3(tmax3, __uint_as_float(sv[i + 4]), __uint_as_float(sv[i + 5]));
+                tmax4 = at_max3(tmax4, __uint_as_float(sv[i + 6]), __uint_as_float(sv[i + 7]));
+            }
+            tmax = fmaxf(at_max3(tmax, tmax2, tmax3), tmax4) * sl2;
+            float m_new = m_run, corr = 1.0f;
+            if (tmax > m_run + AT_RESCALE_STEP) {
+                m_new = tmax;
+                corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - tmax);
+            }
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            m_run = m_new;
+            // (the previous P . V has landed: the commit that announced these scores was issued after it)
+            if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    unsigned ov[32];
+                    AT_LD32(ov, tmem_o + lane_addr + c0);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+                    AT_ST32(ov, tmem_o + lane_addr + c0);
+                }
+            }
+            const unsigned long long sl2_2 = at_pack2(sl2, sl2), negm_2 = at_pack2(-m_use, -m_use);
+            unsigned long long psum2 = 0ull, psum2b = 0ull;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                unsigned pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    unsigned long long x2;
+                    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(x2) : "l"(at_pack2(__uint_as_float(sv[32 * c + i]), __uint_as_float(sv[32 * c + i + 1]))), "l"(sl2_2), "l"(negm_2));
+                    float e0, e1;
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(at_lo(x2)));
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(at_hi(x2)));
+                    if (i & 2) asm("add.rn.f32x2 %0, %1, %2;" : "=l"(psum2b) : "l"(psum2b), "l"(at_pack2(e0, e1)));
+                    else asm("add.rn.f32x2 %0, %1, %2;" : "=l"(psum2) : "l"(psum2), "l"(at_pack2(e0, e1)));
+                    __nv_bfloat162 bb = __floats2bfloat162_rn(e0, e1);
+                    pk[i >> 1] = *reinterpret_cast<unsigned*>(&bb);
+                }
+                AT_ST16(pk, tmem_s + lane_addr + (unsigned)(16 * c));
+            }
+            asm("add.rn.f32x2 %0, %1, %2;" : "=l"(psum2) : "l"(psum2), "l"(psum2b));
+            l_run = l_run * corr + (at_lo(psum2) + at_hi(psum2));
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            asm volatile("bar.arrive %0, %1;\n" ::"r"(AT2_BAR_P + t), "r"(AT_M + 32) : "memory");
+        }
+        if (ok && n_t > 0) {
+            if (lane == 0) ok = mbar_wait(&o_done[t], 0, abort_flag, err);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        }
+        if (ok && n_t > 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            bf16* dst = out + ((size_t)(t0 + t * AT_M + row) * H + h) * HD;
+#pragma unroll
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                unsigned ov[32];
+                AT_LD32(ov, tmem_o + lane_addr + c0);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (row < rows_valid) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        unsigned pk[4];
+#pragma unroll
+                        for (int e = 0; e < 8; e += 2) {
+                            __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(ov[i + e]) * inv,
+                                                                     __uint_as_float(ov[i + e + 1]) * inv);
+                            pk[e >> 1] = *reinterpret_cast<unsigned*>(&b);
+                        }
+                        *reinterpret_cast<uint4*>(dst + c0 + i) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (*abort_flag && tid == 0) {      // give copies in flight a bounded time to land
+        for (int s = 0; s < NS; ++s) {
+            for (unsigned i = 0; i < (1u << 16) && !mbar_try_wait(&full[s], 0) && !mbar_try_wait(&full[s], 1); ++i) {}
+        }
+    }
+    __syncthreads();
+    if (warp == 9) {
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512));
+    }
+}
+
+template <int HD>
+static int launch_prefill_tc_pair(const void* q, const void* k_pages, const void* v_pages, void* out, const int* units,
+                                  int n_units, const int* q_start, const int* q_len, const int* ctx_len,
+                                  const int* block_table, int bt_width, int num_pages, int P, int T, int H, int K,
+                                  float scale, unsigned* err, cudaStream_t stream) {
+    CUtensorMap mq, mk, mv;
+    int rc = tc_make_map_2d(&mq, q, (unsigned long long)T, (unsigned long long)H * HD, (unsigned long long)H * HD * 2, AT_M, 64);
+    if (rc) return rc;
+    const unsigned long long rows = (unsigned long long)num_pages * K * P;
+    rc = tc_make_map_rows8(&mk, k_pages, rows, HD / 64, P / 8);
+    if (rc) return rc;
+    rc = tc_make_map_rows8(&mv, v_pages, rows, HD / 64, P / 8);
+    if (rc) return rc;
+    cudaFuncSetAttribute(paged_prefill_tc_pair_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, At2Smem<HD>::bytes);
+    paged_prefill_tc_pair_kernel<HD><<<dim3(H, n_units), AT2_THREADS, At2Smem<HD>::bytes, stream>>>(
+        mq, mk, mv, (bf16*)out, units, n_units, q_start, q_len, ctx_len, block_table, bt_width, num_pages, P, H, K,
+        scale, err);
+    AIE_LAUNCH_CHECK();
+}
+
 template <int HD>
 static int launch_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out, const int* tiles,
                              int n_tiles, const int* q_start, const int* q_len, const int* ctx_len,
@@ -461,5 +869,22 @@ extern "C" int aie_paged_attention_prefill_tc(const void* q, const void* k_pages
 #define ARGS q, k_pages, v_pages, out, tiles, n_tiles, q_start, q_len, ctx_len, block_table, bt_width, num_pages, P, T, H, K, \
              scale, err, stream
     return d == 128 ? launch_prefill_tc<128>(ARGS) : launch_prefill_tc<64>(ARGS);
+#undef ARGS
+}
+
+// The same with two query tiles per CTA.  units: [n_units][2] = (request row, offset of the 256-token unit
+// within the request's tokens; a unit's last tile may be short or missing).  Same sizes as above.
+extern "C" int aie_paged_attention_prefill_tc_pair(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                                   const int* units, int n_units, const int* q_start,
+                                                   const int* q_len, const int* ctx_len, const int* block_table,
+                                                   int bt_width, int num_pages, int P, int T, int H, int K, int d,
+                                                   int window, float scale, unsigned* err, cudaStream_t stream) {
+    if (n_units <= 0) return 0;
+    if (K <= 0 || H % K) return AIE_BAD_ARG;
+    if ((d != 64 && d != 128) || P < 8 || P > 128 || 128 % P || n_units > 65535 || window > 0) return AIE_UNSUPPORTED;
+    if (((size_t)q & 15) || ((size_t)k_pages & 15) || ((size_t)v_pages & 15)) return AIE_UNSUPPORTED;
+#define ARGS q, k_pages, v_pages, out, units, n_units, q_start, q_len, ctx_len, block_table, bt_width, num_pages, P, T, H, K, \
+             scale, err, stream
+    return d == 128 ? launch_prefill_tc_pair<128>(ARGS) : launch_prefill_tc_pair<64>(ARGS);
 #undef ARGS
 }

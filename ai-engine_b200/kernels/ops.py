@@ -466,22 +466,22 @@ def paged_attention_prefill(q, k_pages, v_pages, tiles, q_start, q_len, ctx_len,
 
 
 def paged_attention_prefill_tc(q, k_pages, v_pages, tiles, q_start, q_len, ctx_len, block_table,
-                               scale: float, window: int, err, out, cost=(0.0, 0.0)) -> bool:
+                               scale: float, window: int, err, out, cost=(0.0, 0.0), pair: bool = False) -> bool:
     """The tcgen05 version of paged_attention_prefill (scores and outputs in tensor memory,
     operands by TMA).  Takes head sizes 64 and 128, pages of 8 .. 128 keys that divide 128, no window; returns
-    False when it does not take the sizes (nothing was launched)."""
+    False when it does not take the sizes (nothing was launched).  `pair`: the kernel whose CTAs take two tiles
+    each; `tiles` then lists units of 2 * PREFILL_TILE tokens (request row, offset of the unit)."""
     _dev(q, k_pages, v_pages, tiles, q_start, q_len, ctx_len, block_table, err, out)
     T, H, d = q.shape
     num_pages, K, P, _ = k_pages.shape
     if d not in (64, 128) or window > 0 or P < 8 or P > 128 or 128 % P:
         return False
     lib = library("attention_prefill_tc.cu")
+    fn = lib.aie_paged_attention_prefill_tc_pair if pair else lib.aie_paged_attention_prefill_tc
     with region("attention_prefill_tcgen05", *cost):
-        rc = lib.aie_paged_attention_prefill_tc(_p(q), _p(k_pages), _p(v_pages), _p(out), _p(tiles),
-                                                c_int(tiles.shape[0]), _p(q_start), _p(q_len), _p(ctx_len),
-                                                _p(block_table), c_int(block_table.shape[1]),
-                                                c_int(num_pages), c_int(P), c_int(T), c_int(H), c_int(K),
-                                                c_int(d), c_int(window), c_float(scale), _p(err), _stream())
+        rc = fn(_p(q), _p(k_pages), _p(v_pages), _p(out), _p(tiles), c_int(tiles.shape[0]), _p(q_start), _p(q_len),
+                _p(ctx_len), _p(block_table), c_int(block_table.shape[1]), c_int(num_pages), c_int(P), c_int(T),
+                c_int(H), c_int(K), c_int(d), c_int(window), c_float(scale), _p(err), _stream())
     if rc == -2:
         return False
     check(rc, "paged_attention_prefill_tc")

@@ -317,7 +317,10 @@ def time_attention(torch, tokens, context):
     err = torch.zeros(1, dtype=torch.int32, device=dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     outs, row = {}, {}
+    units = i32([[0, o] for o in range(0, tokens, 2 * ops.PREFILL_TILE)])
     impls = {"tcgen05": lambda o: ops.paged_attention_prefill_tc(q, kp, vp, tiles, qs, ql, cl, bt, d ** -0.5, 0, err, o),
+             "tcgen05_pair": lambda o: ops.paged_attention_prefill_tc(q, kp, vp, units, qs, ql, cl, bt, d ** -0.5, 0, err, o,
+                                                                      pair=True),
              "mma_sync": lambda o: ops.paged_attention_prefill(q, kp, vp, tiles, qs, ql, cl, bt, d ** -0.5, 0, err, o)}
     flops = 4.0 * d * H * (tokens * context + tokens * (tokens + 1) / 2)
     for name, fn in impls.items():
@@ -337,6 +340,7 @@ def time_attention(torch, tokens, context):
         row[name] = dict(us=round(us, 1), tflops=round(flops / us / 1e6, 1))
     assert int(err.item()) == 0
     row["max_difference"] = float((outs["tcgen05"].float() - outs["mma_sync"].float()).abs().max())
+    row["max_difference_pair"] = float((outs["tcgen05_pair"].float() - outs["mma_sync"].float()).abs().max())
     return {f"attention[{tokens} tokens after {context}]": row}
 
 

@@ -434,14 +434,21 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 //   warps 0-3   softmax of tile A, one thread per query row
 //   warps 4-7   softmax of tile B
 //   warp 8      loader (as above)
-//   warp 9      one lane issues tile A's products: per key tile j its P . V, then its scores for j + 1, which
-//               go over the tile's own P (the tensor pipe runs what one thread issues in order, so the
-//               P . V has read it)
-//   warp 10     the same for tile B: one issuing thread for both tiles was busy all the time (each mbarrier
-//               test costs it some hundred cycles while the pipe reads shared memory), and the tiles' chains
-//               softmax -> P . V -> scores -> softmax waited for it
-//   warp 11     nothing: it fills the third warpgroup, which hands most of its registers to the softmax
+//   warp 9      one lane issues the products of both tiles, tile A's then tile B's: per key tile j the tile's
+//               P . V, then its scores for j + 1, which go over the tile's own P (the tensor pipe runs what
+//               one thread issues in order, so the P . V has read it).  The serial issue is what staggers the
+//               tiles by half a period; with an issuing warp for each tile the two softmaxes ran in
+//               lockstep, fought for the exponential unit and left the pipe idle meanwhile (321 us against
+//               232 us for 2,048 tokens after 6,144).  The warp meets the softmax warps at named barriers:
+//               an mbarrier test cost the issuing thread some hundred cycles while the pipe reads shared
+//               memory, and one stood between every softmax and its products (257 us).
+//   warps 10-11 nothing: they fill the third warpgroup, which hands most of its registers to the softmax
 //               warpgroups (setmaxnreg), whose threads keep a row of 128 scores each
+// A tile's period is its chain softmax (about 2,000 cycles: 590 reading the row out of tensor memory, 1,400
+// exponentials) -> 16 products (1,400) -> softmax; the pipe is busy three quarters of the time.  Tried without
+// gain: exponentials taken against the old reference maximum while the row's chunks arrive (259 us), the
+// probabilities handed over in two halves (240 us), a warp that waits for the loads in the issuing warp's place
+// (233 us), the row read by one x128 load (233 us), a part of the exponentials as polynomials (slower).
 // Tile B sees 128 more keys than tile A: A takes part in key tiles 0 .. nA - 1, B in all of the unit's.
 #define AT2_THREADS 384
 #define AT2_BAR_P 1         // named barriers 1, 2: the probabilities of tile A / B are in tensor memory

@@ -4,6 +4,7 @@ stream.  Shapes and dtypes a kernel does not take are refused with an error.
 """
 from __future__ import annotations
 
+import math
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -488,6 +489,21 @@ def paged_attention_prefill_tc(q, k_pages, v_pages, tiles, q_start, q_len, ctx_l
     return True
 
 
+def prefill_takes_pairs(n_tiles: int, n_units: int, heads: int) -> bool:
+    """Whether the tcgen05 prompt kernel with two query tiles per CTA is the faster one for a step with `n_tiles`
+    tiles in `n_units` units of two.  Measured on heads of 128 and of 64: it takes 0.80-0.86 of the one-tile
+    kernel's time when nearly all units are whole and its CTAs (units x heads) fill the SMs in whole rounds about as
+    well as the one-tile kernel's; with a lone tile in a unit it runs at half speed, and with fewer CTAs than SMs
+    the longest CTA decides, which is twice as long."""
+    if n_units == 0 or n_tiles < 1.8 * n_units:
+        return False
+    sms = sm_count()
+    w1, w2 = n_tiles * heads / sms, n_units * heads / sms
+    if w2 <= 1.0:
+        return False
+    return 0.86 * math.ceil(w2) / w2 < math.ceil(w1) / w1
+
+
 def paged_attention(q, k_pages, v_pages, ctx, work, block_table, scale: float, window: int):
     """Attention of a step's query tokens over the cache.  `ctx` gives the step's generic arrays
     (positions, token_req, q_start, q_len, ctx_len, R), `work` the attention work lists derived from
@@ -523,8 +539,14 @@ def paged_attention(q, k_pages, v_pages, ctx, work, block_table, scale: float, w
                                decode_splits(work.n_decode, K, H // K, keys, block_table.shape[1]),
                                ctx.err, out, cost=dec_cost)
     if work.n_decode < ctx.R:
-        if not paged_attention_prefill_tc(q, k_pages, v_pages, work.prefill_tiles, ctx.q_start, ctx.q_len,
-                                          ctx.ctx_len, block_table, scale, window, ctx.err, out, cost=pre_cost):
+        pairs = getattr(work, "prefill_pairs", None)
+        if pairs is not None and prefill_takes_pairs(work.prefill_tiles.shape[0], pairs.shape[0], H):
+            took = paged_attention_prefill_tc(q, k_pages, v_pages, pairs, ctx.q_start, ctx.q_len, ctx.ctx_len,
+                                              block_table, scale, window, ctx.err, out, cost=pre_cost, pair=True)
+        else:
+            took = paged_attention_prefill_tc(q, k_pages, v_pages, work.prefill_tiles, ctx.q_start, ctx.q_len,
+                                              ctx.ctx_len, block_table, scale, window, ctx.err, out, cost=pre_cost)
+        if not took:
             paged_attention_prefill(q, k_pages, v_pages, work.prefill_tiles, ctx.q_start, ctx.q_len,
                                     ctx.ctx_len, block_table, scale, window, ctx.err, out, cost=pre_cost)
     return out

@@ -24,7 +24,8 @@ class AttentionWork(StepPlanner):
     """The work lists of the attention kernels, derived from a step's generic arrays: `decode_tokens`
     (rows of requests that bring one token, for the split-KV kernel), `other_tokens` (rows of all others),
     `prefill_tiles` [n, 2] = (request row, offset of a tile of `ops.PREFILL_TILE` tokens among the tokens it
-    brings), `n_decode`, and `max_decode_len`.  The lone-token rows are listed longest context first: the
+    brings), `prefill_pairs` [m, 2] = the same in units of two tiles (for the kernel whose CTAs take two),
+    `n_decode`, and `max_decode_len`.  The lone-token rows are listed longest context first: the
     decode kernel's CTAs start in that order, so when there are more of them than fit the machine at once the
     long requests do not start last (the most keys a lone token reads: of the layout's widest
     possible request when the step may be replayed from a graph)."""
@@ -36,7 +37,7 @@ class AttentionWork(StepPlanner):
         if T == R:        # every request brings one token
             dec, other = q_start[np.argsort(-ctx.h_ctx_len, kind="stable")], np.empty(0, dtype=np.int32)
             n_decode, max_decode_len = R, ctx.max_total_len
-            tiles = np.empty((0, 2), dtype=np.int32)
+            tiles = pairs = np.empty((0, 2), dtype=np.int32)
         else:
             is_dec = q_len == 1
             dec = q_start[is_dec][np.argsort(-ctx.h_ctx_len[is_dec], kind="stable")]
@@ -46,10 +47,11 @@ class AttentionWork(StepPlanner):
             # tiles by the keys they read, fewest first: the prompt kernels start their CTAs from the end of the list
             tiles = sorted(((int(ctx.h_ctx_len[r]) + o, r, o) for r in range(R) if q_len[r] != 1
                             for o in range(0, int(q_len[r]), ops.PREFILL_TILE)))
+            pairs = np.asarray([(r, o) for _, r, o in tiles if o % (2 * ops.PREFILL_TILE) == 0], dtype=np.int32).reshape(-1, 2)
             tiles = np.asarray([(r, o) for _, r, o in tiles], dtype=np.int32).reshape(-1, 2)
         if ctx.bucketed and n_decode:
             max_decode_len = ctx.bt_width * ctx.page_size      # a property of the layout, not of the step
-        return (dict(decode_tokens=dec.astype(np.int32), other_tokens=other, prefill_tiles=tiles),
+        return (dict(decode_tokens=dec.astype(np.int32), other_tokens=other, prefill_tiles=tiles, prefill_pairs=pairs),
                 dict(n_decode=n_decode, max_decode_len=max_decode_len))
 
 

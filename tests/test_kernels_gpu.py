@@ -340,12 +340,22 @@ PREFILL_TC_SHAPES = [  # H, K, P, lens, q_lens  (head sizes 64 and 128, no windo
     (3, 3, 16, [200], [2]),
     (4, 1, 64, [191, 192, 193], [191, 128, 2]),
     (8, 2, 128, [128, 129, 384], [128, 129, 128]),
+    (3, 1, 16, [256, 257, 255, 640], [256, 257, 255, 513]),      # units of two tiles: whole, one row over, one short
+    (2, 1, 16, [1000, 1500], [300, 900]),                        # portions that start off a tile's edge, many key tiles
+    (4, 4, 8, [77 + 384, 128 + 130], [384, 130]),
 ]
 
 
+def prefill_work(q_lens, pair):
+    """(request row, offset) of every tile of 128 tokens, or of every unit of two tiles."""
+    step = 256 if pair else 128
+    return [(r, o) for r, n in enumerate(q_lens) for o in range(0, n, step)]
+
+
+@pytest.mark.parametrize("pair", [False, True], ids=["one_tile", "two_tiles"])
 @pytest.mark.parametrize("d", [128, 64])
 @pytest.mark.parametrize("shape", PREFILL_TC_SHAPES)
-def test_paged_attention_prefill_tcgen05(shape, d):
+def test_paged_attention_prefill_tcgen05(shape, d, pair):
     H, K, P, lens, q_lens = shape
     s = paged_setup(torch.bfloat16, H, K, d, P, lens, q_lens, seed=H + P + len(lens))
     scale = 1.0 / math.sqrt(d)
@@ -353,9 +363,9 @@ def test_paged_attention_prefill_tcgen05(shape, d):
     out = torch.full_like(s["q"], float("nan"))
     i32 = lambda a: torch.tensor(a, device=DEV, dtype=torch.int32)
     q_start = np.concatenate([[0], np.cumsum(q_lens)[:-1]])
-    tiles = [(r, o) for r, n in enumerate(q_lens) for o in range(0, n, 128)]
-    took = ops().paged_attention_prefill_tc(s["q"], s["k_pages"], s["v_pages"], i32(tiles), i32(q_start), i32(q_lens),
-                                            i32([n - ql for n, ql in zip(lens, q_lens)]), s["bt"], scale, 0, e, out)
+    took = ops().paged_attention_prefill_tc(s["q"], s["k_pages"], s["v_pages"], i32(prefill_work(q_lens, pair)),
+                                            i32(q_start), i32(q_lens), i32([n - ql for n, ql in zip(lens, q_lens)]),
+                                            s["bt"], scale, 0, e, out, pair=pair)
     assert took
     torch.cuda.synchronize()
     assert int(e.item()) == 0, "a bounded wait ran out or a page was missing"
@@ -365,7 +375,8 @@ def test_paged_attention_prefill_tcgen05(shape, d):
     assert err.max() <= 2e-2, f"first wrong token {int((err > 2e-2).nonzero()[0])} of {sum(q_lens)}: {float(err.max())}"
 
 
-def test_prefill_tcgen05_scores_that_grow_along_the_sequence():
+@pytest.mark.parametrize("pair", [False, True], ids=["one_tile", "two_tiles"])
+def test_prefill_tcgen05_scores_that_grow_along_the_sequence(pair):
     """Keys whose size grows from tile to tile (scores up to tens of units above everything before) and
     then falls again: rows whose reference maximum has to move, and rows where it may stay."""
     H, K, d, P = 6, 2, 128, 16
@@ -381,9 +392,8 @@ def test_prefill_tcgen05_scores_that_grow_along_the_sequence():
     e = err_word()
     out = torch.full_like(s["q"], float("nan"))
     i32 = lambda a: torch.tensor(a, device=DEV, dtype=torch.int32)
-    tiles = [(0, o) for o in range(0, n, 128)]
-    assert ops().paged_attention_prefill_tc(s["q"], s["k_pages"], s["v_pages"], i32(tiles), i32([0]), i32([n]),
-                                            i32([0]), s["bt"], scale, 0, e, out)
+    assert ops().paged_attention_prefill_tc(s["q"], s["k_pages"], s["v_pages"], i32(prefill_work([n], pair)), i32([0]),
+                                            i32([n]), i32([0]), s["bt"], scale, 0, e, out, pair=pair)
     torch.cuda.synchronize()
     assert int(e.item()) == 0
     want = attention_reference(s, H, K, d, scale, 0)
@@ -425,6 +435,48 @@ def test_mixed_step_decode_and_prefill_kernels_side_by_side():
     out = ops().paged_attention(s["q"], s["k_pages"], s["v_pages"], ctx, ctx, s["bt"], scale, 0)
     want = attention_reference(s, H, K, d, scale, 0)
     assert (out.double() - want).abs().max() <= 2e-2
+
+
+def test_step_attention_with_the_two_tile_kernel(monkeypatch):
+    """`paged_attention` with the rule that picks the prompt kernel turned to "two tiles": portions of three requests
+    (one of them with a lone last tile, one shorter than a tile) beside a lone decoded token, work lists as the
+    planner makes them."""
+    H, K, d, P = 8, 2, 128, 16
+    lens, q_lens = [700, 90, 300, 411], [520, 40, 1, 256]
+    s = paged_setup(torch.bfloat16, H, K, d, P, lens, q_lens, seed=5)
+    scale = 1.0 / math.sqrt(d)
+    i32 = lambda a: torch.tensor(a, device=DEV, dtype=torch.int32)
+    q_start = np.concatenate([[0], np.cumsum(q_lens)[:-1]])
+
+    class Ctx:
+        pass
+
+    ctx = Ctx()
+    ctx.positions, ctx.token_req, ctx.err = s["positions"], s["token_req"], err_word()
+    ctx.R, ctx.n_decode, ctx.max_decode_len = 4, 1, 300
+    ctx.decode_tokens = i32([int(q_start[2])])
+    ctx.prefill_tiles = i32([(r, o) for r in (0, 1, 3) for o in range(0, q_lens[r], 128)])
+    ctx.prefill_pairs = i32([(r, o) for r in (0, 1, 3) for o in range(0, q_lens[r], 256)])
+    ctx.q_start, ctx.q_len, ctx.ctx_len = i32(q_start), i32(q_lens), i32([n - q for n, q in zip(lens, q_lens)])
+    want = attention_reference(s, H, K, d, scale, 0)
+    asked = []
+    monkeypatch.setattr(ops(), "prefill_takes_pairs", lambda *a: asked.append(a) or True)
+    out = ops().paged_attention(s["q"], s["k_pages"], s["v_pages"], ctx, ctx, s["bt"], scale, 0)
+    torch.cuda.synchronize()
+    assert asked == [(8, 5, H)] and int(ctx.err.item()) == 0
+    err = (out.double() - want).abs().amax(dim=(1, 2))
+    assert err.max() <= 2e-2, f"first wrong token {int((err > 2e-2).nonzero()[0])}: {float(err.max())}"
+
+
+def test_the_rule_that_picks_the_prompt_kernel(monkeypatch):
+    monkeypatch.setattr(ops(), "sm_count", lambda: 148)
+    takes = ops().prefill_takes_pairs
+    assert takes(16, 8, 32)            # 2,048 tokens of one request, 32 heads: 256 CTAs against 512
+    assert takes(64, 32, 8)
+    assert not takes(16, 8, 24)        # 192 CTAs would run in two uneven rounds
+    assert not takes(8, 4, 32)         # fewer CTAs than SMs: the longest decides
+    assert not takes(16, 16, 32)       # every unit holds one tile only
+    assert not takes(0, 0, 32)
 
 
 def test_far_key_among_hundreds_is_found():

@@ -191,11 +191,14 @@ def test_prompt_attention_2048_tokens_after_30720(d, P):
     e = torch.zeros(1, dtype=torch.int32, device=DEV)
     want = long_reference(s, H, K, scale)
     outs = {}
-    for name in ("tcgen05", "mma_sync"):
+    units = i32([[0, o] for o in range(0, n_q, 2 * ops().PREFILL_TILE)])
+    for name in ("tcgen05", "tcgen05_two_tiles", "mma_sync"):
         out = torch.full_like(s["q"], float("nan"))
         args = (s["q"], s["k_pages"], s["v_pages"], tiles, i32([0]), i32([n_q]), i32([n - n_q]), s["bt"], scale, 0, e, out)
         if name == "tcgen05":
             assert ops().paged_attention_prefill_tc(*args)
+        elif name == "tcgen05_two_tiles":
+            assert ops().paged_attention_prefill_tc(*args[:3], units, *args[4:], pair=True)
         else:
             ops().paged_attention_prefill(*args)
         torch.cuda.synchronize()
@@ -204,4 +207,5 @@ def test_prompt_attention_2048_tokens_after_30720(d, P):
         assert err.max() <= 2e-2, f"{name}: first wrong row {int((err > 2e-2).nonzero()[0])} of {n_q}: {float(err.max())}"
         outs[name] = out
     for row, far in planted:
-        assert (outs["tcgen05"][row, 0].float() - s["vs"][far, 0].float()).abs().max() < 0.25, (row, far)
+        for name in ("tcgen05", "tcgen05_two_tiles"):
+            assert (outs[name][row, 0].float() - s["vs"][far, 0].float()).abs().max() < 0.25, (name, row, far)

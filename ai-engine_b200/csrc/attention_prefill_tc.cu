@@ -29,7 +29,10 @@
 //                      result the same softmax.
 // The value rows of keys past the sequence's last token are zeroed in shared memory before the
 // last tile's P . V, so a probability of 0 never meets what an unwritten cache slot holds.
-// Every wait is bounded (see tc_common.cuh); a wait that runs out raises the device error word.
+// The softmax warps hand a tile's probabilities to the issuing warp at a named hardware barrier (bar.arrive /
+// bar.sync); every mbarrier wait is bounded (see tc_common.cuh) and a wait that runs out raises the device error
+// word; a softmax warp whose wait ran out still arrives at the named barrier for every tile, so the issuing warp's
+// bar.sync always returns.
 // Formula: crates/ai-engine-runtime/src/arch/attention.rs:148-157,177-196,203-224.
 #include "tc_common.cuh"
 
@@ -38,6 +41,9 @@
 #define AT_THREADS 192      // loader warp, MMA warp, 4 softmax warps
 #define AT_HALF_BYTES (128 * 64 * 2)      // one [128 x 64] bf16 swizzle atom column: 16 KB
 
+#define AT_BAR_P 1            // named barriers 1, 2: the probabilities of an even / odd key tile are in tensor memory
+                              // (two, because a softmax warp may be a tile ahead of another: its arrival for
+                              // tile j + 1 must not count for tile j)
 #define AT_RESCALE_STEP 8.0f     // a row's reference maximum moves in steps of more than this (log2 units)
 
 // HD: head size, HD / 64 halves of 64 columns.  A tile of 128 keys (or queries) holds 16 KB per half.
@@ -157,7 +163,6 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         mbar_init(&s_full[0], 1);
         mbar_init(&s_full[1], 1);
-        mbar_init(p_ready, 4);      // one arrival per softmax warp
         mbar_init(o_done, 1);
         mbar_init(v_fixed, 1);
         *abort_flag = 0;
@@ -238,7 +243,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             if (lane == 0) mbar_arrive_plain(v_fixed);
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        // the whole warp walks the tiles (it meets the softmax warps at a named barrier); lane 0 issues
+        {
             const unsigned idesc_s = umma_idesc(AT_N), idesc_o = umma_idesc(HD, true);
             // descriptors of the first step of each operand, built once; a step or a stage further along is an
             // addition to the descriptor's address field (bytes / 16)
@@ -254,40 +260,49 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 umma_commit(&k_empty[st]);
                 umma_commit(&s_full[j & 1]);
             };
-            bool ok = mbar_wait(q_full, 0, abort_flag, err);
-            if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag, err);
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                issue_scores(0, 0);
+            bool ok = true;                 // lane 0's; once false, the warp only keeps its appointments at the barrier
+            if (lane == 0) {
+                ok = mbar_wait(q_full, 0, abort_flag, err);
+                if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag, err);
+                if (ok) {
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    issue_scores(0, 0);
+                }
             }
             int st = 0, ph = 0;             // stage and phase of tile j in the rings
-            for (int j = 0; j < n_kt && ok; ++j) {
+            for (int j = 0; j < n_kt; ++j) {
                 const int st1 = st + 1 == NST ? 0 : st + 1, ph1 = st + 1 == NST ? ph ^ 1 : ph;      // of tile j + 1
-                if (j + 1 < n_kt) {
+                if (lane == 0 && ok && j + 1 < n_kt) {
                     // the next tile's scores, while this tile's softmax runs.  They go over the P of tile
                     // j - 1, which the P . V issued before them has read: the tensor pipe runs what one thread
                     // issues in order.
                     ok = mbar_wait(&kv_full[st1], ph1, abort_flag, err);
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    issue_scores(j + 1, st1);
+                    if (ok) {
+                        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                        issue_scores(j + 1, st1);
+                    }
                 }
-                ok = mbar_wait(p_ready, j & 1, abort_flag, err);      // (the tile's values landed with its keys)
-                if (ok && j == n_kt - 1) ok = mbar_wait(v_fixed, 0, abort_flag, err);
-                if (!ok) break;
+                if (lane == 0 && ok && j == n_kt - 1) ok = mbar_wait(v_fixed, 0, abort_flag, err);
+                // the tile's probabilities are written: the 128 softmax threads arrive, this warp waits.  A hardware
+                // barrier: an mbarrier test costs the issuing thread some hundred cycles while the tensor pipe reads
+                // shared memory, and this hand-over is on the tile's critical path (P . V, then the scores of the tile
+                // after the next, which the softmax warps wait for).  (The tile's values landed with its keys.)
+                asm volatile("bar.sync %0, %1;\n" ::"r"(AT_BAR_P + (j & 1)), "r"(AT_M + 32) : "memory");
+                st = st1;
+                ph = ph1;
+                if (lane != 0 || !ok) continue;
+                const int st0 = st == 0 ? NST - 1 : st - 1;      // the stage of tile j again
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 // O += P . V over 128 keys: 8 steps of 16 keys; P is in tensor memory (two keys to a column),
                 // V is MN-major: 16 keys = two groups of 8 rows, the halves of the head 1 KB apart
-                const unsigned long long dv = dv0 + (unsigned long long)((st * TILE) >> 4);
+                const unsigned long long dv = dv0 + (unsigned long long)((st0 * TILE) >> 4);
                 const unsigned tp = tmem_base + (unsigned)((j & 1) * AT_N);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
                     umma_a_tmem(tmem_base + 256u, tp + (unsigned)(ks * 8), dv + (unsigned long long)((ks * 2 * GROUP) >> 4),
                                 idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-                umma_commit(&v_empty[st]);
+                umma_commit(&v_empty[st0]);
                 umma_commit(o_done);
-                st = st1;
-                ph = ph1;
             }
         }
     } else {
@@ -300,11 +315,18 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const float sl2 = scale * 1.4426950408889634f;      // scores in units of log2(e): exp2 below
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
-        for (int j = 0; j < n_kt && ok; ++j) {
+        for (int j = 0; j < n_kt; ++j) {
+            // (a warp that gave up still arrives at the barrier for every tile: the issuing warp waits there
+            // without a limit)
             const unsigned tmem_s = tmem_base + (unsigned)((j & 1) * AT_N);
-            if (lane == 0) ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, err);
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-            if (!ok) break;
+            if (ok) {
+                if (lane == 0) ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, err);
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            }
+            if (!ok) {
+                asm volatile("bar.arrive %0, %1;\n" ::"r"(AT_BAR_P + (j & 1)), "r"(AT_M + 32) : "memory");
+                continue;
+            }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int kbase = j * AT_N;
             const bool edge = kbase + AT_N - 1 > p0;     // the tile touches the diagonal or the sequence's end
@@ -339,7 +361,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
                 if (lane == 0) ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, err);
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (!ok) break;
+                if (!ok) {
+                    asm volatile("bar.arrive %0, %1;\n" ::"r"(AT_BAR_P + (j & 1)), "r"(AT_M + 32) : "memory");
+                    continue;
+                }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
                 for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -376,8 +401,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             l_run = l_run * corr + (at_lo(psum2) + at_hi(psum2));
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive_plain(p_ready);
+            asm volatile("bar.arrive %0, %1;\n" ::"r"(AT_BAR_P + (j & 1)), "r"(AT_M + 32) : "memory");
         }
         // the last P . V, then this row of O divided by the row's sum
         if (ok) {

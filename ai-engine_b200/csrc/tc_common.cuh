@@ -43,19 +43,6 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
     return false;
 }
 
-// The same, polling without suspending: for a lone thread whose wait is on the kernel's critical path
-// (a suspended try_wait was seen to answer some hundred cycles after the phase had completed).
-__device__ __forceinline__ bool mbar_wait_spin(unsigned long long* bar, unsigned parity, volatile int* abort_flag,
-                                               unsigned* err) {
-    for (unsigned i = 0; i < (TC_WAIT_LIMIT << 2); ++i) {
-        if (mbar_test_wait(bar, parity)) return true;
-        if ((i & 4095u) == 4095u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    atomicOr(err, AIE_DEV_WAIT_TIMEOUT);
-    return false;
-}
-
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, unsigned long long* bar, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
                  ::"r"(tc_smem(dst)), "l"(map), "r"(tc_smem(bar)), "r"(x), "r"(y) : "memory");

@@ -4,6 +4,7 @@
 #include <pybind11/stl.h>
 
 #include "runtime.hpp"
+#include "step_pack.hpp"
 
 namespace py = pybind11;
 using namespace aie;
@@ -62,6 +63,39 @@ PYBIND11_MODULE(_aie_host, m) {
                 throw std::invalid_argument("fill_block_table: out must be [>= len(slots), width]");
             c.fill_block_table(g, slots.data(), (int)slots.size(), width, out.mutable_data());
         });
+
+    // The step function's packing: (packed int32 array, segment lengths, T, R, N, max_q_len, max_total_len, width,
+    // has_src).  A fault in the entries raises ValueError with the message the step function reports.
+    m.def("pack_step", [](const CacheManager& cache, const std::vector<int>& slots, const std::vector<int>& starts,
+                          const std::vector<std::vector<long long>>& tokens, const std::vector<std::vector<int>>& wants,
+                          const std::vector<int>& srcs, int n_live, int page_size, bool bucket_width) {
+        if (slots.size() != tokens.size()) throw std::invalid_argument("pack_step: the entries' fields differ in number");
+        const StepShape s = step_shape(cache, starts, tokens, wants, srcs, page_size, bucket_width);
+        py::array_t<int32_t> out(s.total);
+        pack_step(cache, s, slots, starts, tokens, wants, srcs, n_live, out.mutable_data());
+        return py::make_tuple(out, s.lengths, s.T, s.R, s.N, s.max_q_len, s.max_total_len, s.width, s.has_src);
+    }, py::arg("cache"), py::arg("slots"), py::arg("starts"), py::arg("tokens"), py::arg("wants"), py::arg("srcs"),
+       py::arg("n_live"), py::arg("page_size"), py::arg("bucket_width"));
+
+    // The attention kernels' work lists of a step: (decode_tokens, other_tokens, tiles [n, 2], pairs [m, 2],
+    // n_decode, max_decode_len).
+    m.def("attention_lists", [](py::array_t<int32_t, py::array::c_style | py::array::forcecast> q_start,
+                                py::array_t<int32_t, py::array::c_style | py::array::forcecast> q_len,
+                                py::array_t<int32_t, py::array::c_style | py::array::forcecast> ctx_len, int tile) {
+        const int R = (int)q_len.size();
+        if ((int)q_start.size() != R || (int)ctx_len.size() != R || tile < 1)
+            throw std::invalid_argument("attention_lists: arrays differ in length");
+        const AttentionLists a = attention_lists(q_start.data(), q_len.data(), ctx_len.data(), R, tile);
+        auto arr = [](const std::vector<int32_t>& v) {
+            py::array_t<int32_t> o((py::ssize_t)v.size());
+            std::copy(v.begin(), v.end(), o.mutable_data());
+            return o;
+        };
+        py::array_t<int32_t> tiles = arr(a.tiles), pairs = arr(a.pairs);
+        tiles.resize({(py::ssize_t)a.tiles.size() / 2, (py::ssize_t)2});
+        pairs.resize({(py::ssize_t)a.pairs.size() / 2, (py::ssize_t)2});
+        return py::make_tuple(arr(a.decode_tokens), arr(a.other_tokens), tiles, pairs, a.n_decode, a.max_decode_len);
+    });
 
     py::class_<StepEntry>(m, "StepEntry")
         .def_readonly("id", &StepEntry::id)

@@ -85,6 +85,7 @@ class _Buffers:
         self.graph_logits = None
         self.graph_kernels = 0
         self.uses = 0
+        self.views = None          # device views of the segments, made at the layout's first step
 
     def upload(self, arrays) -> None:
         i, host = self.staging.take(self.total)
@@ -112,69 +113,38 @@ class StepContext:
     def __init__(self, entries: Sequence[StepEntry], cache, device, err: torch.Tensor,
                  buffers: Optional[dict] = None, bucket_width: bool = False, planners=(),
                  n_live: Optional[int] = None):
-        R = len(entries)
-        q_len = np.array([len(e.tokens) for e in entries], dtype=np.int32)
-        if R == 0 or int(q_len.min()) < 1:
-            raise StepError("a step needs at least one entry and every entry at least one token")
-        T = int(q_len.sum())
-        ctx_len = np.array([e.start for e in entries], dtype=np.int32)
-        slots = np.array([e.slot for e in entries], dtype=np.int32)
-        q_start = np.zeros(R, dtype=np.int32)
-        np.cumsum(q_len[:-1], out=q_start[1:])
-        if T == R:        # every request brings one token: no ragged arithmetic needed
-            token_ids = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=R)
-            token_req = np.arange(R, dtype=np.int32)
-            positions = ctx_len
-        else:
-            token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
-            token_req = np.repeat(np.arange(R, dtype=np.int32), q_len)
-            positions = (np.arange(T, dtype=np.int32) - np.repeat(q_start, q_len)
-                         + np.repeat(ctx_len, q_len)).astype(np.int32)
-        if token_ids.min() < 0 or token_ids.max() > 2**31 - 1:
-            raise StepError("token ids must be non-negative 32-bit integers")
-        token_src = np.full(T, -1, dtype=np.int32)
-        self.has_src = False
-        for r, e in enumerate(entries):
-            if e.src is not None:
-                if len(e.tokens) != 1:
-                    raise StepError("only an entry of one token can take it from the device")
-                token_src[q_start[r]] = e.src
-                self.has_src = True
-        rows: List[int] = []
-        for r, e in enumerate(entries):
-            for w in e.want:
-                if not 0 <= w < len(e.tokens):
-                    raise StepError(f"wanted place {w} is outside the entry's {len(e.tokens)} tokens")
-                rows.append(int(q_start[r]) + int(w))
-        N = len(rows)
-        live = np.ones(R, dtype=np.int32)
-        if n_live is not None:
-            live[n_live:] = 0
-        self.T, self.R, self.num_logit_rows = T, R, N
-        self.h_q_len, self.h_ctx_len, self.h_slots, self.h_q_start = q_len, ctx_len, slots, q_start
-        self.max_q_len = int(q_len.max())
-        self.max_total_len = int((ctx_len + q_len).max())
-        width = cache.block_table_width(self.max_total_len)
-        if bucket_width:            # few distinct widths, so layouts (and graphs) are reused
-            width = max(64, 1 << (width - 1).bit_length())
-        self.bt_width, self.page_size, self.bucketed = width, cache.page_size, bool(bucket_width)
-        tables = cache.fill_block_tables(slots.tolist(), width)
+        # The generic arrays and the block tables are packed by the host runtime (csrc/host/step_pack.hpp) into one
+        # int32 array; what the planners add goes behind it.
+        from ..cache.manager import host as host_runtime
 
-        arrays = [token_ids.astype(np.int32), positions, token_req, q_start, q_len, ctx_len, slots, live,
-                  np.asarray(rows, dtype=np.int32), token_src]
-        n_generic = len(arrays)
+        try:
+            packed, lengths, T, R, N, max_q, max_total, width, has_src = host_runtime().pack_step(
+                cache.book, [e.slot for e in entries], [e.start for e in entries], [e.tokens for e in entries],
+                [e.want for e in entries], [-1 if e.src is None else e.src for e in entries],
+                -1 if n_live is None else int(n_live), cache.page_size, bool(bucket_width))
+        except ValueError as e:
+            raise StepError(str(e)) from None
+        self.T, self.R, self.num_logit_rows, self.has_src = T, R, N, has_src
+        self.max_q_len, self.max_total_len = max_q, max_total
+        self.bt_width, self.page_size, self.bucketed = width, cache.page_size, bool(bucket_width)
+        offs, o = [], 0
+        for n in lengths:
+            offs.append((o, n))
+            o += (n + 3) // 4 * 4
+        host = [packed[o:o + n] for o, n in offs]
+        self.h_q_start, self.h_q_len, self.h_ctx_len, self.h_slots = host[3], host[4], host[5], host[6]
+
+        arrays = [packed]
         planned = []                # (planner, [(name, shape)], scalars)
         for pl in planners:
             arrs, scalars = pl.plan(self)
             planned.append((pl, [(name, a.shape) for name, a in arrs.items()], scalars))
             arrays += [np.ascontiguousarray(a, dtype=np.int32).reshape(-1) for a in arrs.values()]
-        n_planned = len(arrays)
-        arrays += [tb.reshape(-1) for tb in tables]
-        key = tuple(len(a) for a in arrays) + (width,) + tuple(pl.key for pl in planners)
+        key = tuple(lengths) + tuple(len(a) for a in arrays[1:]) + (width,) + tuple(pl.key for pl in planners)
         self.layout_key = key
         buf = buffers.get(key) if buffers is not None else None
         if buf is None:
-            buf = _Buffers(key[:len(arrays)], device, buffers.get("staging") if buffers is not None else None)
+            buf = _Buffers([len(a) for a in arrays], device, buffers.get("staging") if buffers is not None else None)
             if buffers is not None:
                 if len(buffers) >= 128:
                     buffers.pop(next(k for k in buffers if k != "staging"))
@@ -183,19 +153,22 @@ class StepContext:
         self.buffers = buf
         buf.upload(arrays)
         self.h2d_bytes = buf.total * 4
-        dev = buf.dev
-        views = [dev[o:o + n] for o, n in buf.offsets]
+        if buf.views is None:       # the device views of a layout are made once: its offsets never change
+            dev = buf.dev
+            generic = [dev[o:o + n] for o, n in offs]
+            buf.views = (generic[:10], [v.view(R, width) for v in generic[10:]],
+                         [dev[o:o + n] for o, n in buf.offsets[1:]])
+        generic, self.block_tables, views = buf.views
         (self.token_ids, self.positions, self.token_req, self.q_start, self.q_len, self.ctx_len, self.slots,
-         self.live, self.logit_rows, self.token_src) = views[:n_generic]
+         self.live, self.logit_rows, self.token_src) = generic
         self._plans = {}
-        at = n_generic
+        at = 0
         for pl, shapes, scalars in planned:
             ns = SimpleNamespace(**scalars)
             for name, shape in shapes:
-                setattr(ns, name, views[at].view(shape))
+                setattr(ns, name, views[at] if len(shape) == 1 else views[at].view(shape))
                 at += 1
             self._plans[id(pl)] = ns
-        self.block_tables = [v.view(R, width) for v in views[n_planned:]]
         self.err = err
         self.device = device
 

@@ -33,25 +33,14 @@ class AttentionWork(StepPlanner):
     key = "attention"
 
     def plan(self, ctx):
-        q_len, q_start, R, T = ctx.h_q_len, ctx.h_q_start, ctx.R, ctx.T
-        if T == R:        # every request brings one token
-            dec, other = q_start[np.argsort(-ctx.h_ctx_len, kind="stable")], np.empty(0, dtype=np.int32)
-            n_decode, max_decode_len = R, ctx.max_total_len
-            tiles = pairs = np.empty((0, 2), dtype=np.int32)
-        else:
-            is_dec = q_len == 1
-            dec = q_start[is_dec][np.argsort(-ctx.h_ctx_len[is_dec], kind="stable")]
-            other = np.nonzero(np.repeat(~is_dec, q_len))[0].astype(np.int32)
-            n_decode = int(dec.shape[0])
-            max_decode_len = int((ctx.h_ctx_len[is_dec] + 1).max()) if n_decode else 0
-            # tiles by the keys they read, fewest first: the prompt kernels start their CTAs from the end of the list
-            tiles = sorted(((int(ctx.h_ctx_len[r]) + o, r, o) for r in range(R) if q_len[r] != 1
-                            for o in range(0, int(q_len[r]), ops.PREFILL_TILE)))
-            pairs = np.asarray([(r, o) for _, r, o in tiles if o % (2 * ops.PREFILL_TILE) == 0], dtype=np.int32).reshape(-1, 2)
-            tiles = np.asarray([(r, o) for _, r, o in tiles], dtype=np.int32).reshape(-1, 2)
+        # the lists are made by the host runtime (csrc/host/step_pack.hpp:attention_lists)
+        from ..cache.manager import host as host_runtime
+
+        dec, other, tiles, pairs, n_decode, max_decode_len = host_runtime().attention_lists(
+            ctx.h_q_start, ctx.h_q_len, ctx.h_ctx_len, ops.PREFILL_TILE)
         if ctx.bucketed and n_decode:
             max_decode_len = ctx.bt_width * ctx.page_size      # a property of the layout, not of the step
-        return (dict(decode_tokens=dec.astype(np.int32), other_tokens=other, prefill_tiles=tiles, prefill_pairs=pairs),
+        return (dict(decode_tokens=dec, other_tokens=other, prefill_tiles=tiles, prefill_pairs=pairs),
                 dict(n_decode=n_decode, max_decode_len=max_decode_len))
 
 

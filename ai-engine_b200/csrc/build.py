@@ -141,7 +141,7 @@ def host_module_path() -> str:
     deps = srcs + _headers(folder)
     flags = CXX_FLAGS + ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
                          "-I", folder]
-    key = _hash(deps, flags + [sys.version])
+    key = _hash(deps, [f for f in flags if not f.startswith('/')] + [sysconfig.get_config_var('SOABI') or sys.version])
     target = os.path.join(build_dir(), f"_aie_host-{key}.so")
     if os.path.exists(target):
         return target

@@ -129,14 +129,6 @@ class PagedCache:
     def block_table_width(self, max_tokens: int) -> int:
         return max(1, (max_tokens + self.page_size - 1) // self.page_size)
 
-    def fill_block_tables(self, slots: Sequence[int], width: int) -> List[np.ndarray]:
-        out = []
-        for g in range(len(self.groups)):
-            a = np.empty((len(slots), width), dtype=np.int32)
-            self.book.fill_block_table(g, list(slots), width, a)
-            out.append(a)
-        return out
-
     def part_cache(self, run_index: int, role: str, ctx) -> LayerCache:
         """What the part in `role` of run-order entry `run_index` gets of the cache in this step."""
         lc = LayerCache(state=self.state.get((run_index, role)))

@@ -68,7 +68,6 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     constexpr int STILE = SUB * DEC_TILE;          // keys per stage
     static_assert(D % 64 == 0, "head size of the fast path");
     extern __shared__ __align__(128) unsigned char dec_smem[];
-    __shared__ int ok_s[DEC_WARPS][NST][STILE];
     __shared__ float mrg_m[DEC_WARPS][DEC_HEADS], mrg_l[DEC_WARPS][DEC_HEADS];
 
     // Everything up to the first use of q reads only what earlier steps left (the step's index
@@ -133,7 +132,6 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
                         if (page >= 0 && page < num_pages) prow = (page * K + kvh) * P + (key - pidx * P);
                         else atomicOr(err, AIE_DEV_PAGE_OOB);
                     }
-                    ok_s[warp][st][sub * DEC_TILE + lane] = prow >= 0;
                 }
                 const int cc = lane % CH, kq = lane / CH;
 #pragma unroll
@@ -182,6 +180,7 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         const int st = i % NST;
 #pragma unroll
         for (int sub = 0; sub < SUB; ++sub) {
+        const int kb_tile = lo + (first + i * DEC_WARPS) * STILE + sub * DEC_TILE;      // first key of this 16-key tile
         bf16* ks_t = stage0 + (size_t)st * 2 * STILE * D + sub * DEC_TILE * D;
         bf16* vs_t = stage0 + (size_t)st * 2 * STILE * D + STILE * D + sub * DEC_TILE * D;
 
@@ -204,7 +203,9 @@ paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         for (int j = 0; j < 2; ++j)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const bool valid = ok_s[warp][st][sub * DEC_TILE + j * 8 + qcol + e] != 0;
+                // a key is there when it lies before the end of the sequence (a page that is missing was flagged
+                // when its copy was left out; its keys read as zeros)
+                const bool valid = kb_tile + j * 8 + qcol + e < hi;
                 sc[j][e] = valid ? sc[j][e] * scale : -INFINITY;
                 tmax = fmaxf(tmax, sc[j][e]);
             }
